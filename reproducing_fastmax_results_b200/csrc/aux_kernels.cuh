@@ -1,0 +1,217 @@
+// Memory-bound helper kernels: segment-state scans, forward combine/divide, backward prologue, output casts
+// and the q/k normalisation.
+#pragma once
+#include "common.cuh"
+
+namespace fm {
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+enum ScanOp { SCAN_PREFIX = 0, SCAN_SUFFIX = 1, SCAN_TOTAL = 2 };
+
+// seg: [BH][nseg][n] segment totals.  PREFIX/SUFFIX: replaced in place by the exclusive running sum
+// (starting from init[head] when given).  TOTAL: slot 0 of each head receives the sum of all segments.
+// total_out[head] (optional) = init + all segments.
+__global__ void state_scan_kernel(float* seg, int nseg, long long n, const float* init, float* total_out, int op,
+                                  long long total_elems) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total_elems) return;
+  long long head = idx / n, e = idx - head * n;
+  float run = init ? init[idx] : 0.f;
+  float* base = seg + head * nseg * n + e;
+  if (op == SCAN_PREFIX) {
+    for (int s = 0; s < nseg; ++s) {
+      float t = base[(long long)s * n];
+      base[(long long)s * n] = run;
+      run += t;
+    }
+  } else if (op == SCAN_SUFFIX) {
+    for (int s = nseg - 1; s >= 0; --s) {
+      float t = base[(long long)s * n];
+      base[(long long)s * n] = run;
+      run += t;
+    }
+  } else {
+    for (int s = 0; s < nseg; ++s) run += base[(long long)s * n];
+    base[0] = run;
+  }
+  if (total_out) total_out[idx] = run;
+}
+
+// O' accumulator [BH][nq][ld] -> o = O'[:, :d] / O'[:, d] (dtype T, strided) and g = O'[:, d] (float, strided).
+template <typename T>
+__global__ void finalize_fwd_kernel(const float* __restrict__ acc, int ld, int d, int nq, int heads, View o, View g,
+                                    long long total) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  int c = (int)(idx % d);
+  long long row = idx / d;
+  int l = (int)(row % nq);
+  int head = (int)(row / nq);
+  const float* r = acc + row * ld;
+  float den = r[d];
+  int b = head / heads, h = head - b * heads;
+  T* op = reinterpret_cast<T*>(const_cast<void*>(o.ptr)) + (long long)b * o.sb + (long long)h * o.sh + (long long)l * o.sn;
+  op[c] = from_float<T>(r[c] / den);
+  if (c == 0 && g.ptr != nullptr) {
+    float* gp = reinterpret_cast<float*>(const_cast<void*>(g.ptr)) + (long long)b * g.sb + (long long)h * g.sh +
+                (long long)l * g.sn;
+    *gp = den;
+  }
+}
+
+// dO'[row] = [dO/g, -(dO . o)/g, 0, 0, 0]  (float, row stride ld = d+4); one warp per row.
+template <typename T>
+__global__ void bwd_prologue_kernel(View dout, View o, View g, float* __restrict__ dop, int ld, int d, int nq,
+                                    int heads, long long nrows) {
+  long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  if (row >= nrows) return;
+  int l = (int)(row % nq);
+  int head = (int)(row / nq);
+  int b = head / heads, h = head - b * heads;
+  const T* dp = reinterpret_cast<const T*>(dout.ptr) + (long long)b * dout.sb + (long long)h * dout.sh + (long long)l * dout.sn;
+  const T* op = reinterpret_cast<const T*>(o.ptr) + (long long)b * o.sb + (long long)h * o.sh + (long long)l * o.sn;
+  const float gv = *(reinterpret_cast<const float*>(g.ptr) + (long long)b * g.sb + (long long)h * g.sh + (long long)l * g.sn);
+  const float inv = 1.f / gv;
+  float dot = 0.f;
+  float* out = dop + row * ld;
+  for (int c = lane; c < d; c += 32) {
+    float x = to_float<T>(dp[c]);
+    dot += x * to_float<T>(op[c]);
+    out[c] = x * inv;
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+  if (lane == 0) out[d] = -dot * inv;
+  if (lane >= 1 && lane < ld - d) out[d + lane] = 0.f;
+}
+
+// fp32 accumulator [BH][n][d] -> strided output of dtype T
+template <typename T>
+__global__ void cast_out_kernel(const float* __restrict__ acc, int d, int n, int heads, View out, long long total) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  int c = (int)(idx % d);
+  long long row = idx / d;
+  int l = (int)(row % n);
+  int head = (int)(row / n);
+  int b = head / heads, h = head - b * heads;
+  T* op = reinterpret_cast<T*>(const_cast<void*>(out.ptr)) + (long long)b * out.sb + (long long)h * out.sh + (long long)l * out.sn;
+  op[c] = from_float<T>(acc[idx]);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// q/k normalisation:  y = lim * (x - mean_d x) / max_l ||x_l - mean_d x_l||
+// stats[head] is a packed 64-bit word: (bits of max squared norm) << 32 | (0xffffffff - argmax token),
+// so an atomicMax picks the largest norm and, among equals, the first token (what argmax returns).
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void norm_stats_kernel(View x, int d, int n, int heads, unsigned long long* stats, long long nrows) {
+  long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  if (row >= nrows) return;
+  int l = (int)(row % n);
+  int head = (int)(row / n);
+  int b = head / heads, h = head - b * heads;
+  const T* xp = reinterpret_cast<const T*>(x.ptr) + (long long)b * x.sb + (long long)h * x.sh + (long long)l * x.sn;
+  float s = 0.f;
+  for (int c = lane; c < d; c += 32) s += to_float<T>(xp[c]);
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
+  const float mean = s / (float)d;
+  float q = 0.f;
+  for (int c = lane; c < d; c += 32) {
+    float t = to_float<T>(xp[c]) - mean;
+    q += t * t;
+  }
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) q += __shfl_xor_sync(0xffffffffu, q, k);
+  if (lane == 0) {
+    unsigned long long packed = ((unsigned long long)__float_as_uint(q) << 32) | (unsigned long long)(0xffffffffu - (unsigned)l);
+    atomicMax(stats + head, packed);
+  }
+}
+
+template <typename T>
+__global__ void norm_apply_kernel(View x, View y, int d, int n, int heads, const unsigned long long* stats, float lim,
+                                  long long nrows) {
+  long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  if (row >= nrows) return;
+  int l = (int)(row % n);
+  int head = (int)(row / n);
+  int b = head / heads, h = head - b * heads;
+  const T* xp = reinterpret_cast<const T*>(x.ptr) + (long long)b * x.sb + (long long)h * x.sh + (long long)l * x.sn;
+  T* yp = reinterpret_cast<T*>(const_cast<void*>(y.ptr)) + (long long)b * y.sb + (long long)h * y.sh + (long long)l * y.sn;
+  float s = 0.f;
+  for (int c = lane; c < d; c += 32) s += to_float<T>(xp[c]);
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
+  const float mean = s / (float)d;
+  const float m = sqrtf(__uint_as_float((unsigned)(stats[head] >> 32)));
+  const float sc = lim / m;
+  for (int c = lane; c < d; c += 32) yp[c] = from_float<T>((to_float<T>(xp[c]) - mean) * sc);
+}
+
+// per head: scratch[head] = sum_{l,c} dy * y      (y = normalised output; x - mean = y * m / lim)
+template <typename T>
+__global__ void norm_bwd_dot_kernel(View y, View dy, int d, int n, int heads, float* scratch, long long nrows) {
+  long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  if (row >= nrows) return;
+  int l = (int)(row % n);
+  int head = (int)(row / n);
+  int b = head / heads, h = head - b * heads;
+  const T* yp = reinterpret_cast<const T*>(y.ptr) + (long long)b * y.sb + (long long)h * y.sh + (long long)l * y.sn;
+  const T* gp = reinterpret_cast<const T*>(dy.ptr) + (long long)b * dy.sb + (long long)h * dy.sh + (long long)l * dy.sn;
+  float q = 0.f;
+  for (int c = lane; c < d; c += 32) q += to_float<T>(gp[c]) * to_float<T>(yp[c]);
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) q += __shfl_xor_sync(0xffffffffu, q, k);
+  if (lane == 0) atomicAdd(scratch + head, q);
+}
+
+// dx = (lim/m) * (dy - mean_d dy)  -  [l == argmax] * scratch[head] / (lim * m) * y
+// (the max flows through its arg-max token only; y rows have zero mean, so centring leaves that term as is)
+template <typename T>
+__global__ void norm_bwd_apply_kernel(View y, View dy, View dx, int d, int n, int heads,
+                                      const unsigned long long* stats, const float* scratch, float lim,
+                                      long long nrows) {
+  long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  if (row >= nrows) return;
+  int l = (int)(row % n);
+  int head = (int)(row / n);
+  int b = head / heads, h = head - b * heads;
+  const T* yp = reinterpret_cast<const T*>(y.ptr) + (long long)b * y.sb + (long long)h * y.sh + (long long)l * y.sn;
+  const T* gp = reinterpret_cast<const T*>(dy.ptr) + (long long)b * dy.sb + (long long)h * dy.sh + (long long)l * dy.sn;
+  T* op = reinterpret_cast<T*>(const_cast<void*>(dx.ptr)) + (long long)b * dx.sb + (long long)h * dx.sh + (long long)l * dx.sn;
+  const unsigned long long st = stats[head];
+  const float m = sqrtf(__uint_as_float((unsigned)(st >> 32)));
+  const int am = (int)(0xffffffffu - (unsigned)(st & 0xffffffffu));
+  const float sc = lim / m;
+  float sg = 0.f;
+  for (int c = lane; c < d; c += 32) sg += to_float<T>(gp[c]);
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) sg += __shfl_xor_sync(0xffffffffu, sg, k);
+  const float gmean = sg / (float)d;
+  const float extra = (l == am) ? -scratch[head] / (lim * m) : 0.f;
+  for (int c = lane; c < d; c += 32) {
+    float v = sc * (to_float<T>(gp[c]) - gmean) + extra * to_float<T>(yp[c]);
+    op[c] = from_float<T>(v);
+  }
+}
+
+}  // namespace fm

@@ -1,0 +1,252 @@
+// PyTorch extension `fastmax_cuda`: a thin shim over the C ABI of include/fastmax_b200.h.
+//
+// It exports the two functions of the reference's binding (fastmax_cuda.cpp:17-37)
+//     forwardpass(q,k,v,drop_noise,rpe_matrix,mask,dropout,normalize,temperature,a0,a1,a2,lim,p) -> o
+//     backwardpass(q,k,v,o,grad_output,mask,a0,a1,a2,p) -> [gradq, gradk, gradv]
+// with the reference's tensor contract ((n, b*h, d) float32 contiguous CUDA tensors, o = (nq, b*h, d+1) with
+// the denominator in the last column), plus strided/bf16 entry points used by the FastMax autograd Function.
+// torch is used for memory (outputs, workspace from the caching allocator), the device guard and the
+// current stream; all arithmetic happens in the library's own kernels.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <vector>
+
+#include "../../include/fastmax_b200.h"
+
+namespace {
+
+#define CHECK_CUDA(x) TORCH_CHECK(x.device().is_cuda(), #x " must be a CUDA tensor")
+#define CHECK_CONTIGUOUS(x) TORCH_CHECK(x.is_contiguous(), #x " must be contiguous")
+#define CHECK_INPUT(x) \
+  CHECK_CUDA(x);       \
+  CHECK_CONTIGUOUS(x)
+
+void check_status(int rc, const char* what) {
+  if (rc == FASTMAX_OK) return;
+  if (rc == FASTMAX_ERR_CUDA)
+    TORCH_CHECK(false, what, ": ", fastmax_status_string(rc), " (",
+                fastmax_last_cuda_error_string(), ")");
+  TORCH_CHECK(false, what, ": ", fastmax_status_string(rc));
+}
+
+int dtype_of(const torch::Tensor& t) {
+  if (t.scalar_type() == torch::kFloat32) return FASTMAX_F32;
+  if (t.scalar_type() == torch::kBFloat16) return FASTMAX_BF16;
+  TORCH_CHECK(false, "fastmax: tensors must be float32 or bfloat16, got ", t.scalar_type());
+}
+
+// (n, bh, d) contiguous -> view with batch=1
+fastmax_tensor view_nbd(const torch::Tensor& t) {
+  return fastmax_tensor{t.data_ptr(), 0, t.stride(1), t.stride(0)};
+}
+// (b, h, n, d) with unit innermost stride
+fastmax_tensor view_bhnd(const torch::Tensor& t) {
+  TORCH_CHECK(t.dim() == 4, "fastmax: expected a 4-D (b,h,n,d) tensor");
+  TORCH_CHECK(t.size(3) == 1 || t.stride(3) == 1, "fastmax: the head dim must be contiguous");
+  return fastmax_tensor{t.data_ptr(), t.stride(0), t.stride(1), t.stride(2)};
+}
+fastmax_tensor view_bhn(const torch::Tensor& t) {  // float (b,h,n)
+  return fastmax_tensor{t.data_ptr(), t.stride(0), t.stride(1), t.stride(2)};
+}
+
+torch::Tensor workspace(size_t bytes, const torch::Tensor& like) {
+  return torch::empty({(int64_t)(bytes + 256)}, like.options().dtype(torch::kUInt8));
+}
+void* aligned(const torch::Tensor& ws) {
+  uintptr_t p = (uintptr_t)ws.data_ptr();
+  return (void*)((p + 255) / 256 * 256);
+}
+
+// ---- the reference's binding -----------------------------------------------------------------------
+torch::Tensor forwardpass(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor drop_noise,
+                          torch::Tensor rpe_matrix, bool mask, float dropout, bool normalize, float temperature,
+                          float a0, float a1, float a2, float lim, int p) {
+  CHECK_INPUT(q);
+  CHECK_INPUT(k);
+  CHECK_INPUT(v);
+  (void)drop_noise;  // dead inputs of the reference: its dropout kernel runs with scale 0 (fwd.cu:443)
+  (void)rpe_matrix;  // and its RPE add is commented out (fwd.cu:289)
+  (void)dropout;
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "q, k, v must be (n, b*h, d)");
+  TORCH_CHECK(q.scalar_type() == torch::kFloat32 && k.scalar_type() == torch::kFloat32 &&
+                  v.scalar_type() == torch::kFloat32,
+              "forwardpass takes float32 tensors");
+  const c10::cuda::CUDAGuard guard(q.device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  const int nq = q.size(0), nk = k.size(0), bh = q.size(1), d = q.size(2);
+  // the reference scales k by 1/temperature in place (fwd.cu:282-292) and normalises q, k in place
+  // (fwd.cu:424-433); callers keep the mutated tensors for backward (model.py:29-37).
+  if (normalize) {
+    auto stats = torch::empty({bh}, q.options().dtype(torch::kInt64));
+    fastmax_tensor qv = view_nbd(q), kv = view_nbd(k);
+    check_status(fastmax_normalize_forward(1, bh, nq, d, FASTMAX_F32, lim, &qv, &qv, (uint64_t*)stats.data_ptr(), stream),
+                 "fastmax normalize(q)");
+    check_status(fastmax_normalize_forward(1, bh, nk, d, FASTMAX_F32, lim, &kv, &kv, (uint64_t*)stats.data_ptr(), stream),
+                 "fastmax normalize(k)");
+  }
+  if (temperature != 1.0f) k.div_(temperature);
+  auto o = torch::empty({nq, bh, d + 1}, q.options());
+  fastmax_problem pb{};
+  pb.batch = 1; pb.heads = bh; pb.nq = nq; pb.nk = nk; pb.d = d; pb.order = p; pb.causal = mask ? 1 : 0;
+  pb.dtype = FASTMAX_F32; pb.a0 = a0; pb.a1 = a1; pb.a2 = a2; pb.inv_temperature = 1.0f;
+  fastmax_forward_args a{};
+  a.q = view_nbd(q); a.k = view_nbd(k); a.v = view_nbd(v);
+  a.o = fastmax_tensor{o.data_ptr(), 0, o.stride(1), o.stride(0)};
+  a.g = fastmax_tensor{(float*)o.data_ptr() + d, 0, o.stride(1), o.stride(0)};
+  size_t need = fastmax_forward_workspace(&pb, &a);
+  auto ws = workspace(need, q);
+  check_status(fastmax_forward(&pb, &a, aligned(ws), need, stream), "fastmax forwardpass");
+  return o;
+}
+
+std::vector<torch::Tensor> backwardpass(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor o,
+                                        torch::Tensor grad_output, bool mask, float a0, float a1, float a2, int p) {
+  CHECK_INPUT(q);
+  CHECK_INPUT(k);
+  CHECK_INPUT(v);
+  CHECK_INPUT(o);
+  CHECK_INPUT(grad_output);
+  const c10::cuda::CUDAGuard guard(q.device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  const int nq = q.size(0), nk = k.size(0), bh = q.size(1), d = q.size(2);
+  TORCH_CHECK(o.size(2) == d + 1, "o must be the (nq, b*h, d+1) tensor returned by forwardpass");
+  auto gradq = torch::empty_like(q), gradk = torch::empty_like(k), gradv = torch::empty_like(v);
+  fastmax_problem pb{};
+  pb.batch = 1; pb.heads = bh; pb.nq = nq; pb.nk = nk; pb.d = d; pb.order = p; pb.causal = mask ? 1 : 0;
+  pb.dtype = FASTMAX_F32; pb.a0 = a0; pb.a1 = a1; pb.a2 = a2; pb.inv_temperature = 1.0f;
+  fastmax_backward_args a{};
+  a.q = view_nbd(q); a.k = view_nbd(k); a.v = view_nbd(v);
+  a.o = fastmax_tensor{o.data_ptr(), 0, o.stride(1), o.stride(0)};
+  a.g = fastmax_tensor{(float*)o.data_ptr() + d, 0, o.stride(1), o.stride(0)};
+  a.d_out = view_nbd(grad_output);
+  a.dq = view_nbd(gradq); a.dk = view_nbd(gradk); a.dv = view_nbd(gradv);
+  size_t need = fastmax_backward_workspace(&pb, &a);
+  auto ws = workspace(need, q);
+  check_status(fastmax_backward(&pb, &a, aligned(ws), need, stream), "fastmax backwardpass");
+  return {gradq, gradk, gradv};
+}
+
+// ---- strided / bf16 entry points ((b, h, n, d) views, no permute copies) ----------------------------
+fastmax_problem make_problem(const torch::Tensor& q, const torch::Tensor& k, bool causal, double inv_temp, double a0,
+                             double a1, double a2, int64_t p, int64_t flags) {
+  fastmax_problem pb{};
+  pb.batch = q.size(0); pb.heads = q.size(1); pb.nq = q.size(2); pb.nk = k.size(2); pb.d = q.size(3);
+  pb.order = (int)p; pb.causal = causal ? 1 : 0; pb.dtype = dtype_of(q);
+  pb.a0 = (float)a0; pb.a1 = (float)a1; pb.a2 = (float)a2; pb.inv_temperature = (float)inv_temp;
+  pb.flags = (int)flags;
+  return pb;
+}
+
+// returns (o, g, state_out or empty)
+std::vector<torch::Tensor> forward(torch::Tensor q, torch::Tensor k, torch::Tensor v, bool causal, double inv_temp,
+                                   double a0, double a1, double a2, int64_t p, c10::optional<torch::Tensor> state_in,
+                                   bool want_state, bool want_output, int64_t flags) {
+  CHECK_CUDA(q); CHECK_CUDA(k); CHECK_CUDA(v);
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "q, k, v must be (b, h, n, d)");
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(), "q, k, v dtypes differ");
+  const c10::cuda::CUDAGuard guard(q.device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  fastmax_problem pb = make_problem(q, k, causal, inv_temp, a0, a1, a2, p, flags);
+  fastmax_forward_args a{};
+  a.q = view_bhnd(q); a.k = view_bhnd(k); a.v = view_bhnd(v);
+  torch::Tensor o, g, sout;
+  if (want_output) {
+    o = torch::empty({q.size(0), q.size(1), q.size(2), q.size(3)}, q.options());
+    g = torch::empty({q.size(0), q.size(1), q.size(2)}, q.options().dtype(torch::kFloat32));
+    a.o = view_bhnd(o);
+    a.g = view_bhn(g);
+  }
+  if (state_in.has_value() && state_in->defined()) {
+    TORCH_CHECK(state_in->is_contiguous() && state_in->scalar_type() == torch::kFloat32 &&
+                    (size_t)state_in->numel() * 4 == fastmax_state_bytes(&pb),
+                "state_in has the wrong size");
+    a.state_in = (const float*)state_in->data_ptr();
+  }
+  if (want_state) {
+    sout = torch::empty({q.size(0), q.size(1), fastmax_state_rows(pb.d, pb.order), fastmax_state_ld(pb.d)},
+                        q.options().dtype(torch::kFloat32));
+    a.state_out = (float*)sout.data_ptr();
+  }
+  size_t need = fastmax_forward_workspace(&pb, &a);
+  auto ws = workspace(need, q);
+  check_status(fastmax_forward(&pb, &a, aligned(ws), need, stream), "fastmax forward");
+  return {o, g, sout};
+}
+
+// returns (dq, dk, dv, dstate_out or empty)
+std::vector<torch::Tensor> backward(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor o, torch::Tensor g,
+                                    torch::Tensor d_out, bool causal, double inv_temp, double a0, double a1, double a2,
+                                    int64_t p, c10::optional<torch::Tensor> state_in,
+                                    c10::optional<torch::Tensor> dstate_in, bool want_dstate, bool want_grads,
+                                    int64_t flags) {
+  CHECK_CUDA(q); CHECK_CUDA(k); CHECK_CUDA(v); CHECK_CUDA(o); CHECK_CUDA(g); CHECK_CUDA(d_out);
+  TORCH_CHECK(g.scalar_type() == torch::kFloat32, "g must be float32");
+  const c10::cuda::CUDAGuard guard(q.device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  fastmax_problem pb = make_problem(q, k, causal, inv_temp, a0, a1, a2, p, flags);
+  fastmax_backward_args a{};
+  a.q = view_bhnd(q); a.k = view_bhnd(k); a.v = view_bhnd(v); a.o = view_bhnd(o); a.g = view_bhn(g);
+  a.d_out = view_bhnd(d_out);
+  torch::Tensor dq, dk, dv, dsout;
+  if (want_grads) {
+    dq = torch::empty(q.sizes(), q.options());
+    dk = torch::empty(k.sizes(), k.options());
+    dv = torch::empty(v.sizes(), v.options());
+    a.dq = view_bhnd(dq); a.dk = view_bhnd(dk); a.dv = view_bhnd(dv);
+  }
+  if (state_in.has_value() && state_in->defined()) a.state_in = (const float*)state_in->data_ptr();
+  if (dstate_in.has_value() && dstate_in->defined()) a.dstate_in = (const float*)dstate_in->data_ptr();
+  if (want_dstate) {
+    dsout = torch::empty({q.size(0), q.size(1), fastmax_state_rows(pb.d, pb.order), fastmax_state_ld(pb.d)},
+                         q.options().dtype(torch::kFloat32));
+    a.dstate_out = (float*)dsout.data_ptr();
+  }
+  size_t need = fastmax_backward_workspace(&pb, &a);
+  auto ws = workspace(need, q);
+  check_status(fastmax_backward(&pb, &a, aligned(ws), need, stream), "fastmax backward");
+  return {dq, dk, dv, dsout};
+}
+
+// y = lim * normalise(x); returns (y, stats)
+std::vector<torch::Tensor> normalize_forward(torch::Tensor x, double lim) {
+  CHECK_CUDA(x);
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  auto y = torch::empty(x.sizes(), x.options());
+  auto stats = torch::empty({x.size(0), x.size(1)}, x.options().dtype(torch::kInt64));
+  fastmax_tensor xv = view_bhnd(x), yv = view_bhnd(y);
+  check_status(fastmax_normalize_forward(x.size(0), x.size(1), x.size(2), x.size(3), dtype_of(x), (float)lim, &xv, &yv,
+                                         (uint64_t*)stats.data_ptr(), stream),
+               "fastmax normalize_forward");
+  return {y, stats};
+}
+
+torch::Tensor normalize_backward(torch::Tensor y, torch::Tensor dy, torch::Tensor stats, double lim) {
+  CHECK_CUDA(y); CHECK_CUDA(dy);
+  const c10::cuda::CUDAGuard guard(y.device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  auto dx = torch::empty(y.sizes(), y.options());
+  auto scratch = torch::empty({y.size(0) * y.size(1)}, y.options().dtype(torch::kFloat32));
+  fastmax_tensor yv = view_bhnd(y), gv = view_bhnd(dy), dv = view_bhnd(dx);
+  check_status(fastmax_normalize_backward(y.size(0), y.size(1), y.size(2), y.size(3), dtype_of(y), (float)lim, &yv, &gv,
+                                          &dv, (const uint64_t*)stats.data_ptr(), (float*)scratch.data_ptr(), stream),
+               "fastmax normalize_backward");
+  return dx;
+}
+
+int64_t launch_count() { return (int64_t)fastmax_launch_count(); }
+
+}  // namespace
+
+PYBIND11_MODULE(fastmax_cuda, m) {
+  m.def("forwardpass", &forwardpass, "forwardpass");
+  m.def("backwardpass", &backwardpass, "backwardpass");
+  m.def("forward", &forward, "strided (b,h,n,d) forward: returns [o, g, state_out]");
+  m.def("backward", &backward, "strided (b,h,n,d) backward: returns [dq, dk, dv, dstate_out]");
+  m.def("normalize_forward", &normalize_forward, "q/k normalisation: returns [y, stats]");
+  m.def("normalize_backward", &normalize_backward, "gradient of the q/k normalisation");
+  m.def("launch_count", &launch_count, "kernel launches issued by the library so far");
+  m.def("version", []() { return std::string(fastmax_version()); });
+}

@@ -1,0 +1,6 @@
+// Instantiates the CUDA-core Fastmax kernels for head dim 64.
+#include "scan_inst.cuh"
+namespace fm {
+template cudaError_t launch_scan_d<64>(int, int, bool, const ScanParams&, dim3, cudaStream_t);
+template cudaError_t launch_moments_d<64>(int, int, const MomentParams&, dim3, cudaStream_t);
+}  // namespace fm

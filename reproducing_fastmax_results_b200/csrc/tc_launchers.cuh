@@ -1,0 +1,15 @@
+// Entry points of the tcgen05 / TMA kernels.  Each returns FASTMAX_TC_NOT_HANDLED when the problem is
+// outside what the tensor-core kernels cover, and the caller then runs the CUDA-core engine.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#include "../../include/fastmax_b200.h"
+
+namespace fm {
+enum { FASTMAX_TC_NOT_HANDLED = -1 };
+size_t tc_forward_workspace(const fastmax_problem* pb, const fastmax_forward_args* a);
+size_t tc_backward_workspace(const fastmax_problem* pb, const fastmax_backward_args* a);
+int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void* ws, size_t ws_bytes, cudaStream_t st);
+}  // namespace fm

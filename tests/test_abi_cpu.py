@@ -1,0 +1,94 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every declared symbol, and validates arguments
+before touching the GPU (no kernel is launched here)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from reproducing_fastmax_results_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "fastmax_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fastmax_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    lib = _lib.load()
+    names = _declared_functions()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/fastmax_b200.h but not exported"
+    assert set(_lib.EXPORTED_SYMBOLS) <= set(names)
+
+
+def test_state_geometry():
+    lib = _lib.load()
+    assert lib.fastmax_state_rows(64, 2) == 36 * 64 + 65
+    assert lib.fastmax_state_rows(32, 2) == 10 * 64 + 33
+    assert lib.fastmax_state_rows(16, 2) == 3 * 64 + 17
+    assert lib.fastmax_state_rows(64, 1) == 65
+    assert lib.fastmax_state_ld(64) == 68
+    pb = _lib.Problem(2, 3, 10, 10, 32, 2, 1, 0, 1, 1, 0.5, 1.0, 0, 0)
+    assert lib.fastmax_state_bytes(C.byref(pb)) == 6 * 673 * 36 * 4
+
+
+def _args(ptr=4096):
+    a = _lib.ForwardArgs()
+    for t in (a.q, a.k, a.v, a.o, a.g):
+        t.ptr, t.stride_b, t.stride_h, t.stride_n = ptr, 64 * 32, 32 * 64, 32
+    return a
+
+
+@pytest.mark.parametrize("field,value,status", [
+    ("d", 48, 2), ("order", 3, 2), ("dtype", 7, 1), ("batch", 0, 1), ("nq", 200, 2),
+])
+def test_forward_rejects_bad_problem(field, value, status):
+    lib = _lib.load()
+    pb = _lib.Problem(1, 2, 64, 64, 32, 2, 1, 0, 1, 1, 0.5, 1.0, 0, 0)
+    setattr(pb, field, value)
+    a = _args()
+    assert lib.fastmax_forward(C.byref(pb), C.byref(a), None, 0, None) == status
+    assert lib.fastmax_status_string(status)
+
+
+def test_forward_rejects_misaligned_and_small_workspace():
+    lib = _lib.load()
+    pb = _lib.Problem(1, 2, 64, 64, 32, 2, 1, 0, 1, 1, 0.5, 1.0, 0, 0)
+    a = _args(ptr=4100)
+    assert lib.fastmax_forward(C.byref(pb), C.byref(a), None, 0, None) == 6
+    a = _args()
+    a.k.stride_n = 33
+    assert lib.fastmax_forward(C.byref(pb), C.byref(a), None, 0, None) == 6
+    a = _args()
+    need = lib.fastmax_forward_workspace(C.byref(pb), C.byref(a))
+    assert need > 2 * 64 * 36 * 4
+    assert lib.fastmax_forward(C.byref(pb), C.byref(a), C.c_void_p(4096), need - 1, None) == 3
+    assert lib.fastmax_forward(C.byref(pb), C.byref(a), C.c_void_p(4097), need, None) == 3
+    a.q.ptr = None
+    assert lib.fastmax_forward(C.byref(pb), C.byref(a), C.c_void_p(4096), need, None) == 1
+
+
+def test_backward_rejects_bad_arguments():
+    lib = _lib.load()
+    pb = _lib.Problem(1, 2, 64, 64, 32, 2, 1, 0, 1, 1, 0.5, 1.0, 0, 0)
+    b = _lib.BackwardArgs()
+    assert lib.fastmax_backward(C.byref(pb), C.byref(b), None, 0, None) == 1  # nothing requested
+    for t in (b.q, b.k, b.v, b.o, b.g, b.d_out, b.dq):
+        t.ptr, t.stride_b, t.stride_h, t.stride_n = 4096, 4096, 2048, 32
+    assert lib.fastmax_backward(C.byref(pb), C.byref(b), None, 0, None) == 1  # dq without dk, dv
+    assert lib.fastmax_launch_count() == 0
+
+
+def test_python_extension_module_is_importable_under_reference_name():
+    import reproducing_fastmax_results_b200 as pkg
+
+    ext = pkg.load_extension()
+    import fastmax_cuda
+
+    assert ext is fastmax_cuda
+    assert hasattr(ext, "forwardpass") and hasattr(ext, "backwardpass")

@@ -1,0 +1,101 @@
+"""The reference-facing operator: `fastmax_cuda.forwardpass/backwardpass`, the reference's autograd.Function
+twin and the FastMax Function, checked against the oracle and the golden vectors."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from cases import CASES, make_inputs
+from oracle import fastmax_oracle as orc
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.npz"))
+
+
+def host(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+@pytest.mark.parametrize("mask", [False, True])
+@pytest.mark.parametrize("p", [1, 2])
+def test_forwardpass_backwardpass_contract(mask, p):
+    """(n, b*h, d) float32 in, (nq, b*h, d+1) out with the denominator in the last column; k is scaled by
+    1/temperature in place and the gradients are w.r.t. the scaled k (fastmax_cuda_forward.cu:282-292,
+    transformer/model.py:74)."""
+    import reproducing_fastmax_results_b200 as pkg
+
+    ext = pkg.load_extension()
+    n, bh, d, t = 50, 6, 32, 3.0
+    rng = np.random.default_rng(1)
+    q, k, v, do = (rng.standard_normal((n, bh, d)).astype(np.float32) for _ in range(4))
+    qd, kd, vd, dod = (torch.from_numpy(x).cuda() for x in (q, k, v, do))
+    noise = torch.zeros_like(qd)
+    rpe = torch.zeros(2 * n - 1, d, device="cuda")
+    o = ext.forwardpass(qd, kd, vd, noise, rpe, mask, 0.1, False, t, 1.0, 1.0, 0.5, 1.0, p)
+    assert o.shape == (n, bh, d + 1)
+    assert torch.allclose(kd, torch.from_numpy(k).cuda() / t)
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / t, p)
+    qh, kh, vh, doh = (np.transpose(x, (1, 0, 2)) for x in (q, k, v, do))
+    o_ref, g_ref = orc.fastmax_naive(qh, kh, vh, mask, poly)
+    assert orc.max_norm_err(host(o[:, :, :d]).transpose(1, 0, 2), o_ref) < 1e-4
+    assert orc.max_norm_err(host(o[:, :, d]).T, g_ref) < 1e-4
+    gq, gk, gv = ext.backwardpass(qd, kd, vd, o, dod, mask, 1.0, 1.0, 0.5, p)
+    dq_ref, dk_ref, dv_ref = orc.fastmax_naive_grads(qh, kh, vh, doh, mask, poly)
+    assert orc.max_norm_err(host(gq).transpose(1, 0, 2), dq_ref) < 1e-4
+    assert orc.max_norm_err(host(gk).transpose(1, 0, 2) / t, dk_ref) < 1e-4
+    assert orc.max_norm_err(host(gv).transpose(1, 0, 2), dv_ref) < 1e-4
+    assert torch.equal(dod, torch.from_numpy(do).cuda())  # the upstream gradient is not modified
+
+
+@pytest.mark.parametrize("fn_name", ["FastMax", "FASTMultiHeadAttention_Function"])
+@pytest.mark.parametrize("name", ["small_p2_causal", "small_p1_noncausal", "cfg1_p2_noncausal"])
+def test_autograd_functions_match_reference(fn_name, name):
+    import reproducing_fastmax_results_b200 as pkg
+
+    fn = getattr(pkg, fn_name)
+    B, H, N, D, p, mask, nt, scale, upstream = CASES[name]
+    q, k, v, do = (torch.from_numpy(x).cuda() for x in make_inputs(name))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    noise = torch.zeros_like(q)
+    rpe = pkg.rpe_matrix_creator(N, D, q.device, q.dtype)
+    o = fn.apply(q, k, v, noise, rpe, mask, 0.0, False, nt * math.sqrt(D), 1.0, 1.0, 0.5, 1.0, p)
+    o.backward(do)
+    for got, key in ((o, "o"), (q.grad, "dq"), (k.grad, "dk"), (v.grad, "dv")):
+        assert orc.max_norm_err(host(got), GOLD[f"{name}/einops/{key}"]) < 1e-4, key
+
+
+@pytest.mark.parametrize("name", ["small_p2_causal", "small_p2_noncausal"])
+def test_fastmax_normalized_attention_matches_reference(name):
+    """normalize=True: q, k normalised as fastattention_einops.normalize does, gradient through it exact."""
+    import reproducing_fastmax_results_b200 as pkg
+
+    B, H, N, D, p, mask, nt, scale, upstream = CASES[name]
+    q, k, v, do = (torch.from_numpy(x).cuda() for x in make_inputs(name))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    o = pkg.fastmax(q, k, v, mask=mask, normalize=True, p=p)
+    o.backward(do)
+    for got, key in ((o, "o"), (q.grad, "dq"), (k.grad, "dk"), (v.grad, "dv")):
+        assert orc.max_norm_err(host(got), GOLD[f"{name}/normalized_attention/{key}"]) < 1e-4, key
+
+
+def test_fastmax_bf16_transposed_views_and_module():
+    import reproducing_fastmax_results_b200 as pkg
+
+    B, N, H, D = 2, 128, 4, 64
+    torch.manual_seed(0)
+    x = torch.randn(3, B, N, H, D, device="cuda", dtype=torch.bfloat16)
+    q, k, v = (x[i].transpose(1, 2).detach().requires_grad_(True) for i in range(3))
+    do = torch.randn(B, H, N, D, device="cuda", dtype=torch.bfloat16)
+    o = pkg.fastmax_custom(q, k, v, None, None, True, 0.0, False, 8.0 * math.sqrt(D), 1.0, 1.0, 0.5, 1.0, 2)
+    assert o.dtype == torch.bfloat16
+    o.backward(do)
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / (8.0 * math.sqrt(D)), 2)
+    o_ref, _ = orc.fastmax_naive(host(q), host(k), host(v), True, poly)
+    dq_ref, dk_ref, dv_ref = orc.fastmax_naive_grads(host(q), host(k), host(v), host(do), True, poly)
+    assert orc.max_norm_err(host(o), o_ref) < 2e-2
+    assert orc.max_norm_err(host(q.grad), dq_ref) < 2e-2
+    assert orc.max_norm_err(host(k.grad), dk_ref) < 2e-2
+    assert orc.max_norm_err(host(v.grad), dv_ref) < 2e-2
+    assert pkg.FASTMultiHeadAttention(use_custom_gradient=False)(q, k, v) == 0
