@@ -1,0 +1,360 @@
+#!/usr/bin/env python
+"""Benchmark of the Fastmax hot path:  python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (BASELINE config 2, the configuration the headline metric is quoted on): Fastmax order 2, causal,
+B=8, H=16, N=4096, D=Dv=64, bf16 inputs with fp32 accumulation, q,k,v ~ N(0,1), temperature 8*sqrt(D);
+one step = forward + backward over the whole batch.  Inputs are seeded synthetic tensors (the reference's
+datasets are not available offline).
+
+Multi-GPU: every (batch, head) is independent, so each rank processes its own B=8 batch with no data-path
+collective (weak scaling); the job's throughput is all ranks' tokens over the slowest rank's time.
+
+The printed JSON line carries: value (device-resident inputs, CUDA events), e2e (through the public operator
+with pinned HOST buffers, copies inside the timed region), roofline of the dominant kernel, per-kernel times,
+the CPU baseline (the oracle's restatement of the reference's factorised algorithm on the host cores) and the
+SM clocks sampled during the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, H, N, D, order, causal, dtype, input scale)
+    "cfg2_bf16_causal_p2_B8_H16_N4096_D64": (8, 16, 4096, 64, 2, True, "bf16", 1.0),
+    "small_bf16_causal_p2_B2_H4_N1024_D64": (2, 4, 1024, 64, 2, True, "bf16", 1.0),
+}
+DEFAULT = "cfg2_bf16_causal_p2_B8_H16_N4096_D64"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["_source"] = "measured"
+        return p
+    p = dict(FALLBACK_PEAKS)
+    p["_source"] = "fallback"
+    return p
+
+
+def algorithmic_flops(B, H, N, D, order):
+    """U = 2 B H N M (Dv+1), M = 1 + D + D^2 (order 2) or 1 + D: one GEMM pass over all tokens with the full
+    D^2 feature map.  forward = 2U (moment build + apply), backward = 4U (dq, dS, dk, dv)."""
+    M = 1 + D + (D * D if order == 2 else 0)
+    return 2.0 * B * H * N * M * (D + 1)
+
+
+def executed_units(D, order):
+    """Feature rows the kernels actually contract over (8x8 block-symmetric packing of x (x) x)."""
+    nb = D // 8
+    return (64 * nb * (nb + 1) // 2 if order == 2 else 0) + D + 1
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons for one GPU while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference's factorised algorithm, on the host cores
+# ----------------------------------------------------------------------------------------------------
+def cpu_sample(workload, n_sample=512, heads=1, reps=1):
+    """Times forward+backward of the factorised CPU algorithm (cumsum of per-token moments, the
+    reference's attention_mechanisms implementation) on `heads` heads of n_sample tokens with the workload's
+    D, order and mask.  Memory of that algorithm is O(N D^3) per head, which bounds the sample.
+    Returns (seconds per repetition, head-tokens per repetition, threads)."""
+    import torch
+
+    from oracle import fastmax_oracle as orc
+
+    B, H, N, D, order, causal, dtype, scale = WORKLOADS[workload]
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    q, k, v, do = (torch.randn(1, heads, n_sample, D, generator=g) * scale for _ in range(4))
+    if dtype == "bf16":
+        q, k, v, do = (t.bfloat16().float() for t in (q, k, v, do))
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / (8.0 * math.sqrt(D)), order)
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        orc.fastmax_factorized_fwd_bwd(q, k, v, do, causal, poly)
+        ts.append(time.perf_counter() - t0)
+    return min(ts), heads * n_sample, threads
+
+
+def run_reference_arm(args):
+    """`--impl reference`: the reference's CPU algorithm (oracle port) timed on the host, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    B, H, N, D, order, causal, dtype, scale = WORKLOADS[args.workload]
+    n_sample = args.cpu_tokens
+    for _ in range(args.warmup):
+        cpu_sample(args.workload, n_sample)
+    times = []
+    threads = 1
+    for _ in range(args.steps):
+        t, head_tokens, threads = cpu_sample(args.workload, n_sample)
+        times.append(t)
+    sec = sum(times) / len(times)
+    # metric tokens carry all H heads: one head of n_sample tokens is n_sample / H metric tokens
+    value = (n_sample / H) / sec / 1e6
+    line = {
+        "impl": "reference",
+        "metric": "fastmax_fwd_bwd_mtokens_per_s", "value": value, "unit": "Mtokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "sample": f"1 head x {n_sample} tokens per step"},
+        "cpu_baseline": {"value": value, "unit": "Mtokens/s", "cores": threads, "kind": "port",
+                         "sample": f"factorised causal order-{order} forward+backward (torch CPU, autograd) on 1 of "
+                                   f"{B * H} heads, {n_sample} of {N} tokens, D={D}; scaled by 1/H to metric tokens"},
+        "e2e": {"value": value, "unit": "Mtokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ----------------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-tokens", type=int, default=512, help="tokens of the bounded CPU-baseline sample")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-tensor-cores", action="store_true", help="force the CUDA-core kernels")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = max(args.warmup, 1)
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+
+    from reproducing_fastmax_results_b200 import _lib
+    import reproducing_fastmax_results_b200 as pkg
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, H, N, D, order, causal, dtype_name, scale = WORKLOADS[args.workload]
+    dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
+    inv_temp = 1.0 / (8.0 * math.sqrt(D))
+    flags = _lib.FLAG_NO_TENSOR_CORES if args.no_tensor_cores else 0
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q, k, v, do = ((torch.randn(B, H, N, D, device=dev, generator=gen) * scale).to(dtype) for _ in range(4))
+    lib = _lib.load()
+
+    def step():
+        o, g, _ = _lib.forward(q, k, v, causal, inv_temp, order=order, flags=flags)
+        return _lib.backward(q, k, v, o, g, do, causal, inv_temp, order=order, flags=flags)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.fastmax_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    launches = lib.fastmax_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    tokens_per_step = B * N * world
+    value = tokens_per_step / (ms_step * 1e-3) / 1e6
+
+    # ---- per-kernel device times (same steps again, launches bracketed by events) ----
+    _lib.profile(True)
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    _lib.profile(False)
+    prof = _lib.profile_collect()
+    kernels = {name: {"ms_per_launch": ms / cnt, "launches_per_step": cnt / args.steps, "ms_per_step": ms / args.steps}
+               for name, (ms, cnt) in prof.items()}
+    total_kernel_ms = sum(kk["ms_per_step"] for kk in kernels.values())
+    for kk in kernels.values():
+        kk["share"] = kk["ms_per_step"] / total_kernel_ms if total_kernel_ms else 0.0
+    pk = peaks()
+    U = algorithmic_flops(B, H, N, D, order)
+    units_alg = {"scan_fwd": 2.0, "tc_scan_fwd": 2.0, "scan_bwd_q": 1.0, "tc_scan_bwd_q": 1.0,
+                 "scan_bwd_kv": 3.0, "tc_scan_bwd_kv": 3.0, "moments_kv": 1.0, "moments_qg": 1.0, "tc_moments": 1.0}
+    dominant = max(kernels, key=lambda n: kernels[n]["ms_per_step"]) if kernels else None
+    roofline = None
+    if dominant is not None:
+        m_full = 1 + D + (D * D if order == 2 else 0)
+        ratio_exec = executed_units(D, order) / m_full
+        flops_alg = units_alg.get(dominant, 0.0) * U / max(kernels[dominant]["launches_per_step"], 1e-9)
+        dur_s = kernels[dominant]["ms_per_launch"] * 1e-3
+        peak = pk["bf16_tflops_sustained"] if dtype_name == "bf16" else pk["bf16_tflops_sustained"]
+        achieved = flops_alg / dur_s / 1e12
+        roofline = {
+            "kernel": dominant, "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak, "peak_source": pk["_source"] + " (sustained cuBLAS bf16: kernel timed inside a long step)",
+            "achieved_executed": achieved * ratio_exec,
+            "frac_executed": achieved * ratio_exec / peak,
+            "note": "achieved counts the full D^2 feature contraction (algorithmic flops); achieved_executed counts the "
+                    "block-symmetric feature rows the kernel really contracts over",
+            "traffic": None,
+        }
+    whole = {
+        "flops_alg_per_step": 6.0 * U,
+        "tflops_alg": 6.0 * U / (ms_step * 1e-3) / 1e12 / world * world,
+        "frac_of_peak": 6.0 * U / (ms_step * 1e-3) / 1e12 / (pk["bf16_tflops_sustained"]),
+    }
+
+    # ---- end to end: public operator, pinned host buffers, H2D + D2H inside the timed region ----
+    e2e = None
+    if not args.no_e2e:
+        hq, hk, hv, hdo = (x.cpu().pin_memory() for x in (q, k, v, do))
+        ho = torch.empty_like(hq).pin_memory()
+        hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(3))
+        temperature = 8.0 * math.sqrt(D)
+
+        def e2e_step():
+            dq_, dk_, dv_ = (x.to(dev, non_blocking=True) for x in (hq, hk, hv))
+            ddo = hdo.to(dev, non_blocking=True)
+            dq_.requires_grad_(True), dk_.requires_grad_(True), dv_.requires_grad_(True)
+            o = pkg.FastMax.apply(dq_, dk_, dv_, None, None, causal, 0.0, False, temperature, 1.0, 1.0, 0.5, 1.0, order)
+            o.backward(ddo)
+            ho.copy_(o.detach(), non_blocking=True)
+            hdq.copy_(dq_.grad, non_blocking=True)
+            hdk.copy_(dk_.grad, non_blocking=True)
+            hdv.copy_(dv_.grad, non_blocking=True)
+
+        for _ in range(max(1, min(args.warmup, 3))):
+            e2e_step()
+        barrier()
+        e2e_steps = max(3, min(args.steps, 10))
+        a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        b2.record()
+        barrier()
+        tt = torch.tensor([a.elapsed_time(b2)], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item()) / e2e_steps
+        nbytes = q.numel() * q.element_size()
+        e2e = {"value": tokens_per_step / (e2e_ms * 1e-3) / 1e6, "unit": "Mtokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "steps": e2e_steps,
+               "api": "reproducing_fastmax_results_b200.FastMax.apply + backward, pinned host q,k,v,dO in; o,dq,dk,dv out"}
+
+    cpu = None
+    if rank == 0 and not args.no_cpu and world >= 1:
+        sec, head_tokens, threads = cpu_sample(args.workload, args.cpu_tokens)
+        cpu = {"value": (args.cpu_tokens / H) / sec / 1e6, "unit": "Mtokens/s", "cores": threads, "kind": "port",
+               "seconds": sec,
+               "sample": f"factorised causal order-{order} forward+backward (torch CPU, autograd) on 1 of {B * H} heads, "
+                         f"{args.cpu_tokens} of {N} tokens, D={D}; scaled by 1/H to metric tokens"}
+
+    if rank == 0:
+        line = {
+            "metric": "fastmax_fwd_bwd_mtokens_per_s", "value": value, "unit": "Mtokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": dtype_name + " inputs, f32 accumulate", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": B, "heads": H, "seq_len": N, "head_dim": D,
+                       "order": order, "causal": causal, "parallelism": f"batch x head sharding, {world} rank(s), no collective",
+                       "l2": "inputs (268 MB) + workspace exceed the 126 MB L2; no explicit flush"},
+            "roofline": roofline, "whole_step": whole, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -83,9 +83,10 @@ def test_forward_backward_vs_oracle(shape, order, causal, dtype):
     assert orc.max_norm_err(g, g_ref) < 1e-4
     # gradients: the kernel differentiates at its own (rounded) o, g; the oracle at the exact ones
     dq_ref, dk_ref, dv_ref = orc.fastmax_naive_grads(qr, kr, vr, dor, causal, poly)
-    assert orc.max_norm_err(dq, dq_ref) < tol
-    assert orc.max_norm_err(dk, dk_ref) < tol
-    assert orc.max_norm_err(dv, dv_ref) < tol
+    # with a single visible key o == v exactly and dq, dk vanish analytically: floor the normaliser there
+    floor = 1e-2 if nk == 1 else 0.0
+    for got, ref in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+        assert np.abs(got - ref).max() / max(np.abs(ref).max(), floor) < tol
 
 
 @pytest.mark.parametrize("causal", [False, True])
