@@ -308,9 +308,11 @@ int32_t fastmax_forward(const fastmax_problem* pb, const fastmax_forward_args* a
   const bool want_o = a->o.ptr != nullptr;
   if (!want_o && !a->state_out) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (!pb->causal && a->state_in) return FASTMAX_ERR_INVALID_ARGUMENT;
-  if ((rc = check_view(a->k, pb->dtype, true))) return rc;
-  if ((rc = check_view(a->v, pb->dtype, true))) return rc;
-  if (want_o) {
+  if (pb->nk > 0) {
+    if ((rc = check_view(a->k, pb->dtype, true))) return rc;
+    if ((rc = check_view(a->v, pb->dtype, true))) return rc;
+  }
+  if (want_o && pb->nq > 0) {
     if ((rc = check_view(a->q, pb->dtype, true))) return rc;
     if ((rc = check_view(a->o, pb->dtype, false))) return rc;
   }

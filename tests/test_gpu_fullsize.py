@@ -18,7 +18,8 @@ def host(t):
 def _check_sampled(q, k, v, do, o, g, dq, dk, dv, causal, poly, heads, nrows, tol, rng):
     B, H, N, D = q.shape
     for (b, h) in heads:
-        qh, kh, vh, doh = (host(t[b, h]) for t in (q, k, v, do))
+        qh, kh, vh = (host(t[b, h]) for t in (q, k, v))
+        doh = host(do[b, h]) if do is not None else None
         oh, gh = host(o[b, h]), host(g[b, h])
         rows = sorted(set([0, 1, N // 2, N - 1] + list(rng.integers(0, N, nrows))))
         o_s, g_s = orc.sampled_forward_rows(qh, kh, vh, rows, causal, poly)
