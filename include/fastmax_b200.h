@@ -139,6 +139,10 @@ const char* fastmax_status_string(int32_t status);
 int32_t fastmax_last_cuda_error(void);           /* cudaError_t of the calling thread's last failing runtime call */
 const char* fastmax_last_cuda_error_string(void);
 const char* fastmax_version(void);
+/* Synchronous: copies back the device-side error word.  FASTMAX_ERR_DEVICE_TIMEOUT means a kernel of this
+ * library gave up on a bounded wait (its outputs are then incomplete); the word is cleared by the call.
+ * Call it after synchronising the stream.  No counterpart in the reference (it never checks its launches). */
+int32_t fastmax_check_status(void);
 /* Number of kernel launches issued by this library in this process (all entry points, all threads). */
 uint64_t fastmax_launch_count(void);
 

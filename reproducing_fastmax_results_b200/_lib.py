@@ -21,7 +21,7 @@ EXPORTED_SYMBOLS = [
     "fastmax_backward_workspace", "fastmax_backward",
     "fastmax_normalize_forward", "fastmax_normalize_backward",
     "fastmax_status_string", "fastmax_last_cuda_error", "fastmax_last_cuda_error_string",
-    "fastmax_version", "fastmax_launch_count",
+    "fastmax_version", "fastmax_launch_count", "fastmax_check_status",
     "fastmax_profile_enable", "fastmax_profile_kinds", "fastmax_profile_kind_name", "fastmax_profile_collect",
 ]
 
@@ -235,6 +235,14 @@ def normalize_backward(y, dy, stats, lim=1.0):
                                          C.byref(yv), C.byref(gv), C.byref(dv), stats.data_ptr(), scratch.data_ptr(),
                                          _stream()), "fastmax_normalize_backward")
     return dx
+
+
+def check_status():
+    """Synchronises the device and raises if a kernel reported a bounded-wait timeout."""
+    import torch
+
+    torch.cuda.synchronize()
+    check(load().fastmax_check_status(), "fastmax_check_status")
 
 
 def profile(enable):

@@ -63,6 +63,11 @@ static int sm_count() {
   return cached[dev];
 }
 
+int report_cuda_error(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return FASTMAX_ERR_CUDA;
+}
+
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 static inline View to_view(const fastmax_tensor& t) { return View{t.ptr, t.stride_b, t.stride_h, t.stride_n}; }
 
@@ -208,6 +213,23 @@ static int build_segment_states(const fastmax_problem* pb, const Plan& pl, int s
   return FASTMAX_OK;
 }
 
+int launch_finalize_fwd(const fastmax_problem* pb, const fastmax_forward_args* a, const float* oacc, cudaStream_t st) {
+  const int bh = pb->batch * pb->heads;
+  const int ld = state_ld(pb->d);
+  long long total = (long long)bh * pb->nq * pb->d;
+  int threads = 256;
+  unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  {
+    LaunchScope ls(KK_FINALIZE, st);
+    if (pb->dtype == FASTMAX_F32)
+      finalize_fwd_kernel<float><<<blocks, threads, 0, st>>>(oacc, ld, pb->d, pb->nq, pb->heads, to_view(a->o), to_view(a->g), total);
+    else
+      finalize_fwd_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(oacc, ld, pb->d, pb->nq, pb->heads, to_view(a->o), to_view(a->g), total);
+  }
+  FM_CUDA(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
 }  // namespace fm
 
 using namespace fm;
@@ -237,6 +259,13 @@ int32_t fastmax_last_cuda_error(void) { return g_last_cuda_error; }
 const char* fastmax_last_cuda_error_string(void) { return cudaGetErrorString((cudaError_t)g_last_cuda_error); }
 const char* fastmax_version(void) { return "fastmax_b200 0.1 (sm_100a)"; }
 uint64_t fastmax_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int32_t fastmax_check_status(void) {
+  int v = 0;
+  int rc = tc_device_status(&v);
+  if (rc) return rc;
+  return v ? FASTMAX_ERR_DEVICE_TIMEOUT : FASTMAX_OK;
+}
 
 int32_t fastmax_profile_enable(int32_t on) {
   g_prof_on.store(on ? 1 : 0);
@@ -371,18 +400,7 @@ int32_t fastmax_forward(const fastmax_problem* pb, const fastmax_forward_args* a
   dim3 grid(pl.nslices, P.nseg, pl.bh);
   FM_CUDA(launch_scan(pb->d, pb->dtype, MODE_FWD, pb->causal != 0, P, grid, st));
 
-  long long total = (long long)pl.bh * pb->nq * pb->d;
-  int threads = 256;
-  unsigned blocks = (unsigned)((total + threads - 1) / threads);
-  {
-    LaunchScope ls(KK_FINALIZE, st);
-    if (pb->dtype == FASTMAX_F32)
-      finalize_fwd_kernel<float><<<blocks, threads, 0, st>>>(oacc, pl.ld, pb->d, pb->nq, pb->heads, to_view(a->o), to_view(a->g), total);
-    else
-      finalize_fwd_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(oacc, pl.ld, pb->d, pb->nq, pb->heads, to_view(a->o), to_view(a->g), total);
-  }
-  FM_CUDA(cudaGetLastError());
-  return FASTMAX_OK;
+  return launch_finalize_fwd(pb, a, oacc, st);
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -12,4 +12,10 @@ size_t tc_forward_workspace(const fastmax_problem* pb, const fastmax_forward_arg
 size_t tc_backward_workspace(const fastmax_problem* pb, const fastmax_backward_args* a);
 int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void* ws, size_t ws_bytes, cudaStream_t st);
+// Reads (and clears) the device-side error word the bounded waits of the tensor-core kernels set.
+int tc_device_status(int* out);
+
+// shared with the C-ABI translation unit
+int report_cuda_error(cudaError_t e);  // remembers e for fastmax_last_cuda_error(), returns FASTMAX_ERR_CUDA
+int launch_finalize_fwd(const fastmax_problem* pb, const fastmax_forward_args* a, const float* oacc, cudaStream_t st);
 }  // namespace fm
