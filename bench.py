@@ -34,6 +34,8 @@ WORKLOADS = {
     # name: (B, H, N, D, order, causal, dtype, input scale)
     "cfg2_bf16_causal_p2_B8_H16_N4096_D64": (8, 16, 4096, 64, 2, True, "bf16", 1.0),
     "small_bf16_causal_p2_B2_H4_N1024_D64": (2, 4, 1024, 64, 2, True, "bf16", 1.0),
+    # profiling case: same per-CTA work as config 2, a few GB on the device, inputs (134 MB) larger than L2
+    "prof_bf16_causal_p2_B4_H16_N4096_D64": (4, 16, 4096, 64, 2, True, "bf16", 1.0),
 }
 DEFAULT = "cfg2_bf16_causal_p2_B8_H16_N4096_D64"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -190,6 +192,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-tensor-cores", action="store_true", help="force the CUDA-core kernels")
+    ap.add_argument("--mode", default="fwd_bwd", choices=["fwd_bwd", "fwd"],
+                    help="fwd: time the forward call only (profiling aid; the headline metric is fwd_bwd)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = max(args.warmup, 1)
@@ -222,6 +226,8 @@ def main():
 
     def step():
         o, g, _ = _lib.forward(q, k, v, causal, inv_temp, order=order, flags=flags)
+        if args.mode == "fwd":
+            return o
         return _lib.backward(q, k, v, o, g, do, causal, inv_temp, order=order, flags=flags)
 
     def barrier():
@@ -295,7 +301,7 @@ def main():
 
     # ---- end to end: public operator, pinned host buffers, H2D + D2H inside the timed region ----
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and args.mode == "fwd_bwd":
         hq, hk, hv, hdo = (x.cpu().pin_memory() for x in (q, k, v, do))
         ho = torch.empty_like(hq).pin_memory()
         hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(3))
@@ -341,7 +347,8 @@ def main():
 
     if rank == 0:
         line = {
-            "metric": "fastmax_fwd_bwd_mtokens_per_s", "value": value, "unit": "Mtokens/s", "n_gpus": world,
+            "metric": "fastmax_fwd_bwd_mtokens_per_s" if args.mode == "fwd_bwd" else "fastmax_fwd_mtokens_per_s",
+            "value": value, "unit": "Mtokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": dtype_name + " inputs, f32 accumulate", "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": B, "heads": H, "seq_len": N, "head_dim": D,

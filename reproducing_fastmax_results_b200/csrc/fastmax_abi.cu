@@ -335,6 +335,7 @@ int32_t fastmax_forward(const fastmax_problem* pb, const fastmax_forward_args* a
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const bool want_o = a->o.ptr != nullptr;
+  if (pb->nq == 0 && !a->state_out) return FASTMAX_OK;  // no queries, no state requested: nothing to do
   if (!want_o && !a->state_out) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (!pb->causal && a->state_in) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (pb->nk > 0) {

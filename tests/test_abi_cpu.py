@@ -71,7 +71,8 @@ def test_forward_rejects_misaligned_and_small_workspace():
     assert lib.fastmax_forward(C.byref(pb), C.byref(a), C.c_void_p(4097), need, None) == 3
     a.q.ptr = None
     assert lib.fastmax_forward(C.byref(pb), C.byref(a), C.c_void_p(4096), need, None) == 1
-    pb.nq = 0  # no queries: nothing to validate on q, nothing to launch for the output
+    pb.nq = 0  # no queries and no state requested: nothing to validate, nothing to launch
+    assert lib.fastmax_forward(C.byref(pb), C.byref(a), C.c_void_p(4096), need, None) == 0
 
 
 def test_backward_rejects_bad_arguments():
