@@ -213,6 +213,22 @@ static int build_segment_states(const fastmax_problem* pb, const Plan& pl, int s
   return FASTMAX_OK;
 }
 
+int launch_cast_out(const fastmax_problem* pb, const float* acc, int n, const fastmax_tensor* out, cudaStream_t st) {
+  const long long total = (long long)pb->batch * pb->heads * n * pb->d;
+  if (total == 0) return FASTMAX_OK;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  {
+    LaunchScope ls(KK_CAST, st);
+    if (pb->dtype == FASTMAX_F32)
+      cast_out_kernel<float><<<blocks, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out), total);
+    else
+      cast_out_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out), total);
+  }
+  FM_CUDA(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
 int launch_finalize_fwd(const fastmax_problem* pb, const fastmax_forward_args* a, const float* oacc, cudaStream_t st) {
   const int bh = pb->batch * pb->heads;
   const int ld = state_ld(pb->d);
