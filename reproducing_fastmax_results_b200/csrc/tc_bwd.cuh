@@ -10,12 +10,14 @@
 //   update S_t (128 x 80) += Phi_t(X_c)^T (MN-major) * Y_c (128 x 80)        (X, Y) = (K, [V|1]) | (Q, dO')
 // The chain rule through Phi (dz[m] += dphi[m,r] z[r], dz[r] += dphi[m,r] z[m]) runs on CUDA cores straight
 // out of TMEM; the weights of the polynomial are already inside Sb.
-// Warp roles: 0-7 producers (Phi tiles), 8-11 chain rule + dq/dk drain, 12-15 state conversion + dV drain,
-// 16 MMA issuer, 17 TMA loader.  All waits are bounded (abort flag + error code, as in the forward scan).
+// Warp roles: 0-3 producers (Phi tiles), 4-7 chain rule + dq/dk drain, 8-11 state conversion + dV drain,
+// 12 MMA issuer, 13 TMA loader (448 threads, so the chain-rule warps can keep dz[64] in registers).
+// All waits are bounded (abort flag + error code, as in the forward scan).
 #pragma once
 
-constexpr int BW_THREADS = 576;
-constexpr int BW_WARP_MMA = 16, BW_WARP_TMA = 17;
+constexpr int BW_THREADS = 448;
+constexpr int BW_NPRODUCER = 128;
+constexpr int BW_WARP_MMA = 12, BW_WARP_TMA = 13;
 constexpr int BW_NSLOT = 2;
 constexpr int BW_OFF_RING = 0;
 constexpr int BW_OFF_SB = BW_OFF_RING + BW_NSLOT * TILE;      // 65536
@@ -77,10 +79,10 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
   const int nch = P.nchunks;
 
   if (tid == 0) {
-    for (int i = 0; i < BW_NSLOT; ++i) { mbar_init(&bars[C_FULL + i], NPRODUCER); mbar_init(&bars[C_EMPTY + i], 1); }
+    for (int i = 0; i < BW_NSLOT; ++i) { mbar_init(&bars[C_FULL + i], BW_NPRODUCER); mbar_init(&bars[C_EMPTY + i], 1); }
     for (int i = 0; i < 4; ++i) { mbar_init(&bars[C_SB_READY + i], 128); mbar_init(&bars[C_S_DONE + i], 1); }
     mbar_init(&bars[C_RAW_READY], 1);
-    mbar_init(&bars[C_RAW_FREE], NPRODUCER + 128);
+    mbar_init(&bars[C_RAW_FREE], BW_NPRODUCER + 128);
     mbar_init(&bars[C_GY_READY], 1);
     mbar_init(&bars[C_GY_FREE], 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&bars[C_DPHI_DONE + i], 1); mbar_init(&bars[C_DPHI_FREE + i], 128); }
@@ -112,9 +114,9 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
   fence_proxy_async_smem();
   __syncthreads();
 
-  if (w < 8) {
-    // ================= producers =================
-    const int h = w >> 2, l = (w & 3) * 32 + lane;
+  if (w < 4) {
+    // ================= producers (each thread writes both 64-feature halves of its token row) =================
+    const int l = w * 32 + lane;
     uint32_t n = 0;
     bool ok = true;
     for (int i = 0; i < nch && ok; ++i) {
@@ -125,7 +127,8 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
         for (int which = ((KV && i > 0) ? 0 : 1); which < 2; ++which) {  // 0: Phi(Z) for the dV apply, 1: Phi(X) for the update
           const uint32_t slot = n % BW_NSLOT, k = n / BW_NSLOT;
           if (k > 0 && !WAIT(C_EMPTY + slot, k - 1)) { FAIL(111); ok = false; break; }
-          gen_tile(ring + slot * TILE, which == 0 ? ztile : xtile, gt, l, h);
+          gen_tile(ring + slot * TILE, which == 0 ? ztile : xtile, gt, l, 0);
+          gen_tile(ring + slot * TILE, which == 0 ? ztile : xtile, gt, l, 1);
           fence_proxy_async_smem();
           mbar_arrive(&bars[C_FULL + slot]);
           ++n;
@@ -133,7 +136,7 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
       }
       if (ok) mbar_arrive(&bars[C_RAW_FREE]);
     }
-  } else if (w < 12) {
+  } else if (w < 8) {
     // ================= chain rule: dphi (TMEM) -> dz rows =================
     const int l = (w & 3) * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16);
@@ -177,10 +180,17 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                   dzb[ri] += dphi * za[mi];
                 }
               }
+              // a, b are warp-uniform: selecting the block with an unrolled compare keeps dz in registers
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                dz[8 * a + j] += dza[j];
-                dz[8 * b + j] += dzb[j];
+              for (int blk = 0; blk < 8; ++blk) {
+                if (a == blk) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) dz[8 * blk + j] += dza[j];
+                }
+                if (b == blk) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) dz[8 * blk + j] += dzb[j];
+                }
               }
             } else {
 #pragma unroll
@@ -207,7 +217,7 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
         for (int j = 0; j < 64; ++j) dz[j] = 0.f;
       }
     }
-  } else if (w < 16) {
+  } else if (w < 12) {
     // ================= state conversion (+ dV drain) =================
     const int l = (w & 3) * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16);
