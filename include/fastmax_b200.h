@@ -34,7 +34,8 @@ typedef enum {
   FASTMAX_ERR_WORKSPACE = 3,         /* workspace missing, misaligned (256 B) or smaller than required         */
   FASTMAX_ERR_CUDA = 4,              /* a CUDA runtime call or launch failed; see fastmax_last_cuda_error()    */
   FASTMAX_ERR_DEVICE_TIMEOUT = 5,    /* a bounded device-side wait gave up (reported by fastmax_check_status)  */
-  FASTMAX_ERR_MISALIGNED = 6         /* a tensor base or stride breaks the 16-byte rule of the vector loads    */
+  FASTMAX_ERR_MISALIGNED = 6,        /* a tensor base or stride breaks the 16-byte rule of the vector loads    */
+  FASTMAX_ERR_SCRATCH_LIMIT = 7      /* fastmax_forward_static_scratch: the problem needs more than the built-in array */
 } fastmax_status;
 
 typedef enum { FASTMAX_F32 = 0, FASTMAX_BF16 = 1 } fastmax_dtype;
@@ -96,6 +97,21 @@ typedef struct {
 size_t fastmax_forward_workspace(const fastmax_problem* pb, const fastmax_forward_args* args);
 int32_t fastmax_forward(const fastmax_problem* pb, const fastmax_forward_args* args,
                         void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* Forward pass without a caller workspace.  No counterpart in the reference (its forward_cuda allocates with
+ * torch::zeros on every call, fastmax_cuda_forward.cu:404-414).
+ * For hosts that cannot allocate device memory when they call (a plugin inside a runtime that owns all of HBM,
+ * an FFI binding without an allocator, a "no allocation after start-up" rule): the scratch is a fixed array of
+ * FASTMAX_STATIC_SCRATCH_BYTES inside the library's device image, present on every GPU that loads the library
+ * until the process exits.  Inputs and outputs are still the caller's.  Same arguments and results as
+ * fastmax_forward.  A problem whose fastmax_forward_workspace() exceeds the array is refused with
+ * FASTMAX_ERR_SCRATCH_LIMIT.  The call itself performs no cudaMalloc / cudaFree.
+ * The first call on each device looks the array's address up (cudaGetSymbolAddress): make that first call
+ * before starting any stream capture.  All calls on a device share the one array: two calls whose kernels can
+ * overlap on the GPU (different streams without an ordering between them) race; calls on one stream are safe. */
+#define FASTMAX_STATIC_SCRATCH_BYTES (8u << 20)
+size_t fastmax_static_scratch_bytes(void);
+int32_t fastmax_forward_static_scratch(const fastmax_problem* pb, const fastmax_forward_args* args, void* cuda_stream);
 
 /* ---- backward -------------------------------------------------------------------------------------
  * Replaces backward_cuda / backwardpass (fastmax_cuda.cpp:26-32, fastmax_cuda_backward.cu:518-613) with

@@ -18,6 +18,7 @@ FLAG_NO_TENSOR_CORES = 1
 EXPORTED_SYMBOLS = [
     "fastmax_state_rows", "fastmax_state_ld", "fastmax_state_bytes",
     "fastmax_forward_workspace", "fastmax_forward",
+    "fastmax_static_scratch_bytes", "fastmax_forward_static_scratch",
     "fastmax_backward_workspace", "fastmax_backward",
     "fastmax_normalize_forward", "fastmax_normalize_backward",
     "fastmax_status_string", "fastmax_last_cuda_error", "fastmax_last_cuda_error_string",
@@ -80,6 +81,9 @@ def load():
     lib.fastmax_forward_workspace.argtypes = [C.POINTER(Problem), C.POINTER(ForwardArgs)]
     lib.fastmax_forward.restype = C.c_int32
     lib.fastmax_forward.argtypes = [C.POINTER(Problem), C.POINTER(ForwardArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.fastmax_static_scratch_bytes.restype = C.c_size_t
+    lib.fastmax_forward_static_scratch.restype = C.c_int32
+    lib.fastmax_forward_static_scratch.argtypes = [C.POINTER(Problem), C.POINTER(ForwardArgs), C.c_void_p]
     lib.fastmax_backward_workspace.restype = C.c_size_t
     lib.fastmax_backward_workspace.argtypes = [C.POINTER(Problem), C.POINTER(BackwardArgs)]
     lib.fastmax_backward.restype = C.c_int32
@@ -182,6 +186,22 @@ def forward(q, k, v, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, order=2, state_in
     ws, wptr = _workspace(need, q.device)
     check(lib.fastmax_forward(C.byref(pb), C.byref(args), wptr, need, _stream()), "fastmax_forward")
     return o, g, sout
+
+
+def forward_static_scratch(q, k, v, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, order=2, flags=0):
+    """Calls fastmax_forward_static_scratch: same as forward(), but the library's built-in scratch array is used
+    and no workspace is passed.  Returns (o, g)."""
+    import torch
+
+    lib = load()
+    pb = problem_for(q, k, causal, inv_temp, a0, a1, a2, order, flags)
+    args = ForwardArgs()
+    args.q, args.k, args.v = view_bhnd(q), view_bhnd(k), view_bhnd(v)
+    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    g = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
+    args.o, args.g = view_bhnd(o), view_bhn(g)
+    check(lib.fastmax_forward_static_scratch(C.byref(pb), C.byref(args), _stream()), "fastmax_forward_static_scratch")
+    return o, g
 
 
 def backward(q, k, v, o, g, d_out, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, order=2, state_in=None, dstate_in=None,

@@ -268,6 +268,7 @@ const char* fastmax_status_string(int32_t s) {
     case FASTMAX_ERR_CUDA: return "CUDA runtime error";
     case FASTMAX_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
     case FASTMAX_ERR_MISALIGNED: return "tensor base or stride not 16-byte aligned";
+    case FASTMAX_ERR_SCRATCH_LIMIT: return "the problem needs more scratch than the library's built-in static array holds";
   }
   return "unknown status";
 }
