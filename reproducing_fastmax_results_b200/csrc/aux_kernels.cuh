@@ -71,6 +71,53 @@ __global__ void finalize_fwd_kernel(const float* __restrict__ acc, int ld, int d
   }
 }
 
+// ---- 4-wide variants (grid.y = batch*head, 32-bit index math): used when the output view is 8/16-byte aligned ----
+template <typename T>
+__device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 v;
+  v.x = *reinterpret_cast<uint32_t*>(&lo);
+  v.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
+template <typename T>
+__global__ void finalize_fwd_vec_kernel(const float* __restrict__ acc, int ld, int d, int nq, int heads, View o, View g) {
+  const int head = blockIdx.y;
+  const int d4 = d >> 2;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= nq * d4) return;
+  const int l = t / d4, c = (t - l * d4) << 2;
+  const float* r = acc + ((long long)head * nq + l) * ld;
+  const float4 v = *reinterpret_cast<const float4*>(r + c);
+  const float den = r[d];
+  const float inv = 1.f / den;
+  const int b = head / heads, h = head - b * heads;
+  T* op = reinterpret_cast<T*>(const_cast<void*>(o.ptr)) + (long long)b * o.sb + (long long)h * o.sh + (long long)l * o.sn;
+  store4<T>(op + c, v.x * inv, v.y * inv, v.z * inv, v.w * inv);
+  if (c == 0 && g.ptr != nullptr)
+    *(reinterpret_cast<float*>(const_cast<void*>(g.ptr)) + (long long)b * g.sb + (long long)h * g.sh + (long long)l * g.sn) = den;
+}
+
+template <typename T>
+__global__ void cast_out_vec_kernel(const float* __restrict__ acc, int d, int n, int heads, View out) {
+  const int head = blockIdx.y;
+  const int d4 = d >> 2;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n * d4) return;
+  const int l = t / d4, c = (t - l * d4) << 2;
+  const float4 v = *reinterpret_cast<const float4*>(acc + ((long long)head * n + l) * d + c);
+  const int b = head / heads, h = head - b * heads;
+  T* op = reinterpret_cast<T*>(const_cast<void*>(out.ptr)) + (long long)b * out.sb + (long long)h * out.sh + (long long)l * out.sn;
+  store4<T>(op + c, v.x, v.y, v.z, v.w);
+}
+
 // dO'[row] = [dO/g, -(dO . o)/g, 0, 0, 0]  (float, row stride ld = d+4); one warp per row.
 template <typename T>
 __global__ void bwd_prologue_kernel(View dout, View o, View g, float* __restrict__ dop, int ld, int d, int nq,

@@ -213,10 +213,30 @@ static int build_segment_states(const fastmax_problem* pb, const Plan& pl, int s
   return FASTMAX_OK;
 }
 
+// a view whose rows can take 4-element vector stores
+static bool vec4_ok(const fastmax_tensor& t, int dtype) {
+  const size_t es = dtype == FASTMAX_F32 ? 4 : 2;
+  const size_t al = 4 * es;
+  return ((uintptr_t)t.ptr % al) == 0 && ((size_t)t.stride_b * es) % al == 0 && ((size_t)t.stride_h * es) % al == 0 &&
+         ((size_t)t.stride_n * es) % al == 0;
+}
+
 int launch_cast_out(const fastmax_problem* pb, const float* acc, int n, const fastmax_tensor* out, cudaStream_t st) {
   const long long total = (long long)pb->batch * pb->heads * n * pb->d;
   if (total == 0) return FASTMAX_OK;
   const int threads = 256;
+  if (vec4_ok(*out, pb->dtype) && (long long)n * pb->d / 4 < (1ll << 30)) {
+    dim3 grid((unsigned)(((long long)n * (pb->d / 4) + threads - 1) / threads), (unsigned)(pb->batch * pb->heads));
+    {
+      LaunchScope ls(KK_CAST, st);
+      if (pb->dtype == FASTMAX_F32)
+        cast_out_vec_kernel<float><<<grid, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out));
+      else
+        cast_out_vec_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out));
+    }
+    FM_CUDA(cudaGetLastError());
+    return FASTMAX_OK;
+  }
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   {
     LaunchScope ls(KK_CAST, st);
@@ -234,6 +254,18 @@ int launch_finalize_fwd(const fastmax_problem* pb, const fastmax_forward_args* a
   const int ld = state_ld(pb->d);
   long long total = (long long)bh * pb->nq * pb->d;
   int threads = 256;
+  if (vec4_ok(a->o, pb->dtype) && (long long)pb->nq * pb->d / 4 < (1ll << 30)) {
+    dim3 grid((unsigned)(((long long)pb->nq * (pb->d / 4) + threads - 1) / threads), (unsigned)bh);
+    {
+      LaunchScope ls(KK_FINALIZE, st);
+      if (pb->dtype == FASTMAX_F32)
+        finalize_fwd_vec_kernel<float><<<grid, threads, 0, st>>>(oacc, ld, pb->d, pb->nq, pb->heads, to_view(a->o), to_view(a->g));
+      else
+        finalize_fwd_vec_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(oacc, ld, pb->d, pb->nq, pb->heads, to_view(a->o), to_view(a->g));
+    }
+    FM_CUDA(cudaGetLastError());
+    return FASTMAX_OK;
+  }
   unsigned blocks = (unsigned)((total + threads - 1) / threads);
   {
     LaunchScope ls(KK_FINALIZE, st);
@@ -575,21 +607,9 @@ int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args*
   }
 
   // casts
-  struct { float* acc; const fastmax_tensor* t; int n; } outs[3] = {{dqa, &a->dq, pb->nq}, {dka, &a->dk, pb->nk}, {dva, &a->dv, pb->nk}};
-  for (auto& o : outs) {
-    long long total = (long long)pl.bh * o.n * pb->d;
-    if (total == 0) continue;
-    int threads = 256;
-    unsigned blocks = (unsigned)((total + threads - 1) / threads);
-    {
-      LaunchScope ls(KK_CAST, st);
-      if (pb->dtype == FASTMAX_F32)
-        cast_out_kernel<float><<<blocks, threads, 0, st>>>(o.acc, pb->d, o.n, pb->heads, to_view(*o.t), total);
-      else
-        cast_out_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(o.acc, pb->d, o.n, pb->heads, to_view(*o.t), total);
-    }
-    FM_CUDA(cudaGetLastError());
-  }
+  if ((rc = launch_cast_out(pb, dqa, pb->nq, &a->dq, st))) return rc;
+  if ((rc = launch_cast_out(pb, dka, pb->nk, &a->dk, st))) return rc;
+  if ((rc = launch_cast_out(pb, dva, pb->nk, &a->dv, st))) return rc;
   return FASTMAX_OK;
 }
 

@@ -557,12 +557,13 @@ __global__ void bwd_prologue_bf16_kernel(View dout, View o, View g, __nv_bfloat1
   const __nv_bfloat16* op = reinterpret_cast<const __nv_bfloat16*>(o.ptr) + (long long)b * o.sb + (long long)hh * o.sh + (long long)l * o.sn;
   const float gv = *(reinterpret_cast<const float*>(g.ptr) + (long long)b * g.sb + (long long)hh * g.sh + (long long)l * g.sn);
   const float inv = 1.f / gv;
-  const float x0 = __bfloat162float(dp[lane]), x1 = __bfloat162float(dp[lane + 32]);
-  float dot = x0 * __bfloat162float(op[lane]) + x1 * __bfloat162float(op[lane + 32]);
+  // lane owns columns 2*lane, 2*lane+1 (rows of dO and o are 4-byte aligned: validated on the host)
+  const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(dp)[lane]);
+  const float2 y = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(op)[lane]);
+  float dot = x.x * y.x + x.y * y.y;
 #pragma unroll
   for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
-  __nv_bfloat16* out = dop + row * 80;
-  out[lane] = __float2bfloat16_rn(x0 * inv);
-  out[lane + 32] = __float2bfloat16_rn(x1 * inv);
-  if (lane < 16) out[64 + lane] = __float2bfloat16_rn(lane == 0 ? -dot * inv : 0.f);
+  __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(dop + row * 80);
+  out[lane] = __floats2bfloat162_rn(x.x * inv, x.y * inv);
+  if (lane < 8) out[32 + lane] = __floats2bfloat162_rn(lane == 0 ? -dot * inv : 0.f, 0.f);
 }
