@@ -36,7 +36,10 @@ WORKLOADS = {
     "small_bf16_causal_p2_B2_H4_N1024_D64": (2, 4, 1024, 64, 2, True, "bf16", 1.0),
     # profiling case: same per-CTA work as config 2, a few GB on the device, inputs (134 MB) larger than L2
     "prof_bf16_causal_p2_B4_H16_N4096_D64": (4, 16, 4096, 64, 2, True, "bf16", 1.0),
+    # BASELINE config 3: one long causal sequence, cut into contiguous pieces across the ranks (strong scaling)
+    "cfg3_f32_causal_p2_B1_H8_N131072_D32": (1, 8, 131072, 32, 2, True, "f32", 1.0),
 }
+SEQUENCE_SHARDED = {"cfg3_f32_causal_p2_B1_H8_N131072_D32"}
 DEFAULT = "cfg2_bf16_causal_p2_B8_H16_N4096_D64"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -179,6 +182,88 @@ def run_reference_arm(args):
 
 
 # ----------------------------------------------------------------------------------------------------
+# GPU arm, sequence-sharded workload: every rank owns N/world consecutive tokens of all heads; the ranks
+# exchange the moment states (forward: exclusive prefix, backward: exclusive suffix) with one all_gather each.
+# ----------------------------------------------------------------------------------------------------
+def run_sequence_sharded(args, torch, dist, dev, rank, world):
+    from reproducing_fastmax_results_b200 import _lib, sequence_parallel as sp
+
+    B, H, N, D, order, causal, dtype_name, scale = WORKLOADS[args.workload]
+    dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
+    n_local = N // world
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q, k, v, do = ((torch.randn(B, H, n_local, D, device=dev, generator=gen) * scale).to(dtype) for _ in range(4))
+    eng = sp.CudaEngine(1.0 / (8.0 * math.sqrt(D)), p=order)
+    lib = _lib.load()
+
+    def step():
+        o, g, prefix = sp.forward(eng, q, k, v)
+        return sp.backward(eng, q, k, v, o, g, do, prefix)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else int(os.environ.get("LOCAL_RANK", "0")))
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.fastmax_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    launches = lib.fastmax_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    value = B * N / (ms_step * 1e-3) / 1e6
+    _lib.profile(True)
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    _lib.profile(False)
+    kernels = {name: {"ms_per_launch": ms / cnt, "launches_per_step": cnt / args.steps, "ms_per_step": ms / args.steps}
+               for name, (ms, cnt) in _lib.profile_collect().items()}
+    if rank == 0:
+        pk = peaks()
+        U = algorithmic_flops(B, H, N, D, order)
+        m_full = 1 + D + (D * D if order == 2 else 0)
+        executed = 6.0 * U * executed_units(D, order) / m_full / world  # per rank (the exchange replaces no flops)
+        rows = (64 * (D // 8) * (D // 8 + 1) // 2) + D + 1
+        state_bytes = B * H * rows * (D + 4) * 4
+        line = {
+            "metric": "fastmax_fwd_bwd_mtokens_per_s", "value": value, "unit": "Mtokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": dtype_name + " inputs, f32 accumulate", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": B, "heads": H, "seq_len": N, "tokens_per_rank": n_local,
+                       "head_dim": D, "order": order, "causal": causal,
+                       "parallelism": f"sequence pieces over {world} rank(s); all_gather of {state_bytes} state bytes per rank, "
+                                      "once forward (exclusive prefix) and once backward (exclusive suffix)",
+                       "l2": "inputs exceed the 126 MB L2 at 1-2 ranks; no explicit flush"},
+            "roofline": {"kernel": "whole step (fp32 CUDA-core engine)", "bound": "tensor",
+                         "achieved": executed / (ms_step * 1e-3) / 1e12, "peak": pk["bf16_tflops_sustained"] / 2.0,
+                         "unit": "TFLOP/s", "frac": executed / (ms_step * 1e-3) / 1e12 / (pk["bf16_tflops_sustained"] / 2.0),
+                         "peak_source": pk["_source"] + " bf16 sustained / 2 (TF32 runs at half the bf16 rate; no TF32 peak was measured)",
+                         "note": "executed flops of one rank over the step time; the fp32 engine runs on the FFMA pipe because "
+                                 "TF32 operands miss the 1e-4 tolerance", "traffic": None},
+            "kernels": kernels, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+# ----------------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------------
 def main():
@@ -216,6 +301,8 @@ def main():
 
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.workload in SEQUENCE_SHARDED:
+        return run_sequence_sharded(args, torch, dist, dev, rank, world)
     B, H, N, D, order, causal, dtype_name, scale = WORKLOADS[args.workload]
     dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
     inv_temp = 1.0 / (8.0 * math.sqrt(D))

@@ -237,15 +237,28 @@ def fastmax_streaming(q, k, v, mask: bool, poly: Poly, chunk: int = 64, state_in
     return o, Op[:, Dv]
 
 
-def fastmax_streaming_grads(q, k, v, do, mask: bool, poly: Poly, chunk: int = 64):
-    """Chunked two-scan backward for one head (nq == nk when causal).  Returns dq, dk, dv."""
+def grad_moment_state(q, do, o, g, poly: Poly):
+    """Gradient moments of a block of queries: sum_l Phi(q_l)^T dO'_l, (M, Dv+1), un-weighted."""
+    q = np.asarray(q, np.float64)
+    do = np.asarray(do, np.float64)
+    dO = np.concatenate([do / g[:, None], (-(do * o).sum(-1) / g)[:, None]], -1)
+    return _phi(q, poly.p).T @ dO
+
+
+def fastmax_streaming_grads(q, k, v, do, mask: bool, poly: Poly, chunk: int = 64, state_in=None, dstate_in=None,
+                            return_dstate=False):
+    """Chunked two-scan backward for one head (nq == nk when causal).  Returns dq, dk, dv.
+
+    state_in: moments of keys that precede this piece (as in the forward); dstate_in: gradient moments
+    sum Phi(q)^T dO' of the queries that FOLLOW this piece.  With return_dstate the piece's own gradient
+    moments added to dstate_in are returned too (what a sequence-parallel rank hands to the rank before it)."""
     q = np.asarray(q, np.float64)
     k = np.asarray(k, np.float64)
     v = np.asarray(v, np.float64)
     do = np.asarray(do, np.float64)
     nq, D = q.shape
     nk, Dv = v.shape
-    o, g = fastmax_streaming(q, k, v, mask, poly, chunk)
+    o, g = fastmax_streaming(q, k, v, mask, poly, chunk, state_in=state_in)
     w = _weights(D, poly)
     v1 = np.concatenate([v, np.ones((nk, 1))], -1)
     dO = np.concatenate([do / g[:, None], (-(do * o).sum(-1) / g)[:, None]], -1)
@@ -255,14 +268,14 @@ def fastmax_streaming_grads(q, k, v, do, mask: bool, poly: Poly, chunk: int = 64
     M = w.shape[0]
     if not mask:
         S = _phi(k, poly.p).T @ v1
-        dS = (_phi(q, poly.p) * w).T @ dO
+        dS = _phi(q, poly.p).T @ dO
         dq = _dphi_to_dx((dO @ S.T) * w, q, poly.p)
-        dk = _dphi_to_dx(v1 @ dS.T, k, poly.p)
-        dv = (_phi(k, poly.p) @ dS)[:, :Dv]
+        dk = _dphi_to_dx((v1 @ dS.T) * w, k, poly.p)
+        dv = ((_phi(k, poly.p) * w) @ dS)[:, :Dv]
         return dq, dk, dv
     assert nq == nk
     # forward-direction scan: dq
-    S = np.zeros((M, Dv + 1))
+    S = np.zeros((M, Dv + 1)) if state_in is None else np.array(state_in, np.float64)
     for c0 in range(0, nq, chunk):
         sl = slice(c0, c0 + chunk)
         sc = q[sl] @ k[sl].T * poly.inv_temp
@@ -270,16 +283,18 @@ def fastmax_streaming_grads(q, k, v, do, mask: bool, poly: Poly, chunk: int = 64
         dq[sl] = _dphi_to_dx((dO[sl] @ S.T) * w, q[sl], poly.p) + dA @ k[sl] * poly.inv_temp
         S = S + _phi(k[sl], poly.p).T @ v1[sl]
     # reverse-direction scan: dk, dv
-    dS = np.zeros((M, Dv + 1))
+    dS = np.zeros((M, Dv + 1)) if dstate_in is None else np.array(dstate_in, np.float64)
     starts = list(range(0, nq, chunk))
     for c0 in reversed(starts):
         sl = slice(c0, c0 + chunk)
         sc = q[sl] @ k[sl].T * poly.inv_temp
         A = np.tril(poly.f(sc))
         dA = np.tril((dO[sl] @ v1[sl].T) * poly.df(sc))
-        dk[sl] = _dphi_to_dx(v1[sl] @ dS.T, k[sl], poly.p) + dA.T @ q[sl] * poly.inv_temp
-        dv[sl] = (_phi(k[sl], poly.p) @ dS)[:, :Dv] + A.T @ dO[sl][:, :Dv]
-        dS = dS + (_phi(q[sl], poly.p) * w).T @ dO[sl]
+        dk[sl] = _dphi_to_dx((v1[sl] @ dS.T) * w, k[sl], poly.p) + dA.T @ q[sl] * poly.inv_temp
+        dv[sl] = ((_phi(k[sl], poly.p) * w) @ dS)[:, :Dv] + A.T @ dO[sl][:, :Dv]
+        dS = dS + _phi(q[sl], poly.p).T @ dO[sl]
+    if return_dstate:
+        return dq, dk, dv, dS
     return dq, dk, dv
 
 

@@ -1,0 +1,120 @@
+"""Sequence-parallel causal Fastmax: each rank holds a contiguous piece of the sequence (all heads).
+
+The reference has no multi-GPU path; this is the natural one for a linear-time attention: the only thing a rank
+needs from the ranks before it is the SUM of their moment states (a fixed-size (rows x ld) float32 array per head,
+independent of the sequence length), and the backward needs the sum of the gradient moments of the ranks after it.
+
+    forward   T_r  = Phi(K_r)^T [V_r | 1]                      (local, state-only call)
+              P_r  = sum_{r' < r} T_r'                          (all_gather + local exclusive prefix)
+              o_r  = fastmax(q_r, k_r, v_r, state_in = P_r)
+    backward  dT_r = Phi(Q_r)^T dO'_r                           (local, state-only call)
+              R_r  = sum_{r' > r} dT_r'                         (all_gather + local exclusive suffix)
+              dq_r, dk_r, dv_r = backward(..., state_in = P_r, dstate_in = R_r)
+
+The exchange is one all_gather of world_size x state bytes per direction (config 3: 8 heads x 673 x 36 x 4 B =
+775 KB per rank), latency-bound on NVLink.  The collective goes through torch.distributed (NCCL on GPUs; the same
+code runs on gloo for the CPU tests, where the compute engine is replaced by the CPU oracle).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def _world(group=None):
+    if not (dist.is_available() and dist.is_initialized()):
+        return 1, 0
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
+def exclusive_prefix(local: torch.Tensor, group=None) -> torch.Tensor:
+    """Sum of `local` over the ranks BEFORE this one (zeros on rank 0)."""
+    world, rank = _world(group)
+    if world == 1:
+        return torch.zeros_like(local)
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local.contiguous(), group=group)
+    out = torch.zeros_like(local)
+    for r in range(rank):
+        out += parts[r]
+    return out
+
+
+def exclusive_suffix(local: torch.Tensor, group=None) -> torch.Tensor:
+    """Sum of `local` over the ranks AFTER this one (zeros on the last rank)."""
+    world, rank = _world(group)
+    if world == 1:
+        return torch.zeros_like(local)
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local.contiguous(), group=group)
+    out = torch.zeros_like(local)
+    for r in range(rank + 1, world):
+        out += parts[r]
+    return out
+
+
+class CudaEngine:
+    """The library's kernels through the `fastmax_cuda` extension ((b, h, n, d) CUDA tensors)."""
+
+    def __init__(self, inv_temp, a0=1.0, a1=1.0, a2=0.5, p=2):
+        from . import load_extension
+
+        self.ext = load_extension()
+        self.cfg = (float(inv_temp), float(a0), float(a1), float(a2), int(p))
+
+    def key_state(self, k, v):
+        it, a0, a1, a2, p = self.cfg
+        return self.ext.forward(k, k, v, True, it, a0, a1, a2, p, None, True, False, 0)[2]
+
+    def forward(self, q, k, v, state_in):
+        it, a0, a1, a2, p = self.cfg
+        o, g, _ = self.ext.forward(q, k, v, True, it, a0, a1, a2, p, state_in, False, True, 0)
+        return o, g
+
+    def grad_state(self, q, k, v, o, g, do, state_in):
+        it, a0, a1, a2, p = self.cfg
+        return self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, None, True, False, 0)[3]
+
+    def backward(self, q, k, v, o, g, do, state_in, dstate_in):
+        it, a0, a1, a2, p = self.cfg
+        dq, dk, dv, _ = self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, dstate_in, False, True, 0)
+        return dq, dk, dv
+
+
+def forward(engine, q, k, v, group=None):
+    """Returns (o, g, prefix_state) for this rank's piece (prefix_state is None when there is one rank)."""
+    if _world(group)[0] == 1:
+        o, g = engine.forward(q, k, v, None)
+        return o, g, None
+    prefix = exclusive_prefix(engine.key_state(k, v), group)
+    o, g = engine.forward(q, k, v, prefix)
+    return o, g, prefix
+
+
+def backward(engine, q, k, v, o, g, do, prefix, group=None):
+    """Returns (dq, dk, dv) for this rank's piece; `prefix` is what forward() returned."""
+    if _world(group)[0] == 1:
+        return engine.backward(q, k, v, o, g, do, prefix, None)
+    suffix = exclusive_suffix(engine.grad_state(q, k, v, o, g, do, prefix), group)
+    return engine.backward(q, k, v, o, g, do, prefix, suffix)
+
+
+class SequenceParallelFastMax(torch.autograd.Function):
+    """Causal Fastmax over a sequence that is split into contiguous pieces across the ranks of `group`."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, temperature=1.0, a0=1.0, a1=1.0, a2=0.5, p=2, group=None):
+        engine = CudaEngine(1.0 / float(temperature), a0, a1, a2, p)
+        o, g, prefix = forward(engine, q, k, v, group)
+        ctx.save_for_backward(q, k, v, o, g, *([] if prefix is None else [prefix]))
+        ctx.engine, ctx.group = engine, group
+        return o
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        q, k, v, o, g = ctx.saved_tensors[:5]
+        prefix = ctx.saved_tensors[5] if len(ctx.saved_tensors) > 5 else None
+        if grad_output.stride(-1) != 1:
+            grad_output = grad_output.contiguous()
+        dq, dk, dv = backward(ctx.engine, q, k, v, o, g, grad_output, prefix, ctx.group)
+        return dq, dk, dv, None, None, None, None, None, None
