@@ -159,6 +159,10 @@ const char* fastmax_version(void);
  * library gave up on a bounded wait (its outputs are then incomplete); the word is cleared by the call.
  * Call it after synchronising the stream.  No counterpart in the reference (it never checks its launches). */
 int32_t fastmax_check_status(void);
+/* Diagnostics for FASTMAX_ERR_DEVICE_TIMEOUT: out[i] = how many thread blocks gave up first at wait site i
+ * (i = the site's code modulo 256; the codes are listed beside the waits in csrc/tc_*.cuh).  Synchronous; clears
+ * the counters.  No counterpart in the reference. */
+int32_t fastmax_debug_wait_histogram(int32_t* out, int32_t n);
 /* Number of kernel launches issued by this library in this process (all entry points, all threads). */
 uint64_t fastmax_launch_count(void);
 

@@ -49,7 +49,7 @@ void launch_end(int kind, cudaStream_t st) {
 }
 static const char* kKindNames[KK_COUNT] = {
     "moments_kv", "moments_qg", "state_scan", "scan_fwd", "scan_bwd_q", "scan_bwd_kv", "finalize_fwd",
-    "bwd_prologue", "cast_out", "normalize", "tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_moments", "p1_fwd", "tc_intra_fwd", "tc_intra_bwd"};
+    "bwd_prologue", "cast_out", "normalize", "tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_moments", "p1_fwd", "tc_intra_fwd", "tc_intra_bwd", "tc_transpose"};
 
 static int sm_count() {
   static int cached[64] = {0};
@@ -314,6 +314,11 @@ int32_t fastmax_check_status(void) {
   int rc = tc_device_status(&v);
   if (rc) return rc;
   return v ? FASTMAX_ERR_DEVICE_TIMEOUT : FASTMAX_OK;
+}
+
+int32_t fastmax_debug_wait_histogram(int32_t* out, int32_t n) {
+  if (!out || n <= 0) return FASTMAX_ERR_INVALID_ARGUMENT;
+  return tc_wait_histogram(out, n);
 }
 
 int32_t fastmax_profile_enable(int32_t on) {

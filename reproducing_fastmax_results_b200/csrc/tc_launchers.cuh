@@ -14,6 +14,8 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
 int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void* ws, size_t ws_bytes, cudaStream_t st);
 // Reads (and clears) the device-side error word the bounded waits of the tensor-core kernels set.
 int tc_device_status(int* out);
+// Copies (and clears) the per-wait-site give-up counters (index = error code & 255).
+int tc_wait_histogram(int* out, int n);
 
 // shared with the C-ABI translation unit
 int report_cuda_error(cudaError_t e);  // remembers e for fastmax_last_cuda_error(), returns FASTMAX_ERR_CUDA

@@ -1,0 +1,534 @@
+// Forward causal scan with the Phi operands in tensor memory.  Included by tc_kernels.cu inside fm::tc.
+//
+// Why: an SS tcgen05.mma with N = 80 reads 4 KB of A and 2.5 KB of B from shared memory per K = 16 step (52 clocks
+// of the 128 B/clock shared-memory pipe against 40 clocks of math), and a Phi tile that goes through shared
+// memory costs another write and the read again.  Here the Phi tiles never touch shared memory: CUDA cores
+// compute them in registers and store them with tcgen05.st into TMEM, where tcgen05.mma reads its A operand
+// (45 clocks per K = 16 step measured), so shared memory only carries the B operands ([V|1], the bf16 state
+// copy) and the raw q / k tiles.
+//
+// Per 128-token chunk c and 128-row feature tile t of the CTA's slice (4 tiles, the last slice 3):
+//     apply   O'_c (128 tok x 80) += Phi_t(Q_c) (128 tok x 128 feat, TMEM)    * Sb_t (128 feat x 80, smem)
+//     update  S_t  (128 feat x 80) += Phi_t(K_c)^T (128 feat x 128 tok, TMEM) * [V_c | 1] (128 tok x 80, smem)
+// A operands go through one ring of three 32-column TMEM buffers (128 lanes x 64 bf16 = a 64-deep K slab, four
+// MMAs).  A query slab holds 64 features of Phi(Q) (thread = token, from the raw q tile); a key slab holds 64
+// tokens of Phi(K)^T (thread = feature, from a transposed copy of k, [64][tokens], built by a small pre-pass
+// kernel and streamed with TMA into rows of 144 bytes); both cost two 128-bit shared loads per eight products.  Slab order per (c, t):
+// Q0 K0 Q1 K1 (Q0 Q1 K0 K1 in the last tile, so the O' drain overlaps the updates; K0 K1 only in chunk 0, where
+// there is no earlier state to apply).  Three producer sets of four warps each own one ring slot (set s makes the
+// slabs s, s+3, s+6, ... of the CTA's slab sequence), so every barrier has one producer and one consumer and no
+// waiter is ever more than one phase away from the barrier it polls.
+// TMEM columns: 0..319 four state accumulators, 320..399 O', 400..495 the ring.
+// Warp roles (608 threads): 0-3, 4-7, 8-11 producer sets, 12-15 consumers (state -> bf16 copy, O' drain), 16 apply
+// issuer, 17 update issuer, 18 TMA loader.  Every wait is bounded (abort flag + error code), as in the other kernels.
+#pragma once
+
+namespace s2 {
+
+constexpr int NSETS = 3;                               // producer sets = ring slots
+constexpr int THREADS = 32 * (4 * NSETS + 4 + 3);      // 608
+constexpr int W_CONS = 4 * NSETS, W_MMA = W_CONS + 4, W_MMA2 = W_MMA + 1, W_TMA = W_MMA + 2;
+constexpr int NRING = NSETS;
+constexpr int KT_ROW = 144;                            // row pitch of the transposed tile: 64 tokens + 8 (bank spread)
+constexpr int KT_BOX = 64 * KT_ROW;                    // 9216: one 64-token box, [64 dims][72 tokens]
+constexpr int KT_BUF = 2 * KT_BOX;                     // 18432
+constexpr int VPBUF = 10 * BLK;                       // [V|1] buffer: 9 column blocks + one zero block
+constexpr int OFF_SB = 0;                             // 4 x SB_TILE
+constexpr int OFF_VP = OFF_SB + 4 * SB_TILE;          // 73728, 2 buffers
+constexpr int OFF_RAWQ = OFF_VP + 2 * VPBUF;          // 114688, 2 x REGION, 128-byte swizzle
+constexpr int OFF_KT = OFF_RAWQ + 2 * REGION;         // 147456, 2 x KT_BUF (two 64-token boxes each, not swizzled)
+constexpr int OFF_BAR = OFF_KT + 2 * KT_BUF;          // 184320
+constexpr int OFF_OST = OFF_BAR + 512;                // O' staging for the bulk reduce: 128 rows x 68 floats
+constexpr int OST_BYTES = CH * 68 * 4;                // 34816
+constexpr int OFF_TL = OFF_OST + OST_BYTES;           // development build only: 4 roles x 256 time stamps
+#ifdef FM_TC_TIMELINE
+constexpr int SMEM_BYTES = OFF_TL + 4 * 2048 + 1024;
+#else
+constexpr int SMEM_BYTES = OFF_TL + 1024;
+#endif
+static_assert(OFF_RAWQ % 1024 == 0 && OFF_KT % 128 == 0, "swizzled tiles need 1024-byte alignment");
+constexpr uint32_t COL_O = 320u, COL_A = 400u;
+// barriers
+constexpr int B_FULL_Q = 0, B_FULL_K = 3, B_EMPTY = 6, B_Q_READY = 9, B_Q_FREE = 11, B_KT_READY = 13, B_KT_FREE = 15,
+              B_VP_READY = 17, B_VP_FREE = 19, B_SB_READY = 21, B_S_DONE = 25, B_A_DONE = 29, B_O_DONE = 33, B_O_FREE = 34,
+              B_OST_FREE = 35, B_OST_FULL = 36, B_COUNT = 37;
+
+__device__ __noinline__ bool wait_slow(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
+  return mbar_wait_abortable(bar, parity, WAIT_CYCLES, abort_flag);
+}
+// Waits for the phase of parity `parity`; the common case (already complete) is one try_wait.
+__device__ __forceinline__ bool wait_fast(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
+#ifdef FM_SPIN_TEST_WAIT
+#pragma unroll 1
+  for (int i = 0; i < FM_SPIN_TEST_WAIT; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+#else
+  if (mbar_try_wait(bar, parity)) return true;
+#endif
+  return wait_slow(bar, parity, abort_flag);
+}
+
+// Slab j of tile (c, t): is it a query slab, and which half (64 features / 64 tokens) does it hold?
+__device__ __forceinline__ void slab_kind(bool first_chunk, bool last_tile, int j, bool& is_q, int& half) {
+  if (first_chunk) { is_q = false; half = j; }
+  else if (last_tile) { is_q = (j < 2); half = j & 1; }
+  else { is_q = !(j & 1); half = j >> 1; }
+}
+
+// Row `row` of a 128-byte-swizzled tile with 128-byte rows: 16-byte chunk cc.
+__device__ __forceinline__ uint4 sw_chunk(const uint8_t* tile, int row, int cc) {
+  return *reinterpret_cast<const uint4*>(tile + row * 128 + ((cc ^ (row & 7)) << 4));
+}
+
+// Query slab: 64 features x[8a+mi] * x[8b+ri] of token row l of the raw [token][64] tile -> 32 packed registers
+// (register 4 mi + j holds ri = 2j, 2j + 1).
+__device__ __forceinline__ void query_pair_slab(uint32_t (&r)[32], const uint8_t* raw, int l, int a, int b) {
+  const uint4 xa4 = sw_chunk(raw, l, a);
+  const uint4 xb4 = sw_chunk(raw, l, b);
+  const uint32_t xa[4] = {xa4.x, xa4.y, xa4.z, xa4.w};
+#pragma unroll
+  for (int mi = 0; mi < 8; ++mi) {
+    const uint32_t pr = xa[mi >> 1];
+    const uint32_t bc = (mi & 1) ? __byte_perm(pr, pr, 0x3232) : __byte_perm(pr, pr, 0x1010);
+    r[4 * mi + 0] = hmul2_u32(bc, xb4.x);
+    r[4 * mi + 1] = hmul2_u32(bc, xb4.y);
+    r[4 * mi + 2] = hmul2_u32(bc, xb4.z);
+    r[4 * mi + 3] = hmul2_u32(bc, xb4.w);
+  }
+}
+// Key slab: products x[i][tok] * x[j][tok] for the 64 tokens of one box of the transposed tile ([64 dims] rows of
+// KT_ROW bytes, not swizzled: the pitch spreads consecutive rows over the banks) -> 32 packed registers
+// (register 4 cc + jj holds tokens 8cc + 2jj, +1).
+__device__ __forceinline__ void key_pair_slab(uint32_t (&r)[32], const uint8_t* box, int i, int j) {
+  const uint4* ri = reinterpret_cast<const uint4*>(box + i * KT_ROW);
+  const uint4* rj = reinterpret_cast<const uint4*>(box + j * KT_ROW);
+#pragma unroll
+  for (int cc = 0; cc < 8; ++cc) {
+    const uint4 xi = ri[cc];
+    const uint4 xj = rj[cc];
+    r[4 * cc + 0] = hmul2_u32(xi.x, xj.x);
+    r[4 * cc + 1] = hmul2_u32(xi.y, xj.y);
+    r[4 * cc + 2] = hmul2_u32(xi.z, xj.z);
+    r[4 * cc + 3] = hmul2_u32(xi.w, xj.w);
+  }
+}
+__device__ __forceinline__ void copy_row_slab(uint32_t (&r)[32], const uint8_t* tile, int row) {  // swizzled tile
+#pragma unroll
+  for (int cc = 0; cc < 8; ++cc) {
+    const uint4 x = sw_chunk(tile, row, cc);
+    r[4 * cc + 0] = x.x; r[4 * cc + 1] = x.y; r[4 * cc + 2] = x.z; r[4 * cc + 3] = x.w;
+  }
+}
+__device__ __forceinline__ void copy_trow_slab(uint32_t (&r)[32], const uint8_t* box, int row) {  // transposed box
+  const uint4* rr = reinterpret_cast<const uint4*>(box + row * KT_ROW);
+#pragma unroll
+  for (int cc = 0; cc < 8; ++cc) {
+    const uint4 x = rr[cc];
+    r[4 * cc + 0] = x.x; r[4 * cc + 1] = x.y; r[4 * cc + 2] = x.z; r[4 * cc + 3] = x.w;
+  }
+}
+__device__ __forceinline__ void fill_slab(uint32_t (&r)[32], uint32_t v) {
+#pragma unroll
+  for (int c = 0; c < 32; ++c) r[c] = v;
+}
+
+// One slab of tile gt for TMEM lane `row`: query slabs take row = token, key slabs row = feature of the tile.
+// (a0, b0), (a1, b1): block pairs of the tile's two 64-feature units.  xt: transposed tile (two 64-token boxes).
+__device__ __forceinline__ void make_slab(uint32_t (&r)[32], bool is_q, int half, bool lin, int row, const uint8_t* raw,
+                                          const uint8_t* xt, int a0, int b0, int a1, int b1) {
+  if (is_q) {
+    if (!lin) query_pair_slab(r, raw, row, half ? a1 : a0, half ? b1 : b0);
+    else if (half == 0) copy_row_slab(r, raw, row);           // features 0..63 = x
+    else { fill_slab(r, 0u); r[0] = 0x00003F80u; }            // feature 64 = 1, the rest 0
+  } else {
+    const uint8_t* box = xt + half * KT_BOX;
+    if (!lin) {
+      const int hi = row >> 6;
+      key_pair_slab(r, box, 8 * (hi ? a1 : a0) + ((row >> 3) & 7), 8 * (hi ? b1 : b0) + (row & 7));
+    } else if (row < 64) copy_trow_slab(r, box, row);
+    else fill_slab(r, row == 64 ? 0x3F803F80u : 0u);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+scan_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmkt,
+                const __grid_constant__ CUtensorMap tmv, const FwdParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* sm = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* sb = sm + OFF_SB;
+  uint8_t* vp = sm + OFF_VP;
+  uint8_t* rawq = sm + OFF_RAWQ;
+  uint8_t* kt = sm + OFF_KT;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_BAR);
+  float* ost = reinterpret_cast<float*>(sm + OFF_OST);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_BAR + 320);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BAR + 328);
+
+  const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+  const int slice = blockIdx.x, head = blockIdx.z;
+  const int b_idx = head / P.heads, h_idx = head - b_idx * P.heads;
+  const int tile0 = slice * 4;
+  const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
+  const int nch = P.nchunks;
+#ifdef FM_TC_TIMELINE
+  // development aid: cheap (shared-memory) time stamps of one thread per role of CTA (0, 0), chunks 8..11
+  uint2* tl_ptr = nullptr;
+  int tl_n = 0, tl_c = 0;
+  if (blockIdx.x == 0 && blockIdx.z == 0 && lane == 0 && (w == W_MMA || w == 0 || w == W_MMA2 || w == W_CONS))
+    tl_ptr = reinterpret_cast<uint2*>(sm + OFF_TL) + 256 * (w == W_MMA ? 0 : (w == 0 ? 1 : (w == W_MMA2 ? 2 : 3)));
+#define S2_STAMP(tag) do { if (tl_ptr && tl_c >= 8 && tl_c < 12 && tl_n < 256) tl_ptr[tl_n++] = make_uint2((uint32_t)(tag), (uint32_t)clock()); } while (0)
+#define S2_CHUNK(c) tl_c = (c)
+#else
+#define S2_STAMP(tag) do { } while (0)
+#define S2_CHUNK(c) do { } while (0)
+#endif
+
+  if (tid == 0) {
+    // arrivals are one per WARP (an elected lane after __syncwarp), not one per thread
+    for (int i = 0; i < NRING; ++i) { mbar_init(&bars[B_FULL_Q + i], 4); mbar_init(&bars[B_FULL_K + i], 4); mbar_init(&bars[B_EMPTY + i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[B_Q_READY + i], 1);  mbar_init(&bars[B_Q_FREE + i], 4 * NSETS);
+      mbar_init(&bars[B_KT_READY + i], 1); mbar_init(&bars[B_KT_FREE + i], 4 * NSETS);
+      mbar_init(&bars[B_VP_READY + i], 1); mbar_init(&bars[B_VP_FREE + i], 1);
+    }
+    for (int i = 0; i < 4; ++i) { mbar_init(&bars[B_SB_READY + i], 4); mbar_init(&bars[B_S_DONE + i], 1); mbar_init(&bars[B_A_DONE + i], 1); }
+    mbar_init(&bars[B_O_DONE], 1);
+    mbar_init(&bars[B_O_FREE], 4);
+    mbar_init(&bars[B_OST_FREE], 1);
+    mbar_init(&bars[B_OST_FULL], 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (w == 0) tmem_alloc(tmem_slot, 512);
+  // the MMAs read one column block past the nine stored ones of each B operand: keep those bytes finite
+  for (int i = tid; i < (4 * SB_TILE + 2 * VPBUF) / 16; i += THREADS) reinterpret_cast<uint4*>(sb)[i] = make_uint4(0u, 0u, 0u, 0u);
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto WAIT = [&](int bar, uint32_t n) -> bool {  // waits for completion number n (0-based) of the barrier
+#if defined(FM_DBG_FREERUN) || defined(FM_DBG_FREERUN_WAITFULL)
+    if (bar >= B_Q_READY) return true;   // development aid: only the ring barriers are honoured
+#endif
+    return wait_fast(&bars[bar], n & 1u, abort_flag);
+  };
+  auto FAIL = [&](int code) {
+    if (*abort_flag == 0) atomicAdd(&g_tc_wait_hist[code & 255], 1);
+    *abort_flag = 1;
+    atomicExch(&g_tc_status, code);
+  };
+
+#if defined(FM_DBG_FREERUN) || defined(FM_DBG_FREERUN_WAITFULL)
+  if (w >= W_CONS && w != W_MMA && w != W_MMA2) { /* consumers and loader idle */ } else
+#endif
+#ifdef FM_DBG_FREERUN
+  if (w < W_CONS) { /* producers idle */ } else
+#endif
+  if (w < W_CONS) {
+    // ================= producers: Phi slabs into the TMEM ring =================
+    // Set s fills ring slot s, i.e. every slab whose index in the CTA's slab sequence is s (mod 3).
+    const int set = w >> 2;
+    const int row = (w & 3) * 32 + lane;  // TMEM lane: token (query slab) or feature of the tile (key slab)
+    const uint32_t slot_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16) + COL_A + 32u * set;
+    uint32_t pairs[4];                    // block pairs (a0, b0, a1, b1) of the two 64-feature units of each tile
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      int a0 = 0, b0 = 0, a1 = 0, b1 = 0;
+      if (tile0 + t < NTILES - 1) { pair_decode(2 * (tile0 + t), 8, a0, b0); pair_decode(2 * (tile0 + t) + 1, 8, a1, b1); }
+      pairs[t] = (uint32_t)(a0 | (b0 << 4) | (a1 << 8) | (b1 << 12));
+    }
+    int rem = 0;       // (index of the current tile's first slab) mod 3
+    uint32_t k = 0;    // slabs this set has produced = phase count of its slot
+    bool ok = true;
+    for (int c = 0; c < nch && ok; ++c) {
+      S2_CHUNK(c);
+      const int buf = c & 1;
+      if (!WAIT(B_KT_READY + buf, (uint32_t)(c >> 1)) || !WAIT(B_Q_READY + buf, (uint32_t)(c >> 1))) { FAIL(200); break; }
+      const uint8_t* raw = rawq + buf * REGION;
+      const uint8_t* xt = kt + buf * KT_BUF;
+      const int nb = c == 0 ? 2 : 4;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        if (t < ntl && ok) {
+          const bool lin = (tile0 + t == NTILES - 1);
+          const int a0 = pairs[t] & 15, b0 = (pairs[t] >> 4) & 15, a1 = (pairs[t] >> 8) & 15, b1 = (pairs[t] >> 12) & 15;
+          int j = set - rem;
+          if (j < 0) j += NSETS;
+#pragma unroll 1
+          for (; j < nb; j += NSETS, ++k) {
+            bool is_q; int half;
+            slab_kind(c == 0, t == ntl - 1, j, is_q, half);
+            S2_STAMP(40);
+            uint32_t r[32];
+#ifdef FM_DBG_NOPROD
+            fill_slab(r, 0x3C003C00u + (uint32_t)half + (is_q ? 1u : 0u) + (lin ? 2u : 0u) + (uint32_t)(a0 + b0 + a1 + b1));
+#else
+            make_slab(r, is_q, half, lin, row, raw, xt, a0, b0, a1, b1);
+#endif
+            S2_STAMP(41);
+            if (k > 0 && !WAIT(B_EMPTY + set, k - 1)) { FAIL(201); ok = false; break; }
+            __syncwarp();
+            S2_STAMP(42);
+            tc_fence_after_sync();
+            tmem_st32(slot_addr, r);
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[(is_q ? B_FULL_Q : B_FULL_K) + set]);
+            S2_STAMP(43);
+          }
+          rem += nb - NSETS;            // (rem + nb) mod 3 for nb = 2 or 4
+          if (rem < 0) rem += NSETS;
+          if (rem >= NSETS) rem -= NSETS;
+        }
+      }
+      if (ok) {
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars[B_Q_FREE + buf]);
+          mbar_arrive(&bars[B_KT_FREE + buf]);
+        }
+      }
+    }
+  } else if (w < W_MMA) {
+    // ================= consumers: state conversion and O' drain =================
+    const int l = (w & 3) * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16);
+    float* obase = P.oacc + (long long)head * P.nq * 68;
+    bool ok = true;
+    for (int c = 0; c < nch && ok; ++c) {
+      S2_CHUNK(c);
+      for (int t = 0; t < ntl && ok; ++t) {
+        if (t == ntl - 1 && c > 0) {  // O' of this chunk is complete once the last apply has finished
+          S2_STAMP(60);
+          if (!WAIT(B_O_DONE, (uint32_t)(c - 1))) { FAIL(220); ok = false; break; }
+          __syncwarp();
+          S2_STAMP(61);
+          tc_fence_after_sync();
+          uint32_t ra[32], rb[32], rc[8];
+          tmem_ld32(lane_addr + COL_O, ra);
+          tmem_ld32(lane_addr + COL_O + 32u, rb);
+          tmem_ld8(lane_addr + COL_O + 64u, rc);
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[B_O_FREE]);
+          // O' partial of this slice -> staging rows in shared memory -> ONE bulk reduce-add into the fp32 accumulator
+          // (the chunk's rows are contiguous there); the copy engine does the adds, fully coalesced.
+          if (c >= 2) {  // the previous chunk's reduce has read the staging rows
+            if (w == W_CONS && lane == 0) { bulk_wait_read_all(); mbar_arrive(&bars[B_OST_FREE]); }
+            if (!WAIT(B_OST_FREE, (uint32_t)(c - 2))) { FAIL(222); ok = false; break; }
+          }
+#ifndef FM_DBG_NOCONS
+          {
+            float4* rowp = reinterpret_cast<float4*>(ost + l * 68);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              rowp[j] = make_float4(__uint_as_float(ra[4 * j]), __uint_as_float(ra[4 * j + 1]), __uint_as_float(ra[4 * j + 2]),
+                                    __uint_as_float(ra[4 * j + 3]));
+              rowp[8 + j] = make_float4(__uint_as_float(rb[4 * j]), __uint_as_float(rb[4 * j + 1]), __uint_as_float(rb[4 * j + 2]),
+                                        __uint_as_float(rb[4 * j + 3]));
+            }
+            rowp[16] = make_float4(__uint_as_float(rc[0]), 0.f, 0.f, 0.f);
+          }
+#endif
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[B_OST_FULL]);
+          if (w == W_CONS) {  // the leader warp waits for all four warps' rows, one lane issues the reduce
+            if (!WAIT(B_OST_FULL, (uint32_t)(c - 1))) { FAIL(223); ok = false; break; }
+          }
+          if (w == W_CONS && lane == 0) {
+            const long long q0 = (long long)c * CH - P.off;  // query row of staging row 0
+            const int r0 = q0 < 0 ? (int)(-q0 < CH ? -q0 : CH) : 0;
+            const long long lim = (long long)P.nq - q0;
+            const int r1 = lim < CH ? (lim < 0 ? 0 : (int)lim) : CH;
+            if (r1 > r0) {
+              bulk_reduce_add_f32(obase + (q0 + r0) * 68, ost + r0 * 68, (uint32_t)(r1 - r0) * 272u);
+              bulk_commit_group();
+            }
+          }
+          S2_STAMP(62);
+        }
+        if (c < nch - 1) {  // the bf16 copy of S_t feeds the next chunk's apply
+          S2_STAMP(70);
+          // S_t is final (update issuer) and Sb_t is no longer read (apply issuer; chunk 0 has no apply)
+          if (!WAIT(B_S_DONE + t, (uint32_t)c) || (c > 0 && !WAIT(B_A_DONE + t, (uint32_t)(c - 1)))) { FAIL(221); ok = false; break; }
+          __syncwarp();
+          S2_STAMP(71);
+          tc_fence_after_sync();
+          const float wgt = tile_weight(tile0 + t, l, P.c0, P.c1, P.c2);
+          uint8_t* dst = sb + t * SB_TILE + l * 16;
+#ifdef FM_DBG_NOCONS
+          if (wgt == -12345.f)
+#endif
+          {
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              uint32_t r[32];
+              tmem_ld32(lane_addr + 80u * t + 32u * part, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int jb = 0; jb < 4; ++jb) store_block8(dst + (4 * part + jb) * BLK, &r[8 * jb], wgt);
+            }
+            uint32_t r8[8];
+            tmem_ld8(lane_addr + 80u * t + 64u, r8);
+            tmem_ld_wait();
+            store_block8(dst + 8 * BLK, r8, wgt);
+          }
+          fence_proxy_async_smem();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[B_SB_READY + t]);
+          S2_STAMP(72);
+        }
+      }
+    }
+    if (w == W_CONS && lane == 0) bulk_wait_all();  // the last reduce has landed before the CTA retires
+  } else if (w == W_MMA || w == W_MMA2) {
+    // ================= MMA issuers =================
+    // Warp W_MMA issues the apply MMAs (query slabs -> O'), warp W_MMA2 the update MMAs (key slabs -> S_t); the two
+    // accumulator chains are independent.  Both walk the whole slab sequence to know each slab's ring slot, but
+    // wait only for their own slabs, on per-kind `full` barriers whose phases count that kind's slabs in the slot.
+    // The whole warp runs the loop with warp-uniform values; one elected lane issues each instruction (elect.sync
+    // with a full mask always picks the same lane, which tcgen05.commit relies on).
+    {
+      const bool mine_q = (w == W_MMA);
+      constexpr uint32_t IDESC = make_idesc_bf16(128, 80, 0, 1);  // A from TMEM (K-major), B MN-major
+      const uint64_t dB_V = make_smem_desc(smem_u32(vp), 128, 2048, 0);
+      const uint64_t dB_S = make_smem_desc(smem_u32(sb), 128, 2048, 0);
+      const int b_full = mine_q ? B_FULL_Q : B_FULL_K;
+      uint32_t slot = 0;     // ring slot of the next slab of the sequence
+      uint32_t phases = 0;   // bit s: parity of the next phase of this issuer's `full` barrier of slot s
+      bool ok = true;
+      for (int c = 0; c < nch && ok; ++c) {
+        S2_CHUNK(c);
+        const int nb = c == 0 ? 2 : 4;
+        const uint64_t dB_Vc = dB_V + (uint64_t)(((c & 1) * VPBUF) >> 4);
+        if (!mine_q && !WAIT(B_VP_READY + (c & 1), (uint32_t)(c >> 1))) { FAIL(233); break; }
+        if (mine_q && c >= 2 && !WAIT(B_O_FREE, (uint32_t)(c - 2))) { FAIL(231); break; }
+        for (int t = 0; t < ntl && ok; ++t) {
+          // Sb_t holds S_t of the previous chunk (apply reads it; update may overwrite S_t once it has been copied)
+          if (c > 0 && !WAIT(B_SB_READY + t, (uint32_t)(c - 1))) { FAIL(230); ok = false; break; }
+          const bool last = (t == ntl - 1);
+          const uint64_t dB_St = dB_S + (uint64_t)((t * SB_TILE) >> 4);
+          const uint32_t d_state = tmem_base + 80u * t;
+#pragma unroll 1
+          for (int j = 0; j < nb; ++j) {
+            bool is_q; int half;
+            slab_kind(c == 0, last, j, is_q, half);
+            if (is_q == mine_q) {
+              S2_STAMP(10);
+#ifndef FM_DBG_FREERUN
+              if (!wait_fast(&bars[b_full + slot], (phases >> slot) & 1u, abort_flag)) { FAIL(232); ok = false; break; }
+#endif
+              __syncwarp();
+              S2_STAMP(11);
+              phases ^= (1u << slot);
+              tc_fence_after_sync();
+              const uint32_t a0 = tmem_base + COL_A + 32u * slot;
+              const uint32_t d = is_q ? (tmem_base + COL_O) : d_state;
+              const uint64_t b0 = (is_q ? dB_St : dB_Vc) + (uint64_t)(64 * half);
+              const uint32_t first = is_q ? ((t > 0 || half > 0) ? 1u : 0u) : ((c > 0 || half > 0) ? 1u : 0u);
+              mma_ts_elect(d, a0, b0, IDESC, first);
+              mma_ts_elect(d, a0 + 8u, b0 + 16u, IDESC, 1u);
+              mma_ts_elect(d, a0 + 16u, b0 + 32u, IDESC, 1u);
+              mma_ts_elect(d, a0 + 24u, b0 + 48u, IDESC, 1u);
+              mma_commit_elect(&bars[B_EMPTY + slot]);
+              if (half == 1) {
+                if (is_q) {
+                  mma_commit_elect(&bars[B_A_DONE + t]);
+                  if (last) mma_commit_elect(&bars[B_O_DONE]);
+                } else {
+                  mma_commit_elect(&bars[B_S_DONE + t]);
+                  if (last) mma_commit_elect(&bars[B_VP_FREE + (c & 1)]);
+                }
+              }
+              S2_STAMP(12);
+            }
+            if (++slot == NRING) slot = 0;
+          }
+        }
+      }
+      // every MMA of this issuer has completed once its last commit has arrived
+      if (ok && nch > 0) {
+        if (!mine_q) {
+          if (!wait_fast(&bars[B_VP_FREE + ((nch - 1) & 1)], (uint32_t)((nch - 1) >> 1) & 1u, abort_flag)) FAIL(235);
+        } else if (nch > 1) {
+          if (!wait_fast(&bars[B_A_DONE + ntl - 1], (uint32_t)(nch - 2) & 1u, abort_flag)) FAIL(236);
+        }
+      }
+      tc_fence_after_sync();
+    }
+  } else {
+    // ================= TMA loader =================
+    bool ok = true;
+    for (int c = 0; c < nch && ok; ++c) {
+      const int pos0 = c * CH, buf = c & 1;
+      const uint32_t k = (uint32_t)(c >> 1);
+      if (k > 0 && !WAIT(B_Q_FREE + buf, k - 1)) { FAIL(240); break; }
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&bars[B_Q_READY + buf], REGION);
+        tma_load_4d(rawq + buf * REGION, &tmq, &bars[B_Q_READY + buf], 0, pos0 - P.off, h_idx, b_idx);
+      }
+      if (k > 0 && !WAIT(B_KT_FREE + buf, k - 1)) { FAIL(241); break; }
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&bars[B_KT_READY + buf], KT_BUF);
+        tma_load_3d(kt + buf * KT_BUF, &tmkt, &bars[B_KT_READY + buf], pos0, 0, head);
+        tma_load_3d(kt + buf * KT_BUF + KT_BOX, &tmkt, &bars[B_KT_READY + buf], pos0 + 64, 0, head);
+      }
+      if (k > 0 && !WAIT(B_VP_FREE + buf, k - 1)) { FAIL(242); break; }
+      uint8_t* vbuf = vp + buf * VPBUF;
+      for (int r = lane; r < CH; r += 32)  // the ones column of [V | 1] (zero for rows past the last key)
+        *reinterpret_cast<uint4*>(vbuf + 8 * BLK + r * 16) = make_uint4((pos0 + r < P.nk) ? 0x00003F80u : 0u, 0u, 0u, 0u);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&bars[B_VP_READY + buf], 8 * BLK);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tma_load_4d(vbuf + i * BLK, &tmv, &bars[B_VP_READY + buf], 8 * i, pos0, h_idx, b_idx);
+      }
+      __syncwarp();
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (w == 0) tmem_dealloc(tmem_base, 512);
+#ifdef FM_TC_TIMELINE
+  if (tl_ptr) {
+    const int role = (int)((tl_ptr - reinterpret_cast<uint2*>(sm + OFF_TL)) / 256);
+    for (int i = 0; i < tl_n; ++i) g_tc_timeline[role * 1024 + i] = ((long long)tl_ptr[i].x << 32) | tl_ptr[i].y;
+    g_tc_timeline_cnt[role] = tl_n;
+  }
+#endif
+}
+
+// x (batch, head, token, 64) bf16, any strides -> xt [batch*head][64][ntp] (ntp = tokens rounded up to 64, zero filled).
+// One block per (64-token group, batch*head).
+__global__ void __launch_bounds__(256) transpose_tokens_kernel(View x, __nv_bfloat16* __restrict__ xt, int n, int ntp, int heads) {
+  __shared__ __nv_bfloat16 tile[64][72];
+  const int head = blockIdx.y, t0 = blockIdx.x * 64;
+  const int b = head / heads, h = head - b * heads;
+  const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(x.ptr) + (long long)b * x.sb + (long long)h * x.sh;
+  for (int idx = threadIdx.x; idx < 512; idx += 256) {
+    const int r = idx >> 3, cv = idx & 7;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (t0 + r < n) v = *reinterpret_cast<const uint4*>(src + (long long)(t0 + r) * x.sn + cv * 8);
+    *reinterpret_cast<uint4*>(&tile[r][cv * 8]) = v;
+  }
+  __syncthreads();
+  __nv_bfloat16* dst = xt + ((long long)head * 64) * ntp + t0;
+  for (int idx = threadIdx.x; idx < 512; idx += 256) {
+    const int d = idx >> 3, tc8 = idx & 7;
+    __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = tile[tc8 * 8 + e][d];
+    *reinterpret_cast<uint4*>(dst + (long long)d * ntp + tc8 * 8) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
+}  // namespace s2
