@@ -106,13 +106,13 @@ __global__ void finalize_fwd_vec_kernel(const float* __restrict__ acc, int ld, i
 }
 
 template <typename T>
-__global__ void cast_out_vec_kernel(const float* __restrict__ acc, int d, int n, int heads, View out) {
+__global__ void cast_out_vec_kernel(const float* __restrict__ acc, int d, int n, int heads, View out, int acc_ld) {
   const int head = blockIdx.y;
   const int d4 = d >> 2;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n * d4) return;
   const int l = t / d4, c = (t - l * d4) << 2;
-  const float4 v = *reinterpret_cast<const float4*>(acc + ((long long)head * n + l) * d + c);
+  const float4 v = *reinterpret_cast<const float4*>(acc + ((long long)head * n + l) * acc_ld + c);
   const int b = head / heads, h = head - b * heads;
   T* op = reinterpret_cast<T*>(const_cast<void*>(out.ptr)) + (long long)b * out.sb + (long long)h * out.sh + (long long)l * out.sn;
   store4<T>(op + c, v.x, v.y, v.z, v.w);
@@ -145,9 +145,9 @@ __global__ void bwd_prologue_kernel(View dout, View o, View g, float* __restrict
   if (lane >= 1 && lane < ld - d) out[d + lane] = 0.f;
 }
 
-// fp32 accumulator [BH][n][d] -> strided output of dtype T
+// fp32 accumulator [BH][n][acc_ld] (first d columns) -> strided output of dtype T
 template <typename T>
-__global__ void cast_out_kernel(const float* __restrict__ acc, int d, int n, int heads, View out, long long total) {
+__global__ void cast_out_kernel(const float* __restrict__ acc, int d, int n, int heads, View out, long long total, int acc_ld) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   int c = (int)(idx % d);
@@ -156,7 +156,7 @@ __global__ void cast_out_kernel(const float* __restrict__ acc, int d, int n, int
   int head = (int)(row / n);
   int b = head / heads, h = head - b * heads;
   T* op = reinterpret_cast<T*>(const_cast<void*>(out.ptr)) + (long long)b * out.sb + (long long)h * out.sh + (long long)l * out.sn;
-  op[c] = from_float<T>(acc[idx]);
+  op[c] = from_float<T>(acc[row * acc_ld + c]);
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -49,7 +49,7 @@ void launch_end(int kind, cudaStream_t st) {
 }
 static const char* kKindNames[KK_COUNT] = {
     "moments_kv", "moments_qg", "state_scan", "scan_fwd", "scan_bwd_q", "scan_bwd_kv", "finalize_fwd",
-    "bwd_prologue", "cast_out", "normalize", "tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_moments", "p1_fwd", "tc_intra_fwd", "tc_intra_bwd", "tc_transpose"};
+    "bwd_prologue", "cast_out", "normalize", "tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_moments", "p1_fwd", "tc_intra_fwd", "tc_intra_bwd", "tc_transpose", "tc_scan_bwd_dv"};
 
 static int sm_count() {
   static int cached[64] = {0};
@@ -221,7 +221,8 @@ static bool vec4_ok(const fastmax_tensor& t, int dtype) {
          ((size_t)t.stride_n * es) % al == 0;
 }
 
-int launch_cast_out(const fastmax_problem* pb, const float* acc, int n, const fastmax_tensor* out, cudaStream_t st) {
+int launch_cast_out(const fastmax_problem* pb, const float* acc, int n, const fastmax_tensor* out, cudaStream_t st, int acc_ld) {
+  if (acc_ld <= 0) acc_ld = pb->d;
   const long long total = (long long)pb->batch * pb->heads * n * pb->d;
   if (total == 0) return FASTMAX_OK;
   const int threads = 256;
@@ -230,9 +231,9 @@ int launch_cast_out(const fastmax_problem* pb, const float* acc, int n, const fa
     {
       LaunchScope ls(KK_CAST, st);
       if (pb->dtype == FASTMAX_F32)
-        cast_out_vec_kernel<float><<<grid, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out));
+        cast_out_vec_kernel<float><<<grid, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out), acc_ld);
       else
-        cast_out_vec_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out));
+        cast_out_vec_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out), acc_ld);
     }
     FM_CUDA(cudaGetLastError());
     return FASTMAX_OK;
@@ -241,9 +242,9 @@ int launch_cast_out(const fastmax_problem* pb, const float* acc, int n, const fa
   {
     LaunchScope ls(KK_CAST, st);
     if (pb->dtype == FASTMAX_F32)
-      cast_out_kernel<float><<<blocks, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out), total);
+      cast_out_kernel<float><<<blocks, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out), total, acc_ld);
     else
-      cast_out_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out), total);
+      cast_out_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out), total, acc_ld);
   }
   FM_CUDA(cudaGetLastError());
   return FASTMAX_OK;

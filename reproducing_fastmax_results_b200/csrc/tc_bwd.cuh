@@ -15,6 +15,8 @@
 // All waits are bounded (abort flag + error code, as in the forward scan).
 #pragma once
 
+constexpr int ACC_LD = 68;   // floats per row of the dq / dk / dv accumulators: 272-byte rows keep 128-bit per-thread row
+                             // accesses to the shared-memory staging copies free of bank conflicts
 constexpr int BW_THREADS = 448;
 constexpr int BW_NPRODUCER = 128;
 constexpr int BW_WARP_MMA = 12, BW_WARP_TMA = 13;
@@ -77,6 +79,7 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
   const int tile0 = slice * 4;
   const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
   const int nch = P.nchunks;
+  const bool do_dv = KV && P.dv_acc != nullptr;  // the dV apply can run in its own kernel instead
 
   if (tid == 0) {
     for (int i = 0; i < BW_NSLOT; ++i) { mbar_init(&bars[C_FULL + i], BW_NPRODUCER); mbar_init(&bars[C_EMPTY + i], 1); }
@@ -124,7 +127,7 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
       for (int t = 0; t < ntl && ok; ++t) {
         const int gt = tile0 + t;
 #pragma unroll 1
-        for (int which = ((KV && i > 0) ? 0 : 1); which < 2; ++which) {  // 0: Phi(Z) for the dV apply, 1: Phi(X) for the update
+        for (int which = ((do_dv && i > 0) ? 0 : 1); which < 2; ++which) {  // 0: Phi(Z) for the dV apply, 1: Phi(X) for the update
           const uint32_t slot = n % BW_NSLOT, k = n / BW_NSLOT;
           if (k > 0 && !WAIT(C_EMPTY + slot, k - 1)) { FAIL(111); ok = false; break; }
           gen_tile(ring + slot * TILE, which == 0 ? ztile : xtile, gt, l, 0);
@@ -208,7 +211,7 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
         const long long row = KV ? ((long long)c * CH + l) : ((long long)c * CH + l - P.off);
         const long long nrows = KV ? P.nk : P.nq;
         if (row >= 0 && row < nrows) {
-          float* dst = P.dz_acc + ((long long)head * nrows + row) * 64;
+          float* dst = P.dz_acc + ((long long)head * nrows + row) * ACC_LD;
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             atomicAdd(reinterpret_cast<float4*>(dst + 4 * j), make_float4(dz[4 * j], dz[4 * j + 1], dz[4 * j + 2], dz[4 * j + 3]));
@@ -225,7 +228,7 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
     for (int i = 0; i < nch && ok; ++i) {
       const int c = KV ? (nch - 1 - i) : i;
       for (int t = 0; t < ntl && ok; ++t) {
-        if (KV && i > 0 && t == ntl - 1) {
+        if (do_dv && i > 0 && t == ntl - 1) {
           if (!WAIT(C_DV_DONE, (uint32_t)(i - 1))) { FAIL(130); ok = false; break; }
           tc_fence_after_sync();
           uint32_t r0[32], r1[32];
@@ -236,7 +239,7 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
           mbar_arrive(&bars[C_DV_FREE]);
           const long long row = (long long)c * CH + l;
           if (row < P.nk) {
-            float* dst = P.dv_acc + ((long long)head * P.nk + row) * 64;
+            float* dst = P.dv_acc + ((long long)head * P.nk + row) * ACC_LD;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               atomicAdd(reinterpret_cast<float4*>(dst + 4 * j),
@@ -307,7 +310,7 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             ++m;
           }
           if (!ok) break;
-          if (KV) {  // dV += Phi(K_c) Sb[:, :64]
+          if (do_dv) {  // dV += Phi(K_c) Sb[:, :64]
             const uint32_t slot = n % BW_NSLOT, k = n / BW_NSLOT;
             if (!WAIT(C_FULL + slot, k)) { FAIL(143); ok = false; break; }
             if (t == 0 && i >= 2 && !WAIT(C_DV_FREE, (uint32_t)(i - 2))) { FAIL(144); ok = false; break; }
@@ -519,8 +522,8 @@ intra_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant_
     tc_fence_after_sync();
     const long long ql = (long long)pos0 + l - P.off;
     const long long kpos = (long long)pos0 + l;
-    float* dsts[3] = {P.dq_acc + ((long long)head * P.nq + ql) * 64 + 32 * h, P.dk_acc + ((long long)head * P.nk + kpos) * 64 + 32 * h,
-                      P.dv_acc + ((long long)head * P.nk + kpos) * 64 + 32 * h};
+    float* dsts[3] = {P.dq_acc + ((long long)head * P.nq + ql) * ACC_LD + 32 * h, P.dk_acc + ((long long)head * P.nk + kpos) * ACC_LD + 32 * h,
+                      P.dv_acc + ((long long)head * P.nk + kpos) * ACC_LD + 32 * h};
     const bool valid[3] = {ql >= 0 && ql < P.nq, kpos < P.nk, kpos < P.nk};
     const uint32_t cols[3] = {COL_DQ, COL_DK, COL_DVV};
 #pragma unroll

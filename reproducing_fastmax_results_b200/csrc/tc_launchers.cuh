@@ -19,6 +19,7 @@ int tc_wait_histogram(int* out, int n);
 
 // shared with the C-ABI translation unit
 int report_cuda_error(cudaError_t e);  // remembers e for fastmax_last_cuda_error(), returns FASTMAX_ERR_CUDA
-int launch_cast_out(const fastmax_problem* pb, const float* acc, int n, const fastmax_tensor* out, cudaStream_t st);
+// acc: [batch*heads][n][acc_ld] float32 (acc_ld <= 0: dense, acc_ld = d)
+int launch_cast_out(const fastmax_problem* pb, const float* acc, int n, const fastmax_tensor* out, cudaStream_t st, int acc_ld = 0);
 int launch_finalize_fwd(const fastmax_problem* pb, const fastmax_forward_args* a, const float* oacc, cudaStream_t st);
 }  // namespace fm

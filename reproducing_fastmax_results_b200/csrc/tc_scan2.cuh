@@ -1,26 +1,37 @@
-// Forward causal scan with the Phi operands in tensor memory.  Included by tc_kernels.cu inside fm::tc.
+// Causal "apply + update" scans with the Phi operands in tensor memory.  Included by tc_kernels.cu inside fm::tc.
 //
-// Why: an SS tcgen05.mma with N = 80 reads 4 KB of A and 2.5 KB of B from shared memory per K = 16 step (52 clocks
-// of the 128 B/clock shared-memory pipe against 40 clocks of math), and a Phi tile that goes through shared
-// memory costs another write and the read again.  Here the Phi tiles never touch shared memory: CUDA cores
-// compute them in registers and store them with tcgen05.st into TMEM, where tcgen05.mma reads its A operand
-// (45 clocks per K = 16 step measured), so shared memory only carries the B operands ([V|1], the bf16 state
-// copy) and the raw q / k tiles.
+// One kernel template serves two scans that have the same shape:
+//   forward (DV = false), chunks ascending:    O'_c  = Phi(Q_c) Sb_{<c}           S  += Phi(K_c)^T [V_c | 1]
+//   dv scan (DV = true),  chunks descending:   dV_c  = Phi(K_c) dSb_{>c}[:, :64]  dS += Phi(Q_c)^T dO'_c
+// In both, "Z" is the raw [token][64] tile whose Phi multiplies the state copy (Q | K), "X" the tile whose Phi^T
+// builds the state (K | Q, read from a transposed copy [64][tokens]) and "Y" the 80-column right-hand side of the
+// update ([V|1] | dO').  The intra-chunk (masked) terms are added by separate kernels.
 //
-// Per 128-token chunk c and 128-row feature tile t of the CTA's slice (4 tiles, the last slice 3):
-//     apply   O'_c (128 tok x 80) += Phi_t(Q_c) (128 tok x 128 feat, TMEM)    * Sb_t (128 feat x 80, smem)
-//     update  S_t  (128 feat x 80) += Phi_t(K_c)^T (128 feat x 128 tok, TMEM) * [V_c | 1] (128 tok x 80, smem)
-// A operands go through one ring of three 32-column TMEM buffers (128 lanes x 64 bf16 = a 64-deep K slab, four
-// MMAs).  A query slab holds 64 features of Phi(Q) (thread = token, from the raw q tile); a key slab holds 64
-// tokens of Phi(K)^T (thread = feature, from a transposed copy of k, [64][tokens], built by a small pre-pass
-// kernel and streamed with TMA into rows of 144 bytes); both cost two 128-bit shared loads per eight products.  Slab order per (c, t):
-// Q0 K0 Q1 K1 (Q0 Q1 K0 K1 in the last tile, so the O' drain overlaps the updates; K0 K1 only in chunk 0, where
-// there is no earlier state to apply).  Three producer sets of four warps each own one ring slot (set s makes the
-// slabs s, s+3, s+6, ... of the CTA's slab sequence), so every barrier has one producer and one consumer and no
-// waiter is ever more than one phase away from the barrier it polls.
-// TMEM columns: 0..319 four state accumulators, 320..399 O', 400..495 the ring.
-// Warp roles (608 threads): 0-3, 4-7, 8-11 producer sets, 12-15 consumers (state -> bf16 copy, O' drain), 16 apply
-// issuer, 17 update issuer, 18 TMA loader.  Every wait is bounded (abort flag + error code), as in the other kernels.
+// Why tensor memory: an SS tcgen05.mma with N = 80 reads 4 KB of A and 2.5 KB of B from shared memory per K = 16
+// step (52 clocks of the 128 B/clock shared-memory pipe against 40 clocks of math), and a Phi tile that goes
+// through shared memory costs another write and the read again.  Here the Phi tiles never touch shared memory:
+// CUDA cores compute them in registers and store them with tcgen05.st into TMEM, where tcgen05.mma reads its A
+// operand (45 clocks per K = 16 step measured); shared memory only carries the B operands and the raw tiles.
+//
+// Per 128-token chunk and 128-row feature tile t of the CTA's slice (4 tiles, the last slice 3):
+//     apply   OUT (128 tok x N)    += Phi_t(Z_c) (128 tok x 128 feat, TMEM)     * Sb_t (128 feat x N, smem)
+//     update  S_t (128 feat x 80)  += Phi_t(X_c)^T (128 feat x 128 tok, TMEM)   * Y_c (128 tok x 80, smem)
+// A operands go through a ring of three 32-column TMEM buffers (128 lanes x 64 bf16 = a 64-deep K slab, four MMAs).
+// An apply slab holds 64 features of Phi(Z) (thread = token, from the raw tile); an update slab holds 64 tokens of
+// Phi(X)^T (thread = feature, from the transposed tile, rows of 144 bytes); both cost two 128-bit shared loads
+// per eight products.  Slab order per (chunk, tile): A0 U0 A1 U1 (A0 A1 U0 U1 in the last tile, so the output drain
+// overlaps the updates; U0 U1 only in the first chunk, which has no earlier state).  Three producer sets of four
+// warps each own one ring slot (set s makes the slabs s, s+3, ... of the slab sequence); two issuer warps issue the
+// apply and the update MMAs (independent accumulator chains) and wait on per-kind `full` barriers; every barrier
+// has one producer and one consumer, so no waiter is ever more than one phase away from the barrier it polls.
+// Polynomial weights: an off-diagonal pair unit stands for (a,b) and (b,a), factor 2, which the apply slab carries
+// exactly (x_a is doubled); slices of pair tiles only then scale their output by c2 once, in float32, when it is
+// drained.  The slice that holds the linear/constant tile puts the weights into the bf16 state copy instead.
+// The output partial of the slice is staged in shared memory and added to the float32 accumulator in global
+// memory with ONE bulk reduce (cp.reduce.async.bulk) per chunk.
+// TMEM columns: 0..319 four state accumulators, 320..399 output accumulator, 400..495 the ring.
+// Warp roles (608 threads): 0-3, 4-7, 8-11 producer sets, 12-15 consumers (state -> bf16 copy, output drain),
+// 16 apply issuer, 17 update issuer, 18 TMA loader.  Every wait is bounded (abort flag + error code).
 #pragma once
 
 namespace s2 {
@@ -32,43 +43,55 @@ constexpr int NRING = NSETS;
 constexpr int KT_ROW = 144;                            // row pitch of the transposed tile: 64 tokens + 8 (bank spread)
 constexpr int KT_BOX = 64 * KT_ROW;                    // 9216: one 64-token box, [64 dims][72 tokens]
 constexpr int KT_BUF = 2 * KT_BOX;                     // 18432
-constexpr int VPBUF = 10 * BLK;                       // [V|1] buffer: 9 column blocks + one zero block
-constexpr int OFF_SB = 0;                             // 4 x SB_TILE
-constexpr int OFF_VP = OFF_SB + 4 * SB_TILE;          // 73728, 2 buffers
-constexpr int OFF_RAWQ = OFF_VP + 2 * VPBUF;          // 114688, 2 x REGION, 128-byte swizzle
-constexpr int OFF_KT = OFF_RAWQ + 2 * REGION;         // 147456, 2 x KT_BUF (two 64-token boxes each, not swizzled)
-constexpr int OFF_BAR = OFF_KT + 2 * KT_BUF;          // 184320
-constexpr int OFF_OST = OFF_BAR + 512;                // O' staging for the bulk reduce: 128 rows x 68 floats
-constexpr int OST_BYTES = CH * 68 * 4;                // 34816
-constexpr int OFF_TL = OFF_OST + OST_BYTES;           // development build only: 4 roles x 256 time stamps
+constexpr int VPBUF = 10 * BLK;                        // Y buffer: 9 column blocks + one zero block
+constexpr int OFF_SB = 0;                              // 4 x SB_TILE
+constexpr int OFF_VP = OFF_SB + 4 * SB_TILE;           // 73728, 2 buffers
+constexpr int OFF_RAWQ = OFF_VP + 2 * VPBUF;           // 114688, 2 x REGION, 128-byte swizzle
+constexpr int OFF_KT = OFF_RAWQ + 2 * REGION;          // 147456, 2 x KT_BUF (two 64-token boxes each, not swizzled)
+constexpr int OFF_BAR = OFF_KT + 2 * KT_BUF;           // 184320
+constexpr int OFF_OST = OFF_BAR + 512;                 // output staging for the bulk reduce: 128 rows x <= 68 floats
+constexpr int OST_BYTES = CH * 68 * 4;                 // 34816
+constexpr int OFF_TL = OFF_OST + OST_BYTES;            // development build only: 4 roles x 256 time stamps
 #ifdef FM_TC_TIMELINE
 constexpr int SMEM_BYTES = OFF_TL + 4 * 2048 + 1024;
 #else
 constexpr int SMEM_BYTES = OFF_TL + 1024;
 #endif
-static_assert(OFF_RAWQ % 1024 == 0 && OFF_KT % 128 == 0, "swizzled tiles need 1024-byte alignment");
+static_assert(OFF_RAWQ % 1024 == 0 && OFF_KT % 128 == 0 && OFF_OST % 128 == 0, "tile alignment");
 constexpr uint32_t COL_O = 320u, COL_A = 400u;
 // barriers
 constexpr int B_FULL_Q = 0, B_FULL_K = 3, B_EMPTY = 6, B_Q_READY = 9, B_Q_FREE = 11, B_KT_READY = 13, B_KT_FREE = 15,
               B_VP_READY = 17, B_VP_FREE = 19, B_SB_READY = 21, B_S_DONE = 25, B_A_DONE = 29, B_O_DONE = 33, B_O_FREE = 34,
               B_OST_FREE = 35, B_OST_FULL = 36, B_COUNT = 37;
 
+struct ApplyParams {
+  float* out;          // forward: O' accumulator [BH][nz][68]; dv scan: dV accumulator [BH][nz][ACC_LD = 68]
+  int heads;
+  int nz;              // rows of Z and of the output (forward: nq; dv scan: nk)
+  int ny;              // forward: number of keys (rows of the ones column that are 1)
+  int z_shift;         // Z row of chunk position p is p - z_shift (forward: nk - nq; dv scan: 0)
+  int y_shift;         // Y row of chunk position p is p - y_shift (forward: 0; dv scan: nk - nq)
+  int nchunks;
+  float c0, c1, c2;
+};
+
+// A bounded wait gave up: count the wait site (first failure of the CTA only), raise the CTA's abort flag, set the
+// device status word.
+__device__ __noinline__ void fail_record(int code, volatile int* abort_flag) {
+  if (*abort_flag == 0) atomicAdd(&g_tc_wait_hist[code & 255], 1);
+  *abort_flag = 1;
+  atomicExch(&g_tc_status, code);
+}
 __device__ __noinline__ bool wait_slow(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
   return mbar_wait_abortable(bar, parity, WAIT_CYCLES, abort_flag);
 }
 // Waits for the phase of parity `parity`; the common case (already complete) is one try_wait.
 __device__ __forceinline__ bool wait_fast(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
-#ifdef FM_SPIN_TEST_WAIT
-#pragma unroll 1
-  for (int i = 0; i < FM_SPIN_TEST_WAIT; ++i)
-    if (mbar_test_wait(bar, parity)) return true;
-#else
   if (mbar_try_wait(bar, parity)) return true;
-#endif
   return wait_slow(bar, parity, abort_flag);
 }
 
-// Slab j of tile (c, t): is it a query slab, and which half (64 features / 64 tokens) does it hold?
+// Slab j of tile (chunk, t): is it an apply slab, and which half (64 features / 64 tokens) does it hold?
 __device__ __forceinline__ void slab_kind(bool first_chunk, bool last_tile, int j, bool& is_q, int& half) {
   if (first_chunk) { is_q = false; half = j; }
   else if (last_tile) { is_q = (j < 2); half = j & 1; }
@@ -80,11 +103,15 @@ __device__ __forceinline__ uint4 sw_chunk(const uint8_t* tile, int row, int cc) 
   return *reinterpret_cast<const uint4*>(tile + row * 128 + ((cc ^ (row & 7)) << 4));
 }
 
-// Query slab: 64 features x[8a+mi] * x[8b+ri] of token row l of the raw [token][64] tile -> 32 packed registers
-// (register 4 mi + j holds ri = 2j, 2j + 1).
-__device__ __forceinline__ void query_pair_slab(uint32_t (&r)[32], const uint8_t* raw, int l, int a, int b) {
-  const uint4 xa4 = sw_chunk(raw, l, a);
+// Apply slab: 64 features x[8a+mi] * x[8b+ri] of token row l of the raw [token][64] tile -> 32 packed registers
+// (register 4 mi + j holds ri = 2j, 2j + 1).  `dbl`: x[8a+mi] is doubled (exact) for an off-diagonal unit.
+__device__ __forceinline__ void apply_pair_slab(uint32_t (&r)[32], const uint8_t* raw, int l, int a, int b, bool dbl) {
+  uint4 xa4 = sw_chunk(raw, l, a);
   const uint4 xb4 = sw_chunk(raw, l, b);
+  if (dbl) {
+    const uint32_t two = 0x40004000u;  // bf16x2 (2, 2)
+    xa4.x = hmul2_u32(xa4.x, two); xa4.y = hmul2_u32(xa4.y, two); xa4.z = hmul2_u32(xa4.z, two); xa4.w = hmul2_u32(xa4.w, two);
+  }
   const uint32_t xa[4] = {xa4.x, xa4.y, xa4.z, xa4.w};
 #pragma unroll
   for (int mi = 0; mi < 8; ++mi) {
@@ -96,10 +123,10 @@ __device__ __forceinline__ void query_pair_slab(uint32_t (&r)[32], const uint8_t
     r[4 * mi + 3] = hmul2_u32(bc, xb4.w);
   }
 }
-// Key slab: products x[i][tok] * x[j][tok] for the 64 tokens of one box of the transposed tile ([64 dims] rows of
+// Update slab: products x[i][tok] * x[j][tok] for the 64 tokens of one box of the transposed tile ([64 dims] rows of
 // KT_ROW bytes, not swizzled: the pitch spreads consecutive rows over the banks) -> 32 packed registers
 // (register 4 cc + jj holds tokens 8cc + 2jj, +1).
-__device__ __forceinline__ void key_pair_slab(uint32_t (&r)[32], const uint8_t* box, int i, int j) {
+__device__ __forceinline__ void update_pair_slab(uint32_t (&r)[32], const uint8_t* box, int i, int j) {
   const uint4* ri = reinterpret_cast<const uint4*>(box + i * KT_ROW);
   const uint4* rj = reinterpret_cast<const uint4*>(box + j * KT_ROW);
 #pragma unroll
@@ -132,27 +159,32 @@ __device__ __forceinline__ void fill_slab(uint32_t (&r)[32], uint32_t v) {
   for (int c = 0; c < 32; ++c) r[c] = v;
 }
 
-// One slab of tile gt for TMEM lane `row`: query slabs take row = token, key slabs row = feature of the tile.
-// (a0, b0), (a1, b1): block pairs of the tile's two 64-feature units.  xt: transposed tile (two 64-token boxes).
-__device__ __forceinline__ void make_slab(uint32_t (&r)[32], bool is_q, int half, bool lin, int row, const uint8_t* raw,
-                                          const uint8_t* xt, int a0, int b0, int a1, int b1) {
+// One slab of a tile for TMEM lane `row`: apply slabs take row = token, update slabs row = feature of the tile.
+// pr: block pairs (a0, b0, a1, b1), 4 bits each, of the tile's two 64-feature units.  xt: transposed tile.
+__device__ __forceinline__ void make_slab(uint32_t (&r)[32], bool is_q, int half, bool lin, bool dbl_off, int row,
+                                          const uint8_t* raw, const uint8_t* xt, uint32_t pr) {
   if (is_q) {
-    if (!lin) query_pair_slab(r, raw, row, half ? a1 : a0, half ? b1 : b0);
-    else if (half == 0) copy_row_slab(r, raw, row);           // features 0..63 = x
+    if (!lin) {
+      const int a = (half ? (pr >> 8) : pr) & 15, b = (half ? (pr >> 12) : (pr >> 4)) & 15;
+      apply_pair_slab(r, raw, row, a, b, dbl_off && a != b);
+    } else if (half == 0) copy_row_slab(r, raw, row);         // features 0..63 = x
     else { fill_slab(r, 0u); r[0] = 0x00003F80u; }            // feature 64 = 1, the rest 0
   } else {
     const uint8_t* box = xt + half * KT_BOX;
     if (!lin) {
-      const int hi = row >> 6;
-      key_pair_slab(r, box, 8 * (hi ? a1 : a0) + ((row >> 3) & 7), 8 * (hi ? b1 : b0) + (row & 7));
+      const uint32_t q = (row >> 6) ? (pr >> 8) : pr;
+      update_pair_slab(r, box, 8 * (int)(q & 15) + ((row >> 3) & 7), 8 * (int)((q >> 4) & 15) + (row & 7));
     } else if (row < 64) copy_trow_slab(r, box, row);
     else fill_slab(r, row == 64 ? 0x3F803F80u : 0u);
   }
 }
 
+template <bool DV>
 __global__ void __launch_bounds__(THREADS, 1)
-scan_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmkt,
-                const __grid_constant__ CUtensorMap tmv, const FwdParams P) {
+scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant__ CUtensorMap tmxt,
+                  const __grid_constant__ CUtensorMap tmy, const ApplyParams P) {
+  constexpr int OUT_LD = 68;                  // floats per output row (forward: O' | g | pad; dv scan: ACC_LD)
+  constexpr int N_APPLY = DV ? 64 : 80;       // columns of the apply MMA
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* sm = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -171,6 +203,8 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
   const int tile0 = slice * 4;
   const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
   const int nch = P.nchunks;
+  const bool lin_slice = (tile0 + ntl == NTILES);   // this slice holds the linear/constant tile: weights go into Sb
+  auto chunk_of = [&](int i) -> int { return DV ? (nch - 1 - i) : i; };  // i-th chunk of the scan
 #ifdef FM_TC_TIMELINE
   // development aid: cheap (shared-memory) time stamps of one thread per role of CTA (0, 0), chunks 8..11
   uint2* tl_ptr = nullptr;
@@ -210,80 +244,60 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
 
   auto WAIT = [&](int bar, uint32_t n) -> bool {  // waits for completion number n (0-based) of the barrier
-#if defined(FM_DBG_FREERUN) || defined(FM_DBG_FREERUN_WAITFULL)
-    if (bar >= B_Q_READY) return true;   // development aid: only the ring barriers are honoured
-#endif
     return wait_fast(&bars[bar], n & 1u, abort_flag);
   };
-  auto FAIL = [&](int code) {
-    if (*abort_flag == 0) atomicAdd(&g_tc_wait_hist[code & 255], 1);
-    *abort_flag = 1;
-    atomicExch(&g_tc_status, code);
-  };
+  auto FAIL = [&](int code) { fail_record(code, abort_flag); };  // out of line: keeps the hot loops compact
 
-#if defined(FM_DBG_FREERUN) || defined(FM_DBG_FREERUN_WAITFULL)
-  if (w >= W_CONS && w != W_MMA && w != W_MMA2) { /* consumers and loader idle */ } else
-#endif
-#ifdef FM_DBG_FREERUN
-  if (w < W_CONS) { /* producers idle */ } else
-#endif
   if (w < W_CONS) {
     // ================= producers: Phi slabs into the TMEM ring =================
     // Set s fills ring slot s, i.e. every slab whose index in the CTA's slab sequence is s (mod 3).
     const int set = w >> 2;
-    const int row = (w & 3) * 32 + lane;  // TMEM lane: token (query slab) or feature of the tile (key slab)
+    const int row = (w & 3) * 32 + lane;  // TMEM lane: token (apply slab) or feature of the tile (update slab)
     const uint32_t slot_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16) + COL_A + 32u * set;
-    uint32_t pairs[4];                    // block pairs (a0, b0, a1, b1) of the two 64-feature units of each tile
+    uint64_t pairs = 0;                   // 16 bits per tile: block pairs (a0, b0, a1, b1) of its two 64-feature units
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       int a0 = 0, b0 = 0, a1 = 0, b1 = 0;
       if (tile0 + t < NTILES - 1) { pair_decode(2 * (tile0 + t), 8, a0, b0); pair_decode(2 * (tile0 + t) + 1, 8, a1, b1); }
-      pairs[t] = (uint32_t)(a0 | (b0 << 4) | (a1 << 8) | (b1 << 12));
+      pairs |= (uint64_t)(a0 | (b0 << 4) | (a1 << 8) | (b1 << 12)) << (16 * t);
     }
     int rem = 0;       // (index of the current tile's first slab) mod 3
     uint32_t k = 0;    // slabs this set has produced = phase count of its slot
     bool ok = true;
-    for (int c = 0; c < nch && ok; ++c) {
-      S2_CHUNK(c);
-      const int buf = c & 1;
-      if (!WAIT(B_KT_READY + buf, (uint32_t)(c >> 1)) || !WAIT(B_Q_READY + buf, (uint32_t)(c >> 1))) { FAIL(200); break; }
+    for (int ci = 0; ci < nch && ok; ++ci) {
+      S2_CHUNK(ci);
+      const int buf = ci & 1;
+      if (!WAIT(B_KT_READY + buf, (uint32_t)(ci >> 1)) || !WAIT(B_Q_READY + buf, (uint32_t)(ci >> 1))) { FAIL(200); break; }
       const uint8_t* raw = rawq + buf * REGION;
       const uint8_t* xt = kt + buf * KT_BUF;
-      const int nb = c == 0 ? 2 : 4;
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        if (t < ntl && ok) {
-          const bool lin = (tile0 + t == NTILES - 1);
-          const int a0 = pairs[t] & 15, b0 = (pairs[t] >> 4) & 15, a1 = (pairs[t] >> 8) & 15, b1 = (pairs[t] >> 12) & 15;
-          int j = set - rem;
-          if (j < 0) j += NSETS;
+      const int nb = ci == 0 ? 2 : 4;
+      for (int t = 0; t < ntl && ok; ++t) {
+        const bool lin = (tile0 + t == NTILES - 1);
+        const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
+        int j = set - rem;
+        if (j < 0) j += NSETS;
 #pragma unroll 1
-          for (; j < nb; j += NSETS, ++k) {
-            bool is_q; int half;
-            slab_kind(c == 0, t == ntl - 1, j, is_q, half);
-            S2_STAMP(40);
-            uint32_t r[32];
-#ifdef FM_DBG_NOPROD
-            fill_slab(r, 0x3C003C00u + (uint32_t)half + (is_q ? 1u : 0u) + (lin ? 2u : 0u) + (uint32_t)(a0 + b0 + a1 + b1));
-#else
-            make_slab(r, is_q, half, lin, row, raw, xt, a0, b0, a1, b1);
-#endif
-            S2_STAMP(41);
-            if (k > 0 && !WAIT(B_EMPTY + set, k - 1)) { FAIL(201); ok = false; break; }
-            __syncwarp();
-            S2_STAMP(42);
-            tc_fence_after_sync();
-            tmem_st32(slot_addr, r);
-            tmem_st_wait();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars[(is_q ? B_FULL_Q : B_FULL_K) + set]);
-            S2_STAMP(43);
-          }
-          rem += nb - NSETS;            // (rem + nb) mod 3 for nb = 2 or 4
-          if (rem < 0) rem += NSETS;
-          if (rem >= NSETS) rem -= NSETS;
+        for (; j < nb; j += NSETS, ++k) {
+          bool is_q; int half;
+          slab_kind(ci == 0, t == ntl - 1, j, is_q, half);
+          S2_STAMP(40);
+          uint32_t r[32];
+          make_slab(r, is_q, half, lin, !lin_slice, row, raw, xt, pr);
+          S2_STAMP(41);
+          if (k > 0 && !WAIT(B_EMPTY + set, k - 1)) { FAIL(201); ok = false; break; }
+          __syncwarp();
+          S2_STAMP(42);
+          tc_fence_after_sync();
+          tmem_st32(slot_addr, r);
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[(is_q ? B_FULL_Q : B_FULL_K) + set]);
+          S2_STAMP(43);
         }
+        rem += nb - NSETS;            // (rem + nb) mod 3 for nb = 2 or 4
+        if (rem < 0) rem += NSETS;
+        if (rem >= NSETS) rem -= NSETS;
       }
       if (ok) {
         __syncwarp();
@@ -294,78 +308,75 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
       }
     }
   } else if (w < W_MMA) {
-    // ================= consumers: state conversion and O' drain =================
+    // ================= consumers: state conversion and output drain =================
     const int l = (w & 3) * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16);
-    float* obase = P.oacc + (long long)head * P.nq * 68;
+    float* obase = P.out + (long long)head * P.nz * OUT_LD;
+    const float out_scale = lin_slice ? 1.f : P.c2;   // pair-tile slices: the common weight c2, applied once, exactly
     bool ok = true;
-    for (int c = 0; c < nch && ok; ++c) {
-      S2_CHUNK(c);
+    for (int ci = 0; ci < nch && ok; ++ci) {
+      S2_CHUNK(ci);
+      const int c = chunk_of(ci);
       for (int t = 0; t < ntl && ok; ++t) {
-        if (t == ntl - 1 && c > 0) {  // O' of this chunk is complete once the last apply has finished
+        if (t == ntl - 1 && ci > 0) {  // the output of this chunk is complete once the last apply has finished
           S2_STAMP(60);
-          if (!WAIT(B_O_DONE, (uint32_t)(c - 1))) { FAIL(220); ok = false; break; }
+          if (!WAIT(B_O_DONE, (uint32_t)(ci - 1))) { FAIL(220); ok = false; break; }
           __syncwarp();
           S2_STAMP(61);
           tc_fence_after_sync();
           uint32_t ra[32], rb[32], rc[8];
           tmem_ld32(lane_addr + COL_O, ra);
           tmem_ld32(lane_addr + COL_O + 32u, rb);
-          tmem_ld8(lane_addr + COL_O + 64u, rc);
+          if (!DV) tmem_ld8(lane_addr + COL_O + 64u, rc);
           tmem_ld_wait();
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars[B_O_FREE]);
-          // O' partial of this slice -> staging rows in shared memory -> ONE bulk reduce-add into the fp32 accumulator
-          // (the chunk's rows are contiguous there); the copy engine does the adds, fully coalesced.
-          if (c >= 2) {  // the previous chunk's reduce has read the staging rows
+          // partial of this slice -> staging rows in shared memory -> ONE bulk reduce-add into the float32
+          // accumulator (the chunk's rows are contiguous there); the copy engine does the adds, fully coalesced.
+          if (ci >= 2) {  // the previous chunk's reduce has read the staging rows
             if (w == W_CONS && lane == 0) { bulk_wait_read_all(); mbar_arrive(&bars[B_OST_FREE]); }
-            if (!WAIT(B_OST_FREE, (uint32_t)(c - 2))) { FAIL(222); ok = false; break; }
+            if (!WAIT(B_OST_FREE, (uint32_t)(ci - 2))) { FAIL(222); ok = false; break; }
           }
-#ifndef FM_DBG_NOCONS
           {
-            float4* rowp = reinterpret_cast<float4*>(ost + l * 68);
+            float4* rowp = reinterpret_cast<float4*>(ost + l * OUT_LD);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              rowp[j] = make_float4(__uint_as_float(ra[4 * j]), __uint_as_float(ra[4 * j + 1]), __uint_as_float(ra[4 * j + 2]),
-                                    __uint_as_float(ra[4 * j + 3]));
-              rowp[8 + j] = make_float4(__uint_as_float(rb[4 * j]), __uint_as_float(rb[4 * j + 1]), __uint_as_float(rb[4 * j + 2]),
-                                        __uint_as_float(rb[4 * j + 3]));
+              rowp[j] = make_float4(__uint_as_float(ra[4 * j]) * out_scale, __uint_as_float(ra[4 * j + 1]) * out_scale,
+                                    __uint_as_float(ra[4 * j + 2]) * out_scale, __uint_as_float(ra[4 * j + 3]) * out_scale);
+              rowp[8 + j] = make_float4(__uint_as_float(rb[4 * j]) * out_scale, __uint_as_float(rb[4 * j + 1]) * out_scale,
+                                        __uint_as_float(rb[4 * j + 2]) * out_scale, __uint_as_float(rb[4 * j + 3]) * out_scale);
             }
-            rowp[16] = make_float4(__uint_as_float(rc[0]), 0.f, 0.f, 0.f);
+            rowp[16] = DV ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(__uint_as_float(rc[0]) * out_scale, 0.f, 0.f, 0.f);
           }
-#endif
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars[B_OST_FULL]);
           if (w == W_CONS) {  // the leader warp waits for all four warps' rows, one lane issues the reduce
-            if (!WAIT(B_OST_FULL, (uint32_t)(c - 1))) { FAIL(223); ok = false; break; }
+            if (!WAIT(B_OST_FULL, (uint32_t)(ci - 1))) { FAIL(223); ok = false; break; }
           }
           if (w == W_CONS && lane == 0) {
-            const long long q0 = (long long)c * CH - P.off;  // query row of staging row 0
+            const long long q0 = (long long)c * CH - P.z_shift;  // output row of staging row 0
             const int r0 = q0 < 0 ? (int)(-q0 < CH ? -q0 : CH) : 0;
-            const long long lim = (long long)P.nq - q0;
+            const long long lim = (long long)P.nz - q0;
             const int r1 = lim < CH ? (lim < 0 ? 0 : (int)lim) : CH;
             if (r1 > r0) {
-              bulk_reduce_add_f32(obase + (q0 + r0) * 68, ost + r0 * 68, (uint32_t)(r1 - r0) * 272u);
+              bulk_reduce_add_f32(obase + (q0 + r0) * OUT_LD, ost + r0 * OUT_LD, (uint32_t)(r1 - r0) * (uint32_t)(OUT_LD * 4));
               bulk_commit_group();
             }
           }
           S2_STAMP(62);
         }
-        if (c < nch - 1) {  // the bf16 copy of S_t feeds the next chunk's apply
+        if (ci < nch - 1) {  // the bf16 copy of S_t feeds the next chunk's apply
           S2_STAMP(70);
-          // S_t is final (update issuer) and Sb_t is no longer read (apply issuer; chunk 0 has no apply)
-          if (!WAIT(B_S_DONE + t, (uint32_t)c) || (c > 0 && !WAIT(B_A_DONE + t, (uint32_t)(c - 1)))) { FAIL(221); ok = false; break; }
+          // S_t is final (update issuer) and Sb_t is no longer read (apply issuer; the first chunk has no apply)
+          if (!WAIT(B_S_DONE + t, (uint32_t)ci) || (ci > 0 && !WAIT(B_A_DONE + t, (uint32_t)(ci - 1)))) { FAIL(221); ok = false; break; }
           __syncwarp();
           S2_STAMP(71);
           tc_fence_after_sync();
-          const float wgt = tile_weight(tile0 + t, l, P.c0, P.c1, P.c2);
           uint8_t* dst = sb + t * SB_TILE + l * 16;
-#ifdef FM_DBG_NOCONS
-          if (wgt == -12345.f)
-#endif
-          {
+          if (lin_slice) {  // weights inside the copy: c2 / 2 c2 per unit, c1 and c0 in the linear/constant tile
+            const float wgt = tile_weight(tile0 + t, l, P.c0, P.c1, P.c2);
 #pragma unroll
             for (int part = 0; part < 2; ++part) {
               uint32_t r[32];
@@ -378,6 +389,19 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             tmem_ld8(lane_addr + 80u * t + 64u, r8);
             tmem_ld_wait();
             store_block8(dst + 8 * BLK, r8, wgt);
+          } else {          // plain rounding: the weights are in the apply slabs (factor 2) and in the drain (c2)
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              uint32_t r[32];
+              tmem_ld32(lane_addr + 80u * t + 32u * part, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int jb = 0; jb < 4; ++jb) store_block8_plain(dst + (4 * part + jb) * BLK, &r[8 * jb]);
+            }
+            uint32_t r8[8];
+            tmem_ld8(lane_addr + 80u * t + 64u, r8);
+            tmem_ld_wait();
+            store_block8_plain(dst + 8 * BLK, r8);
           }
           fence_proxy_async_smem();
           tc_fence_before_sync();
@@ -390,106 +414,118 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
     if (w == W_CONS && lane == 0) bulk_wait_all();  // the last reduce has landed before the CTA retires
   } else if (w == W_MMA || w == W_MMA2) {
     // ================= MMA issuers =================
-    // Warp W_MMA issues the apply MMAs (query slabs -> O'), warp W_MMA2 the update MMAs (key slabs -> S_t); the two
-    // accumulator chains are independent.  Both walk the whole slab sequence to know each slab's ring slot, but
+    // Warp W_MMA issues the apply MMAs (apply slabs -> output), warp W_MMA2 the update MMAs (update slabs -> S_t); the
+    // two accumulator chains are independent.  Both walk the whole slab sequence to know each slab's ring slot, but
     // wait only for their own slabs, on per-kind `full` barriers whose phases count that kind's slabs in the slot.
-    // The whole warp runs the loop with warp-uniform values; one elected lane issues each instruction (elect.sync
+    // The whole warp runs the loop with warp-uniform values; one elected lane issues the instructions (elect.sync
     // with a full mask always picks the same lane, which tcgen05.commit relies on).
-    {
-      const bool mine_q = (w == W_MMA);
-      constexpr uint32_t IDESC = make_idesc_bf16(128, 80, 0, 1);  // A from TMEM (K-major), B MN-major
-      const uint64_t dB_V = make_smem_desc(smem_u32(vp), 128, 2048, 0);
-      const uint64_t dB_S = make_smem_desc(smem_u32(sb), 128, 2048, 0);
-      const int b_full = mine_q ? B_FULL_Q : B_FULL_K;
-      uint32_t slot = 0;     // ring slot of the next slab of the sequence
-      uint32_t phases = 0;   // bit s: parity of the next phase of this issuer's `full` barrier of slot s
-      bool ok = true;
-      for (int c = 0; c < nch && ok; ++c) {
-        S2_CHUNK(c);
-        const int nb = c == 0 ? 2 : 4;
-        const uint64_t dB_Vc = dB_V + (uint64_t)(((c & 1) * VPBUF) >> 4);
-        if (!mine_q && !WAIT(B_VP_READY + (c & 1), (uint32_t)(c >> 1))) { FAIL(233); break; }
-        if (mine_q && c >= 2 && !WAIT(B_O_FREE, (uint32_t)(c - 2))) { FAIL(231); break; }
-        for (int t = 0; t < ntl && ok; ++t) {
-          // Sb_t holds S_t of the previous chunk (apply reads it; update may overwrite S_t once it has been copied)
-          if (c > 0 && !WAIT(B_SB_READY + t, (uint32_t)(c - 1))) { FAIL(230); ok = false; break; }
-          const bool last = (t == ntl - 1);
-          const uint64_t dB_St = dB_S + (uint64_t)((t * SB_TILE) >> 4);
-          const uint32_t d_state = tmem_base + 80u * t;
-#pragma unroll 1
-          for (int j = 0; j < nb; ++j) {
-            bool is_q; int half;
-            slab_kind(c == 0, last, j, is_q, half);
-            if (is_q == mine_q) {
-              S2_STAMP(10);
-#ifndef FM_DBG_FREERUN
-              if (!wait_fast(&bars[b_full + slot], (phases >> slot) & 1u, abort_flag)) { FAIL(232); ok = false; break; }
-#endif
-              __syncwarp();
-              S2_STAMP(11);
-              phases ^= (1u << slot);
-              tc_fence_after_sync();
-              const uint32_t a0 = tmem_base + COL_A + 32u * slot;
-              const uint32_t d = is_q ? (tmem_base + COL_O) : d_state;
-              const uint64_t b0 = (is_q ? dB_St : dB_Vc) + (uint64_t)(64 * half);
-              const uint32_t first = is_q ? ((t > 0 || half > 0) ? 1u : 0u) : ((c > 0 || half > 0) ? 1u : 0u);
-              mma_ts_elect(d, a0, b0, IDESC, first);
-              mma_ts_elect(d, a0 + 8u, b0 + 16u, IDESC, 1u);
-              mma_ts_elect(d, a0 + 16u, b0 + 32u, IDESC, 1u);
-              mma_ts_elect(d, a0 + 24u, b0 + 48u, IDESC, 1u);
-              mma_commit_elect(&bars[B_EMPTY + slot]);
-              if (half == 1) {
-                if (is_q) {
-                  mma_commit_elect(&bars[B_A_DONE + t]);
-                  if (last) mma_commit_elect(&bars[B_O_DONE]);
-                } else {
-                  mma_commit_elect(&bars[B_S_DONE + t]);
-                  if (last) mma_commit_elect(&bars[B_VP_FREE + (c & 1)]);
-                }
-              }
-              S2_STAMP(12);
-            }
-            if (++slot == NRING) slot = 0;
-          }
-        }
-      }
-      // every MMA of this issuer has completed once its last commit has arrived
-      if (ok && nch > 0) {
-        if (!mine_q) {
-          if (!wait_fast(&bars[B_VP_FREE + ((nch - 1) & 1)], (uint32_t)((nch - 1) >> 1) & 1u, abort_flag)) FAIL(235);
-        } else if (nch > 1) {
-          if (!wait_fast(&bars[B_A_DONE + ntl - 1], (uint32_t)(nch - 2) & 1u, abort_flag)) FAIL(236);
-        }
-      }
+    const bool mine_q = (w == W_MMA);
+    constexpr uint32_t IDESC_A = make_idesc_bf16(128, N_APPLY, 0, 1);  // A from TMEM (K-major), B MN-major
+    constexpr uint32_t IDESC_U = make_idesc_bf16(128, 80, 0, 1);
+    const uint32_t idesc = mine_q ? IDESC_A : IDESC_U;
+    const uint64_t dB_V = make_smem_desc(smem_u32(vp), 128, 2048, 0);
+    const uint64_t dB_S = make_smem_desc(smem_u32(sb), 128, 2048, 0);
+    uint64_t* full = &bars[mine_q ? B_FULL_Q : B_FULL_K];
+    uint32_t s0 = 0;       // ring slot of the first slab of the current tile
+    uint32_t phases = 0;   // bit s: parity of the next phase of this issuer's `full` barrier of slot s
+    bool ok = true;
+    // one slab: wait for it, four MMAs (K = 64), release the ring slot (+ the tile / chunk level commits)
+    auto issue = [&](uint32_t slot, uint32_t d, uint64_t b0, uint32_t first, uint64_t* done1, uint64_t* done2) -> bool {
+      S2_STAMP(10);
+      if (!wait_fast(&full[slot], (phases >> slot) & 1u, abort_flag)) return false;
+      __syncwarp();
+      S2_STAMP(11);
+      phases ^= (1u << slot);
       tc_fence_after_sync();
+      const uint32_t a0 = tmem_base + COL_A + 32u * slot;
+      if (elect_one()) {
+        mma_ts(d, a0, b0, idesc, first);
+        mma_ts(d, a0 + 8u, b0 + 16u, idesc, 1u);
+        mma_ts(d, a0 + 16u, b0 + 32u, idesc, 1u);
+        mma_ts(d, a0 + 24u, b0 + 48u, idesc, 1u);
+        mma_commit(&bars[B_EMPTY + slot]);
+        if (done1) mma_commit(done1);
+        if (done2) mma_commit(done2);
+      }
+      __syncwarp();
+      S2_STAMP(12);
+      return true;
+    };
+    auto wrap = [](uint32_t x) -> uint32_t { return x >= NRING ? x - NRING : x; };  // x < 2 * NRING
+    for (int ci = 0; ci < nch && ok; ++ci) {
+      S2_CHUNK(ci);
+      const uint64_t dB_Vc = dB_V + (uint64_t)(((ci & 1) * VPBUF) >> 4);
+      if (!mine_q && !WAIT(B_VP_READY + (ci & 1), (uint32_t)(ci >> 1))) { FAIL(233); break; }
+      if (mine_q && ci >= 2 && !WAIT(B_O_FREE, (uint32_t)(ci - 2))) { FAIL(231); break; }
+      for (int t = 0; t < ntl && ok; ++t) {
+        const bool last = (t == ntl - 1);
+        if (ci == 0) {  // slabs of the tile: U0 U1
+          if (!mine_q) {
+            const uint32_t d = tmem_base + 80u * t;
+            ok = issue(s0, d, dB_Vc, 0u, nullptr, nullptr) &&
+                 issue(wrap(s0 + 1), d, dB_Vc + 64u, 1u, &bars[B_S_DONE + t], last ? &bars[B_VP_FREE + (ci & 1)] : nullptr);
+            if (!ok) FAIL(234);
+          }
+          s0 = wrap(s0 + 2);
+          continue;
+        }
+        // Sb_t holds S_t of the previous chunk (apply reads it; update may overwrite S_t once it has been copied)
+        if (!WAIT(B_SB_READY + t, (uint32_t)(ci - 1))) { FAIL(230); ok = false; break; }
+        // slabs of the tile: A0 U0 A1 U1, in the last tile A0 A1 U0 U1
+        if (mine_q) {
+          const uint32_t d = tmem_base + COL_O;
+          const uint64_t b = dB_S + (uint64_t)((t * SB_TILE) >> 4);
+          ok = issue(s0, d, b, t > 0 ? 1u : 0u, nullptr, nullptr) &&
+               issue(wrap(s0 + (last ? 1u : 2u)), d, b + 64u, 1u, &bars[B_A_DONE + t], last ? &bars[B_O_DONE] : nullptr);
+          if (!ok) FAIL(232);
+        } else {
+          const uint32_t d = tmem_base + 80u * t;
+          ok = issue(wrap(s0 + (last ? 2u : 1u)), d, dB_Vc, 1u, nullptr, nullptr) &&
+               issue(s0 /* s0 + 3 */, d, dB_Vc + 64u, 1u, &bars[B_S_DONE + t], last ? &bars[B_VP_FREE + (ci & 1)] : nullptr);
+          if (!ok) FAIL(234);
+        }
+        s0 = wrap(s0 + 1);  // four slabs per tile: (s0 + 4) mod 3
+      }
     }
+    // every MMA of this issuer has completed once its last commit has arrived
+    if (ok && nch > 0) {
+      if (!mine_q) {
+        if (!wait_fast(&bars[B_VP_FREE + ((nch - 1) & 1)], (uint32_t)((nch - 1) >> 1) & 1u, abort_flag)) FAIL(235);
+      } else if (nch > 1) {
+        if (!wait_fast(&bars[B_A_DONE + ntl - 1], (uint32_t)(nch - 2) & 1u, abort_flag)) FAIL(236);
+      }
+    }
+    tc_fence_after_sync();
   } else {
     // ================= TMA loader =================
     bool ok = true;
-    for (int c = 0; c < nch && ok; ++c) {
-      const int pos0 = c * CH, buf = c & 1;
-      const uint32_t k = (uint32_t)(c >> 1);
+    for (int ci = 0; ci < nch && ok; ++ci) {
+      const int pos0 = chunk_of(ci) * CH, buf = ci & 1;
+      const uint32_t k = (uint32_t)(ci >> 1);
       if (k > 0 && !WAIT(B_Q_FREE + buf, k - 1)) { FAIL(240); break; }
       if (lane == 0) {
         mbar_arrive_expect_tx(&bars[B_Q_READY + buf], REGION);
-        tma_load_4d(rawq + buf * REGION, &tmq, &bars[B_Q_READY + buf], 0, pos0 - P.off, h_idx, b_idx);
+        tma_load_4d(rawq + buf * REGION, &tmz, &bars[B_Q_READY + buf], 0, pos0 - P.z_shift, h_idx, b_idx);
       }
       if (k > 0 && !WAIT(B_KT_FREE + buf, k - 1)) { FAIL(241); break; }
       if (lane == 0) {
         mbar_arrive_expect_tx(&bars[B_KT_READY + buf], KT_BUF);
-        tma_load_3d(kt + buf * KT_BUF, &tmkt, &bars[B_KT_READY + buf], pos0, 0, head);
-        tma_load_3d(kt + buf * KT_BUF + KT_BOX, &tmkt, &bars[B_KT_READY + buf], pos0 + 64, 0, head);
+        tma_load_3d(kt + buf * KT_BUF, &tmxt, &bars[B_KT_READY + buf], pos0, 0, head);
+        tma_load_3d(kt + buf * KT_BUF + KT_BOX, &tmxt, &bars[B_KT_READY + buf], pos0 + 64, 0, head);
       }
       if (k > 0 && !WAIT(B_VP_FREE + buf, k - 1)) { FAIL(242); break; }
       uint8_t* vbuf = vp + buf * VPBUF;
-      for (int r = lane; r < CH; r += 32)  // the ones column of [V | 1] (zero for rows past the last key)
-        *reinterpret_cast<uint4*>(vbuf + 8 * BLK + r * 16) = make_uint4((pos0 + r < P.nk) ? 0x00003F80u : 0u, 0u, 0u, 0u);
-      fence_proxy_async_smem();
-      __syncwarp();
+      if (!DV) {
+        for (int r = lane; r < CH; r += 32)  // the ones column of [V | 1] (zero for rows past the last key)
+          *reinterpret_cast<uint4*>(vbuf + 8 * BLK + r * 16) = make_uint4((pos0 + r < P.ny) ? 0x00003F80u : 0u, 0u, 0u, 0u);
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
       if (lane == 0) {
-        mbar_arrive_expect_tx(&bars[B_VP_READY + buf], 8 * BLK);
+        constexpr int NBLK = DV ? 9 : 8;
+        mbar_arrive_expect_tx(&bars[B_VP_READY + buf], NBLK * BLK);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) tma_load_4d(vbuf + i * BLK, &tmv, &bars[B_VP_READY + buf], 8 * i, pos0, h_idx, b_idx);
+        for (int i = 0; i < NBLK; ++i) tma_load_4d(vbuf + i * BLK, &tmy, &bars[B_VP_READY + buf], 8 * i, pos0 - P.y_shift, h_idx, b_idx);
       }
       __syncwarp();
     }
@@ -507,9 +543,10 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
 #endif
 }
 
-// x (batch, head, token, 64) bf16, any strides -> xt [batch*head][64][ntp] (ntp = tokens rounded up to 64, zero filled).
-// One block per (64-token group, batch*head).
-__global__ void __launch_bounds__(256) transpose_tokens_kernel(View x, __nv_bfloat16* __restrict__ xt, int n, int ntp, int heads) {
+// x (batch, head, token, 64) bf16, any strides -> xt [batch*head][64][ntp]: column p of xt holds token p - shift of x
+// (zero where there is none; ntp is a multiple of 64).  One block per (64-column group, batch*head).
+__global__ void __launch_bounds__(256) transpose_tokens_kernel(View x, __nv_bfloat16* __restrict__ xt, int n, int ntp, int heads,
+                                                               int shift) {
   __shared__ __nv_bfloat16 tile[64][72];
   const int head = blockIdx.y, t0 = blockIdx.x * 64;
   const int b = head / heads, h = head - b * heads;
@@ -517,7 +554,8 @@ __global__ void __launch_bounds__(256) transpose_tokens_kernel(View x, __nv_bflo
   for (int idx = threadIdx.x; idx < 512; idx += 256) {
     const int r = idx >> 3, cv = idx & 7;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (t0 + r < n) v = *reinterpret_cast<const uint4*>(src + (long long)(t0 + r) * x.sn + cv * 8);
+    const int tok = t0 + r - shift;
+    if (tok >= 0 && tok < n) v = *reinterpret_cast<const uint4*>(src + (long long)tok * x.sn + cv * 8);
     *reinterpret_cast<uint4*>(&tile[r][cv * 8]) = v;
   }
   __syncthreads();
