@@ -535,7 +535,7 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
   __syncthreads();
   if (w == 0) tmem_dealloc(tmem_base, 512);
 #ifdef FM_TC_TIMELINE
-  if (tl_ptr) {
+  if (tl_ptr && !DV) {
     const int role = (int)((tl_ptr - reinterpret_cast<uint2*>(sm + OFF_TL)) / 256);
     for (int i = 0; i < tl_n; ++i) g_tc_timeline[role * 1024 + i] = ((long long)tl_ptr[i].x << 32) | tl_ptr[i].y;
     g_tc_timeline_cnt[role] = tl_n;

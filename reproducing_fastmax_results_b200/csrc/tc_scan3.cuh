@@ -16,10 +16,10 @@
 // TMEM columns: 0..319 four state accumulators, 320..447 two dphi buffers, 448..511 two update slabs.
 // Warp roles (768 threads, six warp groups): 0-3 / 4-7 chain-rule groups (group g takes the units with sequence
 // parity g and dphi buffer g), 8-11 / 12-15 update-slab producers (set s makes half s of every tile into ring slot
-// s), 16-19 state conversion, 20 dphi issuer, 21 update issuer, 22 TMA loader.  The chain-rule groups raise their
-// register allowance with setmaxnreg (they keep dz[64] and half a dphi tile in registers), the others lower theirs.
-// The two groups' dz partials are combined in a shared-memory staging tile and added to the float32 accumulator
-// in global memory with one bulk reduce per chunk.  Every wait is bounded (abort flag + error code).
+// s), 16-19 state conversion, 20 dphi issuer, 21 update issuer, 22 TMA loader, 23 drain.  The chain-rule groups raise
+// their register allowance with setmaxnreg (block accumulators and half a dphi tile in registers), the others lower
+// theirs.  The two groups add their dz blocks into a shared-memory staging tile; the drain warp adds it to the
+// float32 accumulator in global memory with one bulk reduce per chunk and zeroes it again.  Every wait is bounded (abort flag + error code).
 #pragma once
 
 namespace s3 {
@@ -31,7 +31,7 @@ using s2::KT_BOX;
 using s2::KT_BUF;
 
 constexpr int THREADS = 768;
-constexpr int W_PROD = 8, W_CONS = 16, W_DPHI = 20, W_UPD = 21, W_TMA = 22;
+constexpr int W_PROD = 8, W_CONS = 16, W_DPHI = 20, W_UPD = 21, W_TMA = 22, W_DRAIN = 23;
 // setmaxnreg moves registers inside the pool the CTA was LAUNCHED with (80 per thread x 768 threads, i.e. 6 x 80 = 480 per
 // lane slot): an `inc` that the pool cannot satisfy blocks forever, so the four allowances below must add up to <= 480.
 constexpr int REG_LAUNCH = 80;   // what ptxas gives a 768-thread kernel; the host checks it (cudaFuncGetAttributes) before launching
@@ -46,7 +46,12 @@ constexpr int OFF_XT = OFF_ZERO + BLK;                 // 149504: transposed X t
 constexpr int OFF_STG = OFF_XT + 2 * KT_BUF;           // 186368: dz staging, 128 rows x ACC_LD floats
 constexpr int STG_BYTES = CH * ACC_LD * 4;             // 34816
 constexpr int OFF_BAR = OFF_STG + STG_BYTES;           // 221184
+#ifdef FM_TC_TIMELINE
+constexpr int OFF_TL = OFF_BAR + 512;                  // development build only: 5 roles x 200 time stamps
+constexpr int SMEM_BYTES = OFF_TL + 5 * 1600 + 1024;
+#else
 constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
+#endif
 static_assert(OFF_XT % 128 == 0 && OFF_STG % 128 == 0 && OFF_BAR % 8 == 0, "tile alignment");
 static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 constexpr uint32_t COL_DPHI = 320u, COL_A = 448u;
@@ -108,6 +113,20 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
   const int nch = P.nchunks;
   auto chunk_of = [&](int i) -> int { return DK ? (nch - 1 - i) : i; };  // i-th chunk of the scan
   auto units_of = [&](int t) -> int { return (tile0 + t < NTILES - 1) ? 2 : 1; };  // the constant feature has no gradient
+#ifdef FM_TC_TIMELINE
+  // development aid: cheap (shared-memory) time stamps of one thread per role of CTA (0, 0), chunks 8..11
+  uint2* tl_ptr = nullptr;
+  int tl_n = 0, tl_c = 0;
+  {
+    const int role = w == 0 ? 0 : w == W_PROD ? 1 : w == W_CONS ? 2 : w == W_DPHI ? 3 : w == W_UPD ? 4 : -1;
+    if (blockIdx.x == 0 && blockIdx.z == 0 && lane == 0 && role >= 0) tl_ptr = reinterpret_cast<uint2*>(sm + OFF_TL) + 200 * role;
+  }
+#define S3_STAMP(tag) do { if (tl_ptr && tl_c >= 8 && tl_c < 12 && tl_n < 200) tl_ptr[tl_n++] = make_uint2((uint32_t)(tag), (uint32_t)clock()); } while (0)
+#define S3_CHUNK(c) tl_c = (c)
+#else
+#define S3_STAMP(tag) do { } while (0)
+#define S3_CHUNK(c) do { } while (0)
+#endif
 
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -119,14 +138,15 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     }
     for (int i = 0; i < 4; ++i) { mbar_init(&bars[B_SB_READY + i], 4); mbar_init(&bars[B_S_DONE + i], 1); mbar_init(&bars[B_A_DONE + i], 1); }
     mbar_init(&bars[B_STG_FREE], 1);
-    mbar_init(&bars[B_STG_HALF], 4);
-    mbar_init(&bars[B_STG_FULL], 4);
+    mbar_init(&bars[B_STG_HALF], 4);   // group 0's warps
+    mbar_init(&bars[B_STG_FULL], 4);   // group 1's warps
     *abort_flag = 0;
     fence_mbar_init();
   }
   if (w == 0) tmem_alloc(tmem_slot, 512);
   // operands are read one column block past what is stored (times zeros): keep every byte of them finite
   for (int i = tid; i < OFF_XT / 16; i += THREADS) reinterpret_cast<uint4*>(sm)[i] = make_uint4(0u, 0u, 0u, 0u);
+  for (int i = tid; i < STG_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(stg)[i] = make_uint4(0u, 0u, 0u, 0u);  // dz staging starts at zero
   fence_proxy_async_smem();
   tc_fence_before_sync();
   __syncthreads();
@@ -143,136 +163,163 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
 
   if (w < W_PROD) {
     // ================= chain rule: dphi (TMEM) -> dz rows =================
+    // Group g takes the units with sequence parity g.  In any slice those touch at most five of the eight 8-column
+    // blocks of dz, so a thread keeps five block accumulators (40 registers) instead of dz[64], which leaves room
+    // to read half a dphi tile (32 values) per TMEM load.
     reg_inc<REG_CHAIN>();
     const int grp = w >> 2;
     const int l = (w & 3) * 32 + lane;
     const uint32_t dphi_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16) + COL_DPHI + 64u * grp;
     const __nv_bfloat16* zbase = reinterpret_cast<const __nv_bfloat16*>(P.z.ptr) + (long long)b_idx * P.z.sb + (long long)h_idx * P.z.sh;
-    float* obase = P.out + (long long)head * P.nz * ACC_LD;
-    uint64_t pairs = 0;   // 16 bits per tile: block pairs (a0, b0, a1, b1) of its two 64-feature units
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      int a0 = 0, b0 = 0, a1 = 0, b1 = 0;
-      if (tile0 + t < NTILES - 1) { pair_decode(2 * (tile0 + t), 8, a0, b0); pair_decode(2 * (tile0 + t) + 1, 8, a1, b1); }
-      pairs |= (uint64_t)(a0 | (b0 << 4) | (a1 << 8) | (b1 << 12)) << (16 * t);
+    uint64_t pairs = 0;     // 16 bits per tile: block pairs (a0, b0, a1, b1) of its two 64-feature units
+    uint32_t slot_of = 0xffffffffu;  // 4 bits per block: accumulator slot of the block in this group (15 = not used)
+    uint32_t blk_of = 0;    // 4 bits per slot: the block it accumulates
+    int nslots = 0;
+    {
+      int mm = 0;
+      for (int t = 0; t < ntl; ++t) {
+        if (tile0 + t == NTILES - 1) continue;
+        int ab[4];
+        pair_decode(2 * (tile0 + t), 8, ab[0], ab[1]);
+        pair_decode(2 * (tile0 + t) + 1, 8, ab[2], ab[3]);
+        pairs |= (uint64_t)(ab[0] | (ab[1] << 4) | (ab[2] << 8) | (ab[3] << 12)) << (16 * t);
+        for (int u = 0; u < 2; ++u, ++mm) {
+          if ((mm & 1) != grp) continue;
+          for (int e = 0; e < 2; ++e) {
+            const int blk = ab[2 * u + e];
+            if (((slot_of >> (4 * blk)) & 15u) == 15u) {
+              slot_of = (slot_of & ~(15u << (4 * blk))) | ((uint32_t)nslots << (4 * blk));
+              blk_of |= (uint32_t)blk << (4 * nslots);
+              ++nslots;
+            }
+          }
+        }
+      }
     }
-    float dz[64];
-    uint32_t m = 0;       // units of the CTA so far (both groups count them; group g takes those with m & 1 == g)
+    float acc[5][8];
+    uint32_t cnt = 0;     // units this group has taken = phase count of its dphi buffer
     bool ok = true;
     for (int ci = 1; ci < nch && ok; ++ci) {
+      S3_CHUNK(ci);
       const int c = chunk_of(ci);
       const long long row = (long long)c * CH + l - P.z_shift;
       const bool valid = row >= 0 && row < P.nz;
       const uint4* zrow = reinterpret_cast<const uint4*>(zbase + (valid ? row : 0) * P.z.sn);
 #pragma unroll
-      for (int j = 0; j < 64; ++j) dz[j] = 0.f;
+      for (int sl = 0; sl < 5; ++sl)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[sl][j] = 0.f;
+      bool lin_mine = false;   // this group owns the linear tile's unit (the last unit of the chunk): added at the drain
+      int mu = 0;              // index of the unit within the chunk: group g takes those with mu & 1 == g
       for (int t = 0; t < ntl && ok; ++t) {
         const bool lin = (tile0 + t == NTILES - 1);
         const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
         const int nu = lin ? 1 : 2;
-        for (int u = 0; u < nu; ++u, ++m) {
-          if ((int)(m & 1u) != grp) continue;
+        for (int u = 0; u < nu; ++u, ++mu) {
+          if ((mu & 1) != grp) continue;
+          if (lin) { lin_mine = true; continue; }
           const int a = (int)((u ? (pr >> 8) : pr) & 15u), b = (int)((u ? (pr >> 12) : (pr >> 4)) & 15u);
+          const int sa = (int)((slot_of >> (4 * a)) & 15u), sbk = (int)((slot_of >> (4 * b)) & 15u);
           // the z blocks of this unit, before the wait so the loads fly meanwhile
           uint4 za4 = make_uint4(0u, 0u, 0u, 0u), zb4 = make_uint4(0u, 0u, 0u, 0u);
-          if (valid && !lin) { za4 = zrow[a]; zb4 = zrow[b]; }
-          if (!WAIT(B_DPHI_DONE + grp, m >> 1)) { FAIL(320); ok = false; break; }
+          if (valid) { za4 = zrow[a]; zb4 = zrow[b]; }
+          S3_STAMP(10);
+          if (!WAIT(B_DPHI_DONE + grp, cnt)) { FAIL(320); ok = false; break; }
+          ++cnt;
           __syncwarp();
+          S3_STAMP(11);
           tc_fence_after_sync();
-          if (!lin) {
-            // Two passes over the unit's 64 dphi values (re-read from TMEM) keep few values live at a time:
-            // pass 0: dz[8a + mi] += w sum_ri D[mi][ri] z[8b + ri];  pass 1: dz[8b + ri] += w sum_mi D[mi][ri] z[8a + mi].
-            const float wgt = (a == b) ? P.c2 : 2.f * P.c2;
+          const float wgt = (a == b) ? P.c2 : 2.f * P.c2;
+          float za[8], zb[8], dza[8], dzb[8];
+          unpack8(za4, wgt, za);
+          unpack8(zb4, wgt, zb);
 #pragma unroll
-            for (int pass = 0; pass < 2; ++pass) {
-              float zs[8], acc[8];
-              unpack8(pass == 0 ? zb4 : za4, wgt, zs);
+          for (int j = 0; j < 8; ++j) { dza[j] = 0.f; dzb[j] = 0.f; }
 #pragma unroll
-              for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t r[32];
+            tmem_ld32(dphi_addr + 32u * hf, r);
+            tmem_ld_wait();
+            if (hf == 1) {  // the whole unit has been read: the buffer can take the next one
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&bars[B_DPHI_FREE + grp]);
+            }
 #pragma unroll
-              for (int qt = 0; qt < 4; ++qt) {
-                uint32_t r[16];
-                tmem_ld16(dphi_addr + 16u * qt, r);
-                tmem_ld_wait();
-                if (pass == 1 && qt == 3) {  // last read of the buffer: it can take the next unit
-                  tc_fence_before_sync();
-                  __syncwarp();
-                  if (lane == 0) mbar_arrive(&bars[B_DPHI_FREE + grp]);
-                }
+            for (int mi = 0; mi < 4; ++mi) {
 #pragma unroll
-                for (int mi = 0; mi < 2; ++mi) {
-#pragma unroll
-                  for (int ri = 0; ri < 8; ++ri) {
-                    const float d = __uint_as_float(r[mi * 8 + ri]);
-                    if (pass == 0) acc[2 * qt + mi] += d * zs[ri];
-                    else acc[ri] += d * zs[2 * qt + mi];
-                  }
-                }
-              }
-              // a, b are warp-uniform: selecting the block with an unrolled compare keeps dz in registers
-              const int blk_sel = pass == 0 ? a : b;
-#pragma unroll
-              for (int blk = 0; blk < 8; ++blk) {
-                if (blk_sel == blk) {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) dz[8 * blk + j] += acc[j];
-                }
+              for (int ri = 0; ri < 8; ++ri) {
+                const float d = __uint_as_float(r[mi * 8 + ri]);
+                dza[4 * hf + mi] += d * zb[ri];
+                dzb[ri] += d * za[4 * hf + mi];
               }
             }
-          } else {  // linear tile: feature m = x[m], weight c1
+          }
+          // the slots are warp-uniform: selecting them with unrolled compares keeps the accumulators in registers
 #pragma unroll
-            for (int qt = 0; qt < 4; ++qt) {
-              uint32_t r[16];
-              tmem_ld16(dphi_addr + 16u * qt, r);
-              tmem_ld_wait();
-              if (qt == 3) {
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars[B_DPHI_FREE + grp]);
-              }
+          for (int sl = 0; sl < 5; ++sl) {
+            if (sa == sl) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) dz[16 * qt + j] += P.c1 * __uint_as_float(r[j]);
+              for (int j = 0; j < 8; ++j) acc[sl][j] += dza[j];
+            }
+            if (sbk == sl) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[sl][j] += dzb[j];
             }
           }
         }
       }
       if (!ok) break;
-      // ---- the chunk's dz: group 0 writes the staging rows, group 1 adds its partial, one bulk reduce-add ----
-      float4* rowp = reinterpret_cast<float4*>(stg + l * ACC_LD);
+      S3_STAMP(12);
+      // ---- the chunk's dz: both groups add their blocks into the (zeroed) staging rows, group 0 first; the drain
+      //      warp then adds the rows to global memory with one bulk reduce and zeroes them again ----
+      float* rowf = stg + l * ACC_LD;
       const uint32_t j = (uint32_t)(ci - 1);  // drains so far
       if (grp == 0) {
-        if (j > 0 && !WAIT(B_STG_FREE, j - 1)) { FAIL(321); break; }   // the previous reduce has read the rows
-#pragma unroll
-        for (int q = 0; q < 16; ++q) rowp[q] = make_float4(dz[4 * q], dz[4 * q + 1], dz[4 * q + 2], dz[4 * q + 3]);
-        rowp[16] = make_float4(0.f, 0.f, 0.f, 0.f);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[B_STG_HALF]);
+        if (j > 0 && !WAIT(B_STG_FREE, j - 1)) { FAIL(321); break; }   // reduced, read and zeroed
       } else {
-        if (j > 0 && w == 4 && lane == 0) { bulk_wait_read_all(); mbar_arrive(&bars[B_STG_FREE]); }
-        if (!WAIT(B_STG_HALF, j)) { FAIL(322); break; }
+        if (!WAIT(B_STG_HALF, j)) { FAIL(322); break; }                // group 0's blocks are in
+      }
 #pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          float4 v = rowp[q];
-          v.x += dz[4 * q]; v.y += dz[4 * q + 1]; v.z += dz[4 * q + 2]; v.w += dz[4 * q + 3];
-          rowp[q] = v;
+      for (int sl = 0; sl < 5; ++sl) {
+        if (sl < nslots) {
+          float4* p4 = reinterpret_cast<float4*>(rowf + 8 * ((blk_of >> (4 * sl)) & 15u));
+          float4 v0 = p4[0], v1 = p4[1];
+          v0.x += acc[sl][0]; v0.y += acc[sl][1]; v0.z += acc[sl][2]; v0.w += acc[sl][3];
+          v1.x += acc[sl][4]; v1.y += acc[sl][5]; v1.z += acc[sl][6]; v1.w += acc[sl][7];
+          p4[0] = v0; p4[1] = v1;
         }
-        fence_proxy_async_smem();
+      }
+      if (lin_mine) {  // linear tile: feature m = x[m], weight c1: dz[m] += c1 dphi[m]
+        if (!WAIT(B_DPHI_DONE + grp, cnt)) { FAIL(324); break; }
+        ++cnt;
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[B_STG_FULL]);
-        if (w == 4) {  // leader warp: all four warps' rows are complete, one lane issues the reduce
-          if (!WAIT(B_STG_FULL, j)) { FAIL(323); break; }
-          if (lane == 0) {
-            const long long q0 = (long long)c * CH - P.z_shift;  // output row of staging row 0
-            const int r0 = q0 < 0 ? (int)(-q0 < CH ? -q0 : CH) : 0;
-            const long long lim = (long long)P.nz - q0;
-            const int r1 = lim < CH ? (lim < 0 ? 0 : (int)lim) : CH;
-            if (r1 > r0) bulk_reduce_add_f32(obase + (q0 + r0) * ACC_LD, stg + r0 * ACC_LD, (uint32_t)(r1 - r0) * (uint32_t)(ACC_LD * 4));
-            bulk_commit_group();
+        tc_fence_after_sync();
+        float4* p4 = reinterpret_cast<float4*>(rowf);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t r[32];
+          tmem_ld32(dphi_addr + 32u * hf, r);
+          tmem_ld_wait();
+          if (hf == 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[B_DPHI_FREE + grp]);
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            float4 v = p4[8 * hf + q];
+            v.x += P.c1 * __uint_as_float(r[4 * q]);     v.y += P.c1 * __uint_as_float(r[4 * q + 1]);
+            v.z += P.c1 * __uint_as_float(r[4 * q + 2]); v.w += P.c1 * __uint_as_float(r[4 * q + 3]);
+            p4[8 * hf + q] = v;
           }
         }
       }
+      fence_proxy_async_smem();   // the copy engine reads these rows
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[grp == 0 ? B_STG_HALF : B_STG_FULL]);
+      S3_STAMP(13);
     }
-    if (w == 4 && lane == 0) bulk_wait_all();  // the last reduce has landed before the CTA retires
   } else if (w < W_CONS) {
     // ================= producers: update slabs (Phi(X)^T, thread = feature) into the two TMEM slots =================
     reg_dec<REG_PROD>();
@@ -289,26 +336,31 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     uint32_t k = 0;   // slabs this set has produced = phase count of its slot
     bool ok = true;
     for (int ci = 0; ci < nch && ok; ++ci) {
+      S3_CHUNK(ci);
       const int buf = ci & 1;
       if (!WAIT(B_XT_READY + buf, (uint32_t)(ci >> 1))) { FAIL(300); break; }
       const uint8_t* box = xtile + buf * KT_BUF + set * KT_BOX;
       for (int t = 0; t < ntl && ok; ++t, ++k) {
         const bool lin = (tile0 + t == NTILES - 1);
         const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
+        S3_STAMP(40);
         uint32_t r[32];
         if (!lin) {
           const uint32_t q = (f >> 6) ? (pr >> 8) : pr;
           s2::update_pair_slab(r, box, 8 * (int)(q & 15) + ((f >> 3) & 7), 8 * (int)((q >> 4) & 15) + (f & 7));
         } else if (f < 64) s2::copy_trow_slab(r, box, f);
         else s2::fill_slab(r, f == 64 ? 0x3F803F80u : 0u);
+        S3_STAMP(41);
         if (k > 0 && !WAIT(B_EMPTY + set, k - 1)) { FAIL(301); ok = false; break; }
         __syncwarp();
+        S3_STAMP(42);
         tc_fence_after_sync();
         tmem_st32(slot_addr, r);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[B_FULL + set]);
+        S3_STAMP(43);
       }
       if (ok) {
         __syncwarp();
@@ -322,10 +374,13 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     const uint32_t lane_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16);
     bool ok = true;
     for (int ci = 0; ci + 1 < nch && ok; ++ci) {
+      S3_CHUNK(ci);
       for (int t = 0; t < ntl && ok; ++t) {
+        S3_STAMP(70);
         // S_t is final (update issuer) and Sb_t is no longer read (dphi issuer; the first chunk has no dphi)
         if (!WAIT(B_S_DONE + t, (uint32_t)ci) || (ci > 0 && !WAIT(B_A_DONE + t, (uint32_t)(ci - 1)))) { FAIL(310); ok = false; break; }
         __syncwarp();
+        S3_STAMP(71);
         tc_fence_after_sync();
         uint8_t* dst = sb + t * SB_TILE + l * 16;
 #pragma unroll
@@ -344,6 +399,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[B_SB_READY + t]);
+        S3_STAMP(72);
       }
     }
   } else {
@@ -351,10 +407,12 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     if (w == W_DPHI) {
       // ================= dphi issuer: D_u = G_c Sb_t[unit u]^T, five K = 16 steps over the 80 columns =================
       constexpr uint32_t IDESC = make_idesc_bf16(128, 64, 0, 0);   // A K-major, B K-major
-      uint32_t m = 0;
+      uint32_t cnt0 = 0, cnt1 = 0;   // units issued into dphi buffer 0 / 1
       bool ok = true;
       for (int ci = 0; ci < nch && ok; ++ci) {
+        S3_CHUNK(ci);
         const int buf = ci & 1;
+        int mu = 0;                  // index of the unit within the chunk: buffer (= chain group) mu & 1
         if (!WAIT(B_G_READY + buf, (uint32_t)(ci >> 1))) { FAIL(330); break; }
         const uint32_t g_addr = smem_u32(gtile + buf * TILE9);
         const uint64_t dA = make_smem_desc(g_addr, 2048, 128, 0);                       // column blocks 2 ks, 2 ks + 1
@@ -362,10 +420,14 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
         for (int t = 0; t < ntl && ok && ci > 0; ++t) {
           if (!WAIT(B_SB_READY + t, (uint32_t)(ci - 1))) { FAIL(331); ok = false; break; }
           const int nu = units_of(t);
-          for (int u = 0; u < nu && ok; ++u, ++m) {
-            const uint32_t db = m & 1u;
-            if (m >= 2 && !WAIT(B_DPHI_FREE + db, (m >> 1) - 1u)) { FAIL(332); ok = false; break; }
+          for (int u = 0; u < nu && ok; ++u, ++mu) {
+            const uint32_t db = (uint32_t)(mu & 1);
+            const uint32_t used = db ? cnt1 : cnt0;
+            S3_STAMP(20);
+            if (used > 0 && !WAIT(B_DPHI_FREE + db, used - 1u)) { FAIL(332); ok = false; break; }
+            if (db) ++cnt1; else ++cnt0;
             __syncwarp();
+            S3_STAMP(21);
             tc_fence_after_sync();
             if (elect_one()) {
               const uint32_t d = tmem_base + COL_DPHI + 64u * db;
@@ -377,6 +439,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
               if (u == nu - 1) mma_commit(&bars[B_A_DONE + t]);
             }
             __syncwarp();
+            S3_STAMP(22);
           }
         }
         if (ok && elect_one()) mma_commit(&bars[B_G_FREE + buf]);   // every dphi MMA of the chunk has read G
@@ -390,6 +453,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
       uint32_t k = 0;   // tiles issued = phase count of both slots
       bool ok = true;
       for (int ci = 0; ci < nch && ok; ++ci) {
+        S3_CHUNK(ci);
         const int buf = ci & 1;
         if (!WAIT(B_Y_READY + buf, (uint32_t)(ci >> 1))) { FAIL(340); break; }
         const uint64_t dB = make_smem_desc(smem_u32(ytile + buf * TILE9), 128, 2048, 0);
@@ -399,8 +463,10 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
           const uint32_t d = tmem_base + 80u * t;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
+            S3_STAMP(30);
             if (!WAIT(B_FULL + hf, k)) { FAIL(342); ok = false; break; }
             __syncwarp();
+            S3_STAMP(31);
             tc_fence_after_sync();
             if (elect_one()) {
               const uint32_t a0 = tmem_base + COL_A + 32u * hf;
@@ -416,11 +482,34 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
               }
             }
             __syncwarp();
+            S3_STAMP(32);
           }
         }
       }
       if (ok && nch > 0 && !WAIT(B_Y_FREE + ((nch - 1) & 1), (uint32_t)((nch - 1) >> 1))) FAIL(343);
       tc_fence_after_sync();
+    } else if (w == W_DRAIN) {
+      // ================= drain: staging rows -> global accumulator (one bulk reduce-add per chunk) =================
+      float* obase = P.out + (long long)head * P.nz * ACC_LD;
+      for (int ci = 1; ci < nch; ++ci) {
+        const uint32_t j = (uint32_t)(ci - 1);
+        if (!WAIT(B_STG_FULL, j)) { FAIL(360); break; }
+        __syncwarp();
+        if (lane == 0) {
+          const long long q0 = (long long)chunk_of(ci) * CH - P.z_shift;  // output row of staging row 0
+          const int r0 = q0 < 0 ? (int)(-q0 < CH ? -q0 : CH) : 0;
+          const long long lim = (long long)P.nz - q0;
+          const int r1 = lim < CH ? (lim < 0 ? 0 : (int)lim) : CH;
+          if (r1 > r0) bulk_reduce_add_f32(obase + (q0 + r0) * ACC_LD, stg + r0 * ACC_LD, (uint32_t)(r1 - r0) * (uint32_t)(ACC_LD * 4));
+          bulk_commit_group();
+          bulk_wait_read_all();   // the copy engine has read the rows
+        }
+        __syncwarp();
+        for (int i = lane; i < STG_BYTES / 16; i += 32) reinterpret_cast<uint4*>(stg)[i] = make_uint4(0u, 0u, 0u, 0u);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[B_STG_FREE]);
+      }
+      if (lane == 0) bulk_wait_all();  // the last reduce has landed before the CTA retires
     } else if (w == W_TMA) {
       // ================= TMA loader =================
       bool ok = true;
@@ -459,6 +548,13 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   if (w == 0) tmem_dealloc(tmem_base, 512);
+#ifdef FM_TC_TIMELINE
+  if (tl_ptr && !DK) {
+    const int role = (int)((tl_ptr - reinterpret_cast<uint2*>(sm + OFF_TL)) / 200);
+    for (int i = 0; i < tl_n; ++i) g_tc_timeline[role * 1024 + i] = ((long long)tl_ptr[i].x << 32) | tl_ptr[i].y;
+    g_tc_timeline_cnt[role] = tl_n;
+  }
+#endif
 }
 
 }  // namespace s3
