@@ -41,6 +41,12 @@ WORKLOADS = {
 }
 SEQUENCE_SHARDED = {"cfg3_f32_causal_p2_B1_H8_N131072_D32"}
 DEFAULT = "cfg2_bf16_causal_p2_B8_H16_N4096_D64"
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch from the ncu captures summarised under profiles/ (taken
+# on the prof_ workload: 64 heads x 4096 tokens); bench.py scales them by head-tokens to its own workload.
+DRAM_TRAFFIC = {
+    name: {"bytes_per_launch": b, "head_tokens": 64 * 4096, "source": "profiles/ncu_tc_scans_prof_workload.md"}
+    for name, b in (("tc_scan_fwd", 204.99e6), ("tc_scan_bwd_q", 256.05e6), ("tc_scan_bwd_kv", 258.17e6), ("tc_scan_bwd_dv", 215.86e6))
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -70,55 +76,84 @@ def executed_units(D, order):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons for one GPU while the timed region runs."""
+    """Samples SM clocks and throttle reasons of one GPU while the timed region runs (NVML every 5 ms in a thread;
+    `nvidia-smi -lms` when the NVML binding is missing).  Reading the settings changes nothing on the GPU."""
 
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index):
         self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self.stop_flag = threading.Event()
+        self.thread = None
         self.proc = None
-        self.lines = []
+
+    def _nvml_loop(self, nv, handle):
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(handle)) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml as nv
+
+            nv.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[self.index]) if vis and vis.split(",")[self.index].isdigit() else self.index
+            handle = nv.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+        try:
+            q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._smi_loop, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
+    def _smi_loop(self):
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 7:
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                self.samples.append(float(parts[0]))
+                self.max_mhz = float(parts[1])
             except ValueError:
                 continue
-            for nm, val in zip(names, parts[3:7]):
+            for nm, val in zip(names, parts[2:6]):
                 if val.lower().startswith("active"):
-                    reasons.add(nm)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                    self.reasons.add(nm)
+
+    def stop(self):
+        self.stop_flag.set()
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "samples": 0, "reasons": ["no clock samples"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "samples": len(self.samples),
+                "reasons": sorted(self.reasons)}
 
 
 # ----------------------------------------------------------------------------------------------------
@@ -208,7 +243,7 @@ def run_sequence_sharded(args, torch, dist, dev, rank, world):
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else int(os.environ.get("LOCAL_RANK", "0")))
+    sampler = ClockSampler(torch.cuda.current_device())
     if rank == 0:
         sampler.start()
     launches0 = lib.fastmax_launch_count()
@@ -325,7 +360,7 @@ def main():
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
+    sampler = ClockSampler(torch.cuda.current_device())
     if rank == 0:
         sampler.start()
     launches0 = lib.fastmax_launch_count()
@@ -360,30 +395,48 @@ def main():
         kk["share"] = kk["ms_per_step"] / total_kernel_ms if total_kernel_ms else 0.0
     pk = peaks()
     U = algorithmic_flops(B, H, N, D, order)
-    units_alg = {"scan_fwd": 2.0, "tc_scan_fwd": 2.0, "scan_bwd_q": 1.0, "tc_scan_bwd_q": 1.0,
-                 "scan_bwd_kv": 3.0, "tc_scan_bwd_kv": 3.0, "moments_kv": 1.0, "moments_qg": 1.0, "tc_moments": 1.0}
+    # Work units per launch, in passes over all tokens (one pass = U flops with the full D^2 feature map):
+    #   algorithmic: what the reference's formulation needs (forward 2, dq 1, dS + dk 2, dv 1: 6 per step);
+    #   executed:    contraction passes the kernel really runs, over the block-symmetric feature rows (x 0.569):
+    #                every scan recomputes its state (apply/dphi + update = 2 passes).
+    units_alg = {"scan_fwd": 2.0, "tc_scan_fwd": 2.0, "scan_bwd_q": 1.0, "tc_scan_bwd_q": 1.0, "scan_bwd_kv": 3.0,
+                 "tc_scan_bwd_kv": 2.0, "tc_scan_bwd_dv": 1.0, "moments_kv": 1.0, "moments_qg": 1.0, "tc_moments": 1.0}
+    units_exec = {"tc_scan_fwd": 2.0, "tc_scan_bwd_q": 2.0, "tc_scan_bwd_kv": 2.0, "tc_scan_bwd_dv": 2.0}
+    m_full = 1 + D + (D * D if order == 2 else 0)
+    ratio_exec = executed_units(D, order) / m_full
+
+    def counted_flops(name):
+        """min(algorithmic, executed) flops of one launch: never credits more than the hardware did."""
+        alg = units_alg.get(name, 0.0) * U
+        ex = units_exec.get(name, units_alg.get(name, 0.0)) * U * (ratio_exec if name.startswith("tc_") else 1.0)
+        return min(alg, ex), alg
+
     dominant = max(kernels, key=lambda n: kernels[n]["ms_per_step"]) if kernels else None
     roofline = None
     if dominant is not None:
-        m_full = 1 + D + (D * D if order == 2 else 0)
-        ratio_exec = executed_units(D, order) / m_full
-        flops_alg = units_alg.get(dominant, 0.0) * U / max(kernels[dominant]["launches_per_step"], 1e-9)
+        counted, alg = counted_flops(dominant)
+        per_launch = 1.0 / max(kernels[dominant]["launches_per_step"], 1e-9)
         dur_s = kernels[dominant]["ms_per_launch"] * 1e-3
-        peak = pk["bf16_tflops_sustained"] if dtype_name == "bf16" else pk["bf16_tflops_sustained"]
-        achieved = flops_alg / dur_s / 1e12
+        peak = pk["bf16_tflops_sustained"]
+        achieved = counted * per_launch / dur_s / 1e12
         roofline = {
             "kernel": dominant, "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": achieved / peak, "peak_source": pk["_source"] + " (sustained cuBLAS bf16: kernel timed inside a long step)",
-            "achieved_executed": achieved * ratio_exec,
-            "frac_executed": achieved * ratio_exec / peak,
-            "note": "achieved counts the full D^2 feature contraction (algorithmic flops); achieved_executed counts the "
-                    "block-symmetric feature rows the kernel really contracts over",
-            "traffic": None,
+            "full_d2_equivalent": alg * per_launch / dur_s / 1e12,
+            "note": "achieved = min(algorithmic, executed) flops of the launch / its CUDA-event time: executed counts the "
+                    "block-symmetric feature rows (0.569 of D^2+D+1) the kernel contracts over, twice (state rebuild + "
+                    "apply or dphi); full_d2_equivalent is the rate the reference's D^2 formulation would need",
+            "traffic": DRAM_TRAFFIC.get(dominant, {}).get("bytes_per_launch") and
+                       DRAM_TRAFFIC[dominant]["bytes_per_launch"] * (B * H * N) / DRAM_TRAFFIC[dominant]["head_tokens"],
+            "traffic_source": DRAM_TRAFFIC.get(dominant, {}).get("source"),
         }
+    step_counted = sum(counted_flops(n)[0] * kernels[n]["launches_per_step"] for n in kernels)
     whole = {
         "flops_alg_per_step": 6.0 * U,
-        "tflops_alg": 6.0 * U / (ms_step * 1e-3) / 1e12 / world * world,
-        "frac_of_peak": 6.0 * U / (ms_step * 1e-3) / 1e12 / (pk["bf16_tflops_sustained"]),
+        "flops_counted_per_step": step_counted,
+        "tflops_counted": step_counted / (ms_step * 1e-3) / 1e12,
+        "frac_of_peak": step_counted / (ms_step * 1e-3) / 1e12 / pk["bf16_tflops_sustained"],
+        "tflops_full_d2_equivalent": 6.0 * U / (ms_step * 1e-3) / 1e12,
     }
 
     # ---- end to end: public operator, pinned host buffers, H2D + D2H inside the timed region ----

@@ -1,23 +1,14 @@
-// tcgen05 / TMEM kernels of the Fastmax engine: bf16 operands, fp32 accumulation in tensor memory.
-//
-// Forward causal scan, head dim 64, order 2.  One CTA = (batch*head, feature slice).  The 2369 feature rows
-// of the state are cut into 19 tiles of 128 rows (18 tiles of two 8x8-block pair units + the lin tile);
-// slice s owns tiles 4s..4s+3 (the last slice three).  Per 128-token chunk c and tile t (operands bf16 in
-// shared memory, accumulators fp32 in TMEM):
-//     apply   O'_c (128 x 80)  += Phi_t(Q_c) (128 x 128)  *  Sb_t (128 x 80)         A K-major,  B MN-major
-//     update  S_t  (128 x 80)  += Phi_t(K_c)^T (128 x 128) *  [V_c | 1] (128 x 80)    A MN-major, B MN-major
-// and, in a separate kernel that is parallel over chunks,
-//     intra   Sc = Q_c K_c^T (128 x 128);  P = tril f(Sc) -> bf16;  O'_c += P [V_c | 1].
-// Phi tiles are generated by the CUDA cores straight into the 128-byte-swizzled operand layout (the same
-// bytes serve as a K-major A operand for `apply` and as an MN-major A operand for `update`); S_t is read
-// back from TMEM once per chunk, weighted, rounded to bf16 and stored as the B operand Sb_t of the next
-// chunk's `apply`.
-// The scan CTA is warp-specialised: a TMA warp streams the raw q, k tiles (128-byte swizzle) and the
-// [V | 1] column blocks, eight producer warps generate Phi tiles into a ring of three operand buffers, one
-// warp issues the tcgen05.mma instructions, four consumer warps convert states and drain O' (double-buffered
-// in TMEM) with float4 atomics into the fp32 accumulator the combine/divide kernel reads.  All hand-offs are
-// mbarriers (full/empty ring, tcgen05.commit); every wait is bounded: on a timeout a role records an error
-// code, raises the CTA's abort flag, and the CTA frees its TMEM and returns.
+// tcgen05 / TMEM kernels of the Fastmax engine: bf16 operands, fp32 accumulation in tensor memory; causal, head
+// dim 64, order 2.  The 2369 feature rows of the state are cut into 19 tiles of 128 rows (18 tiles of two 8x8-block
+// pair units + the tile with the linear and constant features); a scan CTA = (batch*head, slice of 4 tiles).
+// This file holds what the scans share and the host side:
+//   intra_fwd_kernel   O'_c += tril f(Q_c K_c^T) [V_c | 1], one CTA per (chunk, head), parallel over chunks
+//   tc_bwd.cuh         intra-chunk backward kernel, dO' prologue
+//   tc_scan2.cuh       forward scan and dv scan ("apply + update", Phi operands in tensor memory)
+//   tc_scan3.cuh       dq and dk scans (dphi + chain rule + update)
+//   tc_forward / tc_backward: tensor maps, workspace layout, launch sequences
+// Every device-side wait is bounded: on a timeout a role records an error code, raises the CTA's abort flag, and
+// the CTA frees its TMEM and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <stdlib.h>
@@ -33,47 +24,20 @@ __device__ int g_tc_status = 0;
 // how often each wait site of the tensor-core kernels gave up first in its CTA (index = code & 255); diagnostics only
 __device__ int g_tc_wait_hist[256];
 
-// Optional phase timeline of CTA (0,0,0) (development aid, compiled in with -DFM_TC_TIMELINE; call from ONE thread).
+// Development aid, compiled in with -DFM_TC_TIMELINE only: per-role clock stamps of CTA (0, 0) of the scan kernels
+// (1024 entries per role, tag << 32 | clock), read back with fastmax_debug_timeline_roles().
 #ifdef FM_TC_TIMELINE
 __device__ long long g_tc_timeline[8192];
-__device__ int g_tc_timeline_n = 0;
 __device__ int g_tc_timeline_cnt[8];
-#define FM_STAMP(tag)                                                                  \
-  do {                                                                                 \
-    if (blockIdx.x == 0 && blockIdx.z == 0) {                                          \
-      const int i_ = atomicAdd(&g_tc_timeline_n, 2);                                   \
-      if (i_ < 8190) {                                                                 \
-        g_tc_timeline[i_] = (long long)(tag);                                          \
-        g_tc_timeline[i_ + 1] = clock64();                                             \
-      }                                                                                \
-    }                                                                                  \
-  } while (0)
-#else
-#define FM_STAMP(tag) do { } while (0)
 #endif
 
 namespace tc {
 
-constexpr int NPRODUCER = 256;          // warps 0..7
-constexpr int NCONSUMER = 128;          // warps 8..11
-constexpr int WARP_MMA = 12, WARP_TMA = 13;
-constexpr int NTHREADS = 448;
 constexpr int CH = 128;                 // tokens per chunk
 constexpr int REGION = 16384;           // 128 rows x 128 B
-constexpr int TILE = 2 * REGION;        // one Phi tile (128 tokens x 128 features, bf16)
-constexpr int NSLOT = 3;
+constexpr int TILE = 2 * REGION;        // a 128 x 128 bf16 operand tile
 constexpr int BLK = 2048;               // one 8-column block of an MN-major operand: 128 rows x 16 B
 constexpr int SB_TILE = 9 * BLK;        // 72 columns stored; the MMA's columns 72..79 read the bytes that follow
-constexpr int OFF_RING = 0;
-constexpr int OFF_SB = OFF_RING + NSLOT * TILE;       // 98304
-constexpr int OFF_VP = OFF_SB + 4 * SB_TILE;          // 172032
-constexpr int OFF_RAWQ = OFF_VP + 9 * BLK;            // 190464
-constexpr int OFF_RAWK = OFF_RAWQ + REGION;           // 206848
-constexpr int OFF_BAR = OFF_RAWK + REGION;            // 223232
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;      // barriers + alignment slack
-// barrier indices
-constexpr int B_FULL = 0, B_EMPTY = 3, B_SB_READY = 6, B_S_DONE = 10, B_RAW_READY = 14, B_RAW_FREE = 15,
-              B_VP_READY = 16, B_VP_FREE = 17, B_O_DONE = 18, B_O_FREE = 20, B_COUNT = 22;
 constexpr int NTILES = 19;
 constexpr long long WAIT_CYCLES = 4000000000ll;       // ~2 s at 2 GHz
 
@@ -90,47 +54,6 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&r);
-}
-
-// One 64-feature unit of a Phi tile for token row l: features x[8a+mi] * x[8b+ri], chunk mi of the row.
-__device__ __forceinline__ void gen_pair_unit(uint8_t* region, const uint8_t* raw, int l, int a, int b) {
-  const int sw = l & 7;
-  const uint4 xa4 = *reinterpret_cast<const uint4*>(raw + l * 128 + ((a ^ sw) << 4));
-  const uint4 xb4 = *reinterpret_cast<const uint4*>(raw + l * 128 + ((b ^ sw) << 4));
-  const uint32_t xa[4] = {xa4.x, xa4.y, xa4.z, xa4.w};
-#pragma unroll
-  for (int mi = 0; mi < 8; ++mi) {
-    const uint32_t pr = xa[mi >> 1];
-    const uint32_t bc = (mi & 1) ? __byte_perm(pr, pr, 0x3232) : __byte_perm(pr, pr, 0x1010);
-    uint4 o;
-    o.x = hmul2_u32(bc, xb4.x);
-    o.y = hmul2_u32(bc, xb4.y);
-    o.z = hmul2_u32(bc, xb4.z);
-    o.w = hmul2_u32(bc, xb4.w);
-    *reinterpret_cast<uint4*>(region + l * 128 + ((mi ^ sw) << 4)) = o;
-  }
-}
-
-// Phi tile `gt` (global tile index) of the raw tile, written by thread (row l, half h) into `tile`.
-__device__ __forceinline__ void gen_tile(uint8_t* tile, const uint8_t* raw, int gt, int l, int h) {
-  uint8_t* region = tile + h * REGION;
-  if (gt < NTILES - 1) {
-    int a, b;
-    pair_decode(2 * gt + h, 8, a, b);
-    gen_pair_unit(region, raw, l, a, b);
-  } else if (h == 0) {  // lin tile, features 0..63 = x
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-      *reinterpret_cast<uint4*>(region + l * 128 + (c << 4)) = *reinterpret_cast<const uint4*>(raw + l * 128 + (c << 4));
-  } else {  // lin tile, feature 64 = 1, features 65..127 = 0
-    const int sw = l & 7;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      uint4 o = make_uint4(0u, 0u, 0u, 0u);
-      if (c == 0) o.x = 0x00003F80u;  // bf16 1.0 in the low half
-      *reinterpret_cast<uint4*>(region + l * 128 + ((c ^ sw) << 4)) = o;
-    }
-  }
 }
 
 __device__ __forceinline__ float tile_weight(int gt, int f, float c0, float c1, float c2) {
@@ -161,224 +84,6 @@ __device__ __forceinline__ void store_block8_plain(uint8_t* dst, const uint32_t*
   *reinterpret_cast<uint4*>(dst) = o;
 }
 
-
-// ------------------------------------------------------------------------------------------------------
-// warp-specialised forward scan
-// ------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(NTHREADS, 1)
-scan_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
-                const __grid_constant__ CUtensorMap tmv, const FwdParams P) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  uint8_t* sm = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  uint8_t* ring = sm + OFF_RING;
-  uint8_t* sb = sm + OFF_SB;
-  uint8_t* vp = sm + OFF_VP;
-  uint8_t* rawq = sm + OFF_RAWQ;
-  uint8_t* rawk = sm + OFF_RAWK;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_BAR);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_BAR + 192);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BAR + 200);
-
-  const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
-  const int slice = blockIdx.x, head = blockIdx.z;
-  const int b_idx = head / P.heads, h_idx = head - b_idx * P.heads;
-  const int tile0 = slice * 4;
-  const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
-  const int nch = P.nchunks;
-
-  if (tid == 0) {
-    for (int i = 0; i < 3; ++i) { mbar_init(&bars[B_FULL + i], NPRODUCER); mbar_init(&bars[B_EMPTY + i], 1); }
-    for (int i = 0; i < 4; ++i) { mbar_init(&bars[B_SB_READY + i], NCONSUMER); mbar_init(&bars[B_S_DONE + i], 1); }
-    mbar_init(&bars[B_RAW_READY], 1);
-    mbar_init(&bars[B_RAW_FREE], NPRODUCER);
-    mbar_init(&bars[B_VP_READY], 1);
-    mbar_init(&bars[B_VP_FREE], 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&bars[B_O_DONE + i], 1); mbar_init(&bars[B_O_FREE + i], NCONSUMER); }
-    *abort_flag = 0;
-    fence_mbar_init();
-  }
-  if (w == 0) tmem_alloc(tmem_slot, 512);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-  constexpr uint32_t COL_O = 320u;  // two O' buffers of 80 columns behind the four state tiles
-
-  auto WAIT = [&](int bar, uint32_t parity) -> bool {
-    return mbar_wait_abortable(&bars[bar], parity & 1u, WAIT_CYCLES, abort_flag);
-  };
-  auto FAIL = [&](int code) {
-    *abort_flag = 1;
-    atomicExch(&g_tc_status, code);
-  };
-
-  if (w < 8) {
-    // ================= producers: Phi tiles into the ring =================
-    const int h = w >> 2, l = (w & 3) * 32 + lane;
-    uint32_t n = 0;
-    bool ok = true;
-    for (int c = 0; c < nch && ok; ++c) {
-      if (!WAIT(B_RAW_READY, c)) { FAIL(10); break; }
-      for (int t = 0; t < ntl && ok; ++t) {
-        const int gt = tile0 + t;
-#pragma unroll 1
-        for (int which = (c > 0 ? 0 : 1); which < 2; ++which) {  // 0: Phi(Q) for apply, 1: Phi(K) for update
-          const uint32_t slot = n % NSLOT, k = n / NSLOT;
-          if (k > 0 && !WAIT(B_EMPTY + slot, k - 1)) { FAIL(11); ok = false; break; }
-          gen_tile(ring + slot * TILE, which == 0 ? rawq : rawk, gt, l, h);
-          fence_proxy_async_smem();
-          mbar_arrive(&bars[B_FULL + slot]);
-          ++n;
-        }
-      }
-      if (ok) mbar_arrive(&bars[B_RAW_FREE]);
-    }
-  } else if (w < 12) {
-    // ================= consumers: state conversion and O' drain =================
-    const int l = (w & 3) * 32 + lane;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16);
-    float* obase = P.oacc + (long long)head * P.nq * 68;
-    bool ok = true;
-    for (int c = 0; c < nch && ok; ++c) {
-      for (int t = 0; t < ntl && ok; ++t) {
-        if (t == ntl - 1 && c > 0) {  // O' of this chunk is complete once the last apply has finished
-          const int buf = c & 1;
-          if (!WAIT(B_O_DONE + buf, (uint32_t)((c - 1) >> 1))) { FAIL(20); ok = false; break; }
-          tc_fence_after_sync();
-          uint32_t ra[32], rb[32], rc[8];
-          tmem_ld32(lane_addr + COL_O + 80u * buf, ra);
-          tmem_ld32(lane_addr + COL_O + 80u * buf + 32u, rb);
-          tmem_ld8(lane_addr + COL_O + 80u * buf + 64u, rc);
-          tmem_ld_wait();
-          tc_fence_before_sync();
-          mbar_arrive(&bars[B_O_FREE + buf]);
-          const long long ql = (long long)c * CH + l - P.off;
-          if (ql >= 0 && ql < P.nq) {
-            float* dst = obase + ql * 68;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              atomicAdd(reinterpret_cast<float4*>(dst + 4 * j),
-                        make_float4(__uint_as_float(ra[4 * j]), __uint_as_float(ra[4 * j + 1]),
-                                    __uint_as_float(ra[4 * j + 2]), __uint_as_float(ra[4 * j + 3])));
-              atomicAdd(reinterpret_cast<float4*>(dst + 32 + 4 * j),
-                        make_float4(__uint_as_float(rb[4 * j]), __uint_as_float(rb[4 * j + 1]),
-                                    __uint_as_float(rb[4 * j + 2]), __uint_as_float(rb[4 * j + 3])));
-            }
-            atomicAdd(dst + 64, __uint_as_float(rc[0]));
-          }
-        }
-        if (c < nch - 1) {  // the bf16 copy of S_t feeds the next chunk's apply
-          if (!WAIT(B_S_DONE + t, c)) { FAIL(21); ok = false; break; }
-          tc_fence_after_sync();
-          const float wgt = tile_weight(tile0 + t, l, P.c0, P.c1, P.c2);
-          uint8_t* dst = sb + t * SB_TILE + l * 16;
-#pragma unroll
-          for (int part = 0; part < 2; ++part) {
-            uint32_t r[32];
-            tmem_ld32(lane_addr + 80u * t + 32u * part, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int jb = 0; jb < 4; ++jb) store_block8(dst + (4 * part + jb) * BLK, &r[8 * jb], wgt);
-          }
-          uint32_t r8[8];
-          tmem_ld8(lane_addr + 80u * t + 64u, r8);
-          tmem_ld_wait();
-          store_block8(dst + 8 * BLK, r8, wgt);
-          fence_proxy_async_smem();
-          tc_fence_before_sync();
-          mbar_arrive(&bars[B_SB_READY + t]);
-        }
-      }
-    }
-  } else if (w == WARP_MMA) {
-    // ================= MMA issuer =================
-    constexpr uint32_t IDESC_K = make_idesc_bf16(128, 80, 0, 1);   // A K-major,  B MN-major
-    constexpr uint32_t IDESC_MN = make_idesc_bf16(128, 80, 1, 1);  // A MN-major, B MN-major
-    const uint64_t dA_K = make_smem_desc(smem_u32(ring), 16, 1024, 2);
-    const uint64_t dA_MN = make_smem_desc(smem_u32(ring), REGION, 1024, 2);
-    const uint64_t dB_V = make_smem_desc(smem_u32(vp), 128, 2048, 0);
-    const uint64_t dB_S = make_smem_desc(smem_u32(sb), 128, 2048, 0);
-    uint32_t n = 0;
-    bool ok = true;
-    for (int c = 0; c < nch && ok; ++c) {
-      for (int t = 0; t < ntl && ok; ++t) {
-        if (c > 0) {  // apply
-          const uint32_t slot = n % NSLOT, k = n / NSLOT;
-          if (lane == 0) FM_STAMP(10);
-          if (!WAIT(B_FULL + slot, k) || !WAIT(B_SB_READY + t, (uint32_t)(c - 1))) { FAIL(30); ok = false; break; }
-          if (t == 0 && c >= 3 && !WAIT(B_O_FREE + (c & 1), (uint32_t)((c - 3) >> 1))) { FAIL(31); ok = false; break; }
-          tc_fence_after_sync();
-          if (lane == 0) FM_STAMP(11);
-          if (lane == 0) {
-            const uint32_t d = tmem_base + COL_O + 80u * (c & 1);
-            const uint64_t a0 = dA_K + (uint64_t)((slot * TILE) >> 4);
-            const uint64_t b0 = dB_S + (uint64_t)((t * SB_TILE) >> 4);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              mma_ss(d, a0 + (uint64_t)(((ks >> 2) * REGION + (ks & 3) * 32) >> 4), b0 + (uint64_t)(16 * ks), IDESC_K,
-                     (t > 0 || ks > 0) ? 1u : 0u);
-            mma_commit(&bars[B_EMPTY + slot]);
-            if (t == ntl - 1) mma_commit(&bars[B_O_DONE + (c & 1)]);
-            FM_STAMP(12);
-          }
-          __syncwarp();
-          ++n;
-        }
-        {  // update
-          const uint32_t slot = n % NSLOT, k = n / NSLOT;
-          if (lane == 0) FM_STAMP(20);
-          if (!WAIT(B_FULL + slot, k)) { FAIL(32); ok = false; break; }
-          if (t == 0 && !WAIT(B_VP_READY, (uint32_t)c)) { FAIL(33); ok = false; break; }
-          tc_fence_after_sync();
-          if (lane == 0) FM_STAMP(21);
-          if (lane == 0) {
-            const uint32_t d = tmem_base + 80u * t;
-            const uint64_t a0 = dA_MN + (uint64_t)((slot * TILE) >> 4);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              mma_ss(d, a0 + (uint64_t)(128 * ks), dB_V + (uint64_t)(16 * ks), IDESC_MN, (c > 0 || ks > 0) ? 1u : 0u);
-            mma_commit(&bars[B_EMPTY + slot]);
-            mma_commit(&bars[B_S_DONE + t]);
-            if (t == ntl - 1) mma_commit(&bars[B_VP_FREE]);
-            FM_STAMP(22);
-          }
-          __syncwarp();
-          ++n;
-        }
-      }
-    }
-    if (ok && nch > 0 && !WAIT(B_VP_FREE, (uint32_t)(nch - 1))) FAIL(34);  // every MMA has completed
-    tc_fence_after_sync();
-  } else {
-    // ================= TMA loader =================
-    bool ok = true;
-    for (int c = 0; c < nch && ok; ++c) {
-      const int pos0 = c * CH;
-      if (c > 0 && !WAIT(B_RAW_FREE, (uint32_t)(c - 1))) { FAIL(40); break; }
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&bars[B_RAW_READY], 2 * REGION);
-        tma_load_4d(rawq, &tmq, &bars[B_RAW_READY], 0, pos0 - P.off, h_idx, b_idx);
-        tma_load_4d(rawk, &tmk, &bars[B_RAW_READY], 0, pos0, h_idx, b_idx);
-      }
-      if (c > 0 && !WAIT(B_VP_FREE, (uint32_t)(c - 1))) { FAIL(41); break; }
-      for (int r = lane; r < CH; r += 32)  // the ones column of [V | 1] (zero for rows past the last key)
-        *reinterpret_cast<uint4*>(vp + 8 * BLK + r * 16) = make_uint4((pos0 + r < P.nk) ? 0x00003F80u : 0u, 0u, 0u, 0u);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&bars[B_VP_READY], 8 * BLK);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) tma_load_4d(vp + i * BLK, &tmv, &bars[B_VP_READY], 8 * i, pos0, h_idx, b_idx);
-      }
-      __syncwarp();
-    }
-  }
-
-  tc_fence_before_sync();
-  __syncthreads();
-  if (w == 0) tmem_dealloc(tmem_base, 512);
-}
 
 // ------------------------------------------------------------------------------------------------------
 // intra-chunk causal term, one CTA per (chunk, batch*head):  O'_c += tril(f(Q_c K_c^T)) [V_c | 1]
@@ -631,10 +336,7 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   P.c0 = pb->a0;
   P.c1 = pb->a1 * pb->inv_temperature;
   P.c2 = pb->a2 * pb->inv_temperature * pb->inv_temperature;
-  static const bool use_v1 = getenv("FASTMAX_TC_V1") != nullptr;  // development switch: the shared-memory-operand scan
-  e = cudaFuncSetAttribute(tc::scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(tc::s2::scan_apply_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s2::SMEM_BYTES);
+  e = cudaFuncSetAttribute(tc::s2::scan_apply_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s2::SMEM_BYTES);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(tc::intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::I_SMEM_BYTES);
   if (e != cudaSuccess) return report_cuda_error(e);
@@ -646,12 +348,8 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   if (e != cudaSuccess) return report_cuda_error(e);
   {
     LaunchScope ls(KK_TC_FWD, st);
-    if (use_v1)
-      tc::scan_fwd_kernel<<<dim3(5, 1, bh), tc::NTHREADS, tc::SMEM_BYTES, st>>>(tmq, tmk, tmv, P);
-    else {
-      tc::s2::ApplyParams A{oacc, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, 0, P.nchunks, P.c0, P.c1, P.c2};
-      tc::s2::scan_apply_kernel<false><<<dim3(5, 1, bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, st>>>(tmq, tmkt, tmv, A);
-    }
+    tc::s2::ApplyParams A{oacc, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, 0, P.nchunks, P.c0, P.c1, P.c2};
+    tc::s2::scan_apply_kernel<false><<<dim3(5, 1, bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, st>>>(tmq, tmkt, tmv, A);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
@@ -721,8 +419,17 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   {
     const long long nrows = (long long)bh * pb->nq;
     const int threads = 256;
-    const unsigned blocks = (unsigned)((nrows * 32 + threads - 1) / threads);
+    bool vec = true;  // 128-bit path: bases and strides of dO and o are multiples of 8 elements
+    for (const fastmax_tensor* t : {&a->o, &a->d_out})
+      if (((uintptr_t)t->ptr & 15) || (t->stride_b & 7) || (t->stride_h & 7) || (t->stride_n & 7)) vec = false;
+    const unsigned blocks = (unsigned)((nrows * (vec ? 8 : 32) + threads - 1) / threads);
     LaunchScope ls(KK_PROLOGUE, st);
+    if (vec)
+      tc::bwd_prologue_bf16_vec_kernel<<<blocks, threads, 0, st>>>(View{a->d_out.ptr, a->d_out.stride_b, a->d_out.stride_h, a->d_out.stride_n},
+                                                                   View{a->o.ptr, a->o.stride_b, a->o.stride_h, a->o.stride_n},
+                                                                   View{a->g.ptr, a->g.stride_b, a->g.stride_h, a->g.stride_n}, dop,
+                                                                   pb->nq, pb->heads, nrows);
+    else
     tc::bwd_prologue_bf16_kernel<<<blocks, threads, 0, st>>>(View{a->d_out.ptr, a->d_out.stride_b, a->d_out.stride_h, a->d_out.stride_n},
                                                              View{a->o.ptr, a->o.stride_b, a->o.stride_h, a->o.stride_n},
                                                              View{a->g.ptr, a->g.stride_b, a->g.stride_h, a->g.stride_n}, dop,
@@ -732,23 +439,19 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   if (e == cudaSuccess) e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, pb->nk - pb->nq, qt, st);
   if (e == cudaSuccess) e = launch_transpose(a->k, pb->batch, pb->heads, pb->nk, 0, kt, st);
   if (e != cudaSuccess) return report_cuda_error(e);
-  static const bool env_v1 = getenv("FASTMAX_TC_V1") != nullptr;  // development switch: the shared-memory-operand scans
   // The chain-rule scans rebalance registers between their warp groups with setmaxnreg; that only terminates if
-  // the CTA was launched with the register count the budget in tc_scan3.cuh assumes.
+  // the CTA was launched with the register count the budget in tc_scan3.cuh assumes.  Otherwise the CUDA-core
+  // engine takes the call.
   static const bool chain_ok = [] {
     cudaFuncAttributes f0{}, f1{};
     return cudaFuncGetAttributes(&f0, tc::s3::scan_chain_kernel<false>) == cudaSuccess &&
            cudaFuncGetAttributes(&f1, tc::s3::scan_chain_kernel<true>) == cudaSuccess &&
            f0.numRegs >= tc::s3::REG_LAUNCH && f1.numRegs >= tc::s3::REG_LAUNCH;
   }();
-  const bool use_v1 = env_v1 || !chain_ok;
+  if (!chain_ok) return FASTMAX_TC_NOT_HANDLED;
   const float c0 = pb->a0, c1 = pb->a1 * pb->inv_temperature, c2 = pb->a2 * pb->inv_temperature * pb->inv_temperature;
   const int nch = (pb->nk + tc::CH - 1) / tc::CH;
-  e = cudaFuncSetAttribute(tc::scan_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::BW_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(tc::scan_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::BW_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(tc::s2::scan_apply_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s2::SMEM_BYTES);
+  e = cudaFuncSetAttribute(tc::s2::scan_apply_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s2::SMEM_BYTES);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(tc::s3::scan_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s3::SMEM_BYTES);
   if (e == cudaSuccess)
@@ -765,28 +468,18 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   if (e != cudaSuccess) return report_cuda_error(e);
   {
     LaunchScope ls(KK_TC_BWD_Q, st);
-    if (use_v1) {
-      tc::BwdParams P{dqa, nullptr, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, nch, c0, c1, c2};
-      tc::scan_bwd_kernel<false><<<dim3(5, 1, bh), tc::BW_THREADS, tc::BW_SMEM_BYTES, st>>>(tmq, tmk, tmv, tmdo, P);
-    } else {
-      tc::s3::ChainParams C{dqa, View{a->q.ptr, a->q.stride_b, a->q.stride_h, a->q.stride_n}, pb->heads, pb->nq, pb->nk,
-                            pb->nk - pb->nq, pb->nk - pb->nq, nch, c1, c2};
-      tc::s3::scan_chain_kernel<false><<<dim3(5, 1, bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, st>>>(tmkt, tmv, tmdo, C);
-    }
+    tc::s3::ChainParams C{dqa, View{a->q.ptr, a->q.stride_b, a->q.stride_h, a->q.stride_n}, pb->heads, pb->nq, pb->nk,
+                          pb->nk - pb->nq, pb->nk - pb->nq, nch, c1, c2};
+    tc::s3::scan_chain_kernel<false><<<dim3(5, 1, bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, st>>>(tmkt, tmv, tmdo, C);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
   {
-    // dk: the reverse scan with the chain rule (its dV part is off: dv_acc = nullptr); dv: the apply + update scan
+    // dk: the reverse chain-rule scan; dv: the reverse apply + update scan
     LaunchScope ls(KK_TC_BWD_KV, st);
-    if (use_v1) {
-      tc::BwdParams P{dka, nullptr, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, nch, c0, c1, c2};
-      tc::scan_bwd_kernel<true><<<dim3(5, 1, bh), tc::BW_THREADS, tc::BW_SMEM_BYTES, st>>>(tmq, tmk, tmv, tmdo, P);
-    } else {
-      tc::s3::ChainParams C{dka, View{a->k.ptr, a->k.stride_b, a->k.stride_h, a->k.stride_n}, pb->heads, pb->nk, pb->nk, 0,
-                            pb->nk - pb->nq, nch, c1, c2};
-      tc::s3::scan_chain_kernel<true><<<dim3(5, 1, bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, st>>>(tmqt, tmv, tmdo, C);
-    }
+    tc::s3::ChainParams C{dka, View{a->k.ptr, a->k.stride_b, a->k.stride_h, a->k.stride_n}, pb->heads, pb->nk, pb->nk, 0,
+                          pb->nk - pb->nq, nch, c1, c2};
+    tc::s3::scan_chain_kernel<true><<<dim3(5, 1, bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, st>>>(tmqt, tmv, tmdo, C);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
@@ -808,16 +501,6 @@ extern "C" int fastmax_debug_timeline_roles(long long* out, int* counts) {
   cudaMemcpyFromSymbol(out, g_tc_timeline, sizeof(long long) * 8192);
   cudaMemcpyFromSymbol(counts, g_tc_timeline_cnt, sizeof(int) * 8);
   return 0;
-}
-extern "C" int fastmax_debug_timeline(long long* out, int n) {
-  int cnt = 0;
-  cudaMemcpyFromSymbol(&cnt, g_tc_timeline_n, sizeof(int));
-  if (cnt > 8190) cnt = 8190;
-  if (cnt > n) cnt = n;
-  cudaMemcpyFromSymbol(out, g_tc_timeline, sizeof(long long) * cnt);
-  int zero = 0;
-  cudaMemcpyToSymbol(g_tc_timeline_n, &zero, sizeof(int));
-  return cnt;
 }
 #endif
 
