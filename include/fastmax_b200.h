@@ -67,7 +67,11 @@ typedef struct {
 } fastmax_problem;
 
 enum {
-  FASTMAX_FLAG_NO_TENSOR_CORES = 1 /* force the CUDA-core kernels even where a tcgen05 kernel exists */
+  FASTMAX_FLAG_NO_TENSOR_CORES = 1, /* force the CUDA-core kernels even where a tcgen05 kernel exists */
+  FASTMAX_FLAG_SINGLE_STREAM = 2    /* keep every launch on the caller's stream.  By default the tensor-core path runs  */
+                                    /* its independent scans side by side on up to three internal streams (created once */
+                                    /* per device on first use, forked from and joined back into the caller's stream    */
+                                    /* with events), which fills the partly empty last wave of each scan.               */
 };
 
 /* Moment state of one (batch, head): float32 [fastmax_state_rows][fastmax_state_ld], row-major, heads

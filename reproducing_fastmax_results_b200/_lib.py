@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_PKG, "libfastmax_b200.so")
 
 FASTMAX_F32, FASTMAX_BF16 = 0, 1
 FLAG_NO_TENSOR_CORES = 1
+FLAG_SINGLE_STREAM = 2
 
 EXPORTED_SYMBOLS = [
     "fastmax_state_rows", "fastmax_state_ld", "fastmax_state_bytes",

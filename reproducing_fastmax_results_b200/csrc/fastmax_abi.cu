@@ -26,6 +26,8 @@ static std::mutex g_prof_mu;
 static std::vector<ProfRec> g_prof_recs;
 static thread_local cudaEvent_t g_prof_open = nullptr;
 
+bool profiling_on() { return g_prof_on.load(std::memory_order_relaxed) != 0; }
+
 void launch_begin(int kind, cudaStream_t st) {
   (void)kind;
   if (!g_prof_on.load(std::memory_order_relaxed)) return;

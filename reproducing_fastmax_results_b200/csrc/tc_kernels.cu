@@ -13,6 +13,8 @@
 #include <cuda_bf16.h>
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "launchers.cuh"
 #include "tc_launchers.cuh"
@@ -294,6 +296,55 @@ static cudaError_t launch_transpose(const fastmax_tensor& x, int batch, int head
   return cudaGetLastError();
 }
 
+// Side streams for kernels of one call that are independent of each other (each scan fills 4.3 waves of the 148
+// SMs; side by side their last waves overlap).  Created once per device, on first use; forked from the caller's
+// stream with an event and joined back into it, so the call as a whole is still ordered on the caller's stream.
+struct SideStreams {
+  cudaStream_t s[3] = {nullptr, nullptr, nullptr};
+  cudaEvent_t fork = nullptr, join[3] = {nullptr, nullptr, nullptr};
+  bool ok = false;
+};
+static SideStreams* side_streams() {
+  static std::mutex mu;
+  static SideStreams pool[64];
+  static bool tried[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  SideStreams& p = pool[dev];
+  if (!tried[dev]) {
+    tried[dev] = true;
+    bool good = cudaEventCreateWithFlags(&p.fork, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < 3 && good; ++i)
+      good = cudaStreamCreateWithFlags(&p.s[i], cudaStreamNonBlocking) == cudaSuccess &&
+             cudaEventCreateWithFlags(&p.join[i], cudaEventDisableTiming) == cudaSuccess;
+    p.ok = good;
+  }
+  return p.ok ? &p : nullptr;
+}
+// Streams for `n` independent kernels: out[0] is the caller's stream; out[1..] are side streams that wait for
+// everything enqueued on the caller's stream so far (or the caller's stream itself when side streams are off).
+static SideStreams* fork_streams(const fastmax_problem* pb, cudaStream_t st, int n, cudaStream_t* out) {
+  for (int i = 0; i < n; ++i) out[i] = st;
+  if ((pb->flags & FASTMAX_FLAG_SINGLE_STREAM) || profiling_on()) return nullptr;
+  SideStreams* p = side_streams();
+  if (!p || cudaEventRecord(p->fork, st) != cudaSuccess) return nullptr;
+  for (int i = 1; i < n; ++i) {
+    if (cudaStreamWaitEvent(p->s[i - 1], p->fork, 0) != cudaSuccess) return nullptr;
+    out[i] = p->s[i - 1];
+  }
+  return p;
+}
+static cudaError_t join_streams(SideStreams* p, cudaStream_t st, int n) {
+  if (!p) return cudaSuccess;
+  for (int i = 1; i < n; ++i) {
+    cudaError_t e = cudaEventRecord(p->join[i - 1], p->s[i - 1]);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(st, p->join[i - 1], 0);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
 static bool tc_forward_supported(const fastmax_problem* pb, const fastmax_forward_args* a) {
   if (pb->flags & FASTMAX_FLAG_NO_TENSOR_CORES) return false;
   if (pb->dtype != FASTMAX_BF16 || pb->d != 64 || pb->order != 2 || !pb->causal) return false;
@@ -340,18 +391,22 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(tc::intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::I_SMEM_BYTES);
   if (e != cudaSuccess) return report_cuda_error(e);
+  // the scan and the intra-chunk kernel both ADD into the O' accumulator: independent, side by side
+  cudaStream_t ss[2];
+  SideStreams* side = fork_streams(pb, st, 2, ss);
   {
-    LaunchScope ls(KK_TC_INTRA_FWD, st);
-    tc::intra_fwd_kernel<<<dim3(P.nchunks, 1, bh), tc::I_THREADS, tc::I_SMEM_BYTES, st>>>(tmq, tmk, tmv, P);
+    LaunchScope ls(KK_TC_FWD, ss[0]);
+    tc::s2::ApplyParams A{oacc, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, 0, P.nchunks, P.c0, P.c1, P.c2};
+    tc::s2::scan_apply_kernel<false><<<dim3(5, 1, bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmq, tmkt, tmv, A);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
   {
-    LaunchScope ls(KK_TC_FWD, st);
-    tc::s2::ApplyParams A{oacc, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, 0, P.nchunks, P.c0, P.c1, P.c2};
-    tc::s2::scan_apply_kernel<false><<<dim3(5, 1, bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, st>>>(tmq, tmkt, tmv, A);
+    LaunchScope ls(KK_TC_INTRA_FWD, ss[1]);
+    tc::intra_fwd_kernel<<<dim3(P.nchunks, 1, bh), tc::I_THREADS, tc::I_SMEM_BYTES, ss[1]>>>(tmq, tmk, tmv, P);
   }
   e = cudaGetLastError();
+  if (e == cudaSuccess) e = join_streams(side, st, 2);
   if (e != cudaSuccess) return report_cuda_error(e);
   return launch_finalize_fwd(pb, a, oacc, st);
 }
@@ -459,36 +514,41 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(tc::intra_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::IB_SMEM_BYTES);
   if (e != cudaSuccess) return report_cuda_error(e);
+  // Four independent kernels (they ADD into different or the same accumulators with reduce operations): the three
+  // scans go side by side, the intra-chunk kernel follows the dv scan on the caller's stream.
+  cudaStream_t ss[3];
+  SideStreams* side = fork_streams(pb, st, 3, ss);
   {
-    tc::IntraBwdParams I{dqa, dka, dva, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, c0, c1, c2};
-    LaunchScope ls(KK_TC_INTRA_BWD, st);
-    tc::intra_bwd_kernel<<<dim3(nch, 1, bh), tc::IB_THREADS, tc::IB_SMEM_BYTES, st>>>(tmq, tmk, tmv, tmdo, I);
-  }
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return report_cuda_error(e);
-  {
-    LaunchScope ls(KK_TC_BWD_Q, st);
+    LaunchScope ls(KK_TC_BWD_Q, ss[1]);
     tc::s3::ChainParams C{dqa, View{a->q.ptr, a->q.stride_b, a->q.stride_h, a->q.stride_n}, pb->heads, pb->nq, pb->nk,
                           pb->nk - pb->nq, pb->nk - pb->nq, nch, c1, c2};
-    tc::s3::scan_chain_kernel<false><<<dim3(5, 1, bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, st>>>(tmkt, tmv, tmdo, C);
+    tc::s3::scan_chain_kernel<false><<<dim3(5, 1, bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, ss[1]>>>(tmkt, tmv, tmdo, C);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
   {
     // dk: the reverse chain-rule scan; dv: the reverse apply + update scan
-    LaunchScope ls(KK_TC_BWD_KV, st);
+    LaunchScope ls(KK_TC_BWD_KV, ss[2]);
     tc::s3::ChainParams C{dka, View{a->k.ptr, a->k.stride_b, a->k.stride_h, a->k.stride_n}, pb->heads, pb->nk, pb->nk, 0,
                           pb->nk - pb->nq, nch, c1, c2};
-    tc::s3::scan_chain_kernel<true><<<dim3(5, 1, bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, st>>>(tmqt, tmv, tmdo, C);
+    tc::s3::scan_chain_kernel<true><<<dim3(5, 1, bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, ss[2]>>>(tmqt, tmv, tmdo, C);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
   {
     tc::s2::ApplyParams A{dva, pb->heads, pb->nk, pb->nk, 0, pb->nk - pb->nq, nch, c0, c1, c2};
-    LaunchScope ls(KK_TC_BWD_DV, st);
-    tc::s2::scan_apply_kernel<true><<<dim3(5, 1, bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, st>>>(tmk, tmqt, tmdo, A);
+    LaunchScope ls(KK_TC_BWD_DV, ss[0]);
+    tc::s2::scan_apply_kernel<true><<<dim3(5, 1, bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmk, tmqt, tmdo, A);
   }
   e = cudaGetLastError();
+  if (e != cudaSuccess) return report_cuda_error(e);
+  {
+    tc::IntraBwdParams I{dqa, dka, dva, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, c0, c1, c2};
+    LaunchScope ls(KK_TC_INTRA_BWD, ss[0]);
+    tc::intra_bwd_kernel<<<dim3(nch, 1, bh), tc::IB_THREADS, tc::IB_SMEM_BYTES, ss[0]>>>(tmq, tmk, tmv, tmdo, I);
+  }
+  e = cudaGetLastError();
+  if (e == cudaSuccess) e = join_streams(side, st, 3);
   if (e != cudaSuccess) return report_cuda_error(e);
   int rc = launch_cast_out(pb, dqa, pb->nq, &a->dq, st, tc::ACC_LD);
   if (rc == FASTMAX_OK) rc = launch_cast_out(pb, dka, pb->nk, &a->dk, st, tc::ACC_LD);
