@@ -52,8 +52,11 @@ int32_t fastmax_forward_static_scratch(const fastmax_problem* pb, const fastmax_
   const int rc = scratch_for_current_device(&scratch);
   if (rc != FASTMAX_OK) return rc;
   // The launch sequence zeroes the accumulators it sums into and overwrites the rest, so what the previous
-  // call left in the array does not matter.
-  return fastmax_forward(pb, args, scratch, kScratchBytes, cuda_stream);
+  // call left in the array does not matter.  Everything stays on the caller's stream: this entry point creates
+  // nothing, not even the internal side streams the ordinary call may set up on its first use.
+  fastmax_problem one = *pb;
+  one.flags |= FASTMAX_FLAG_SINGLE_STREAM;
+  return fastmax_forward(&one, args, scratch, kScratchBytes, cuda_stream);
 }
 
 }  // extern "C"

@@ -15,6 +15,7 @@ constexpr int IB_THREADS = 256;
 constexpr int IB_OFF_Q = 0, IB_OFF_K = REGION, IB_OFF_P = 2 * REGION, IB_OFF_D = 2 * REGION + TILE,
               IB_OFF_VP = 2 * REGION + 2 * TILE, IB_OFF_DO = IB_OFF_VP + 10 * BLK, IB_OFF_BAR = IB_OFF_DO + 10 * BLK;
 constexpr int IB_SMEM_BYTES = IB_OFF_BAR + 64 + 1024;
+static_assert(3 * CH * ACC_LD * 4 <= IB_OFF_BAR, "the three output staging tiles reuse the operand tiles");
 
 struct IntraBwdParams {
   float *dq_acc, *dk_acc, *dv_acc;
@@ -142,25 +143,41 @@ intra_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant_
     ok = (__syncthreads_or(ok ? 0 : 1) == 0);
   }
   if (ok) {
+    // dq_c, dk_c, dv_c of this chunk -> three staging tiles of ACC_LD-float rows (the operand tiles are dead by
+    // now) -> three bulk reduce-adds into the accumulators
     tc_fence_after_sync();
-    const long long ql = (long long)pos0 + l - P.off;
-    const long long kpos = (long long)pos0 + l;
-    float* dsts[3] = {P.dq_acc + ((long long)head * P.nq + ql) * ACC_LD + 32 * h, P.dk_acc + ((long long)head * P.nk + kpos) * ACC_LD + 32 * h,
-                      P.dv_acc + ((long long)head * P.nk + kpos) * ACC_LD + 32 * h};
-    const bool valid[3] = {ql >= 0 && ql < P.nq, kpos < P.nk, kpos < P.nk};
+    float* stage = reinterpret_cast<float*>(sm);
     const uint32_t cols[3] = {COL_DQ, COL_DK, COL_DVV};
 #pragma unroll
     for (int x = 0; x < 3; ++x) {
       uint32_t r[32];
       tmem_ld32(lane_addr + cols[x] + 32u * h, r);
       tmem_ld_wait();
-      if (valid[x]) {
+      float4* rowp = reinterpret_cast<float4*>(stage + (x * CH + l) * ACC_LD + 32 * h);
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          atomicAdd(reinterpret_cast<float4*>(dsts[x] + 4 * j),
-                    make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                                __uint_as_float(r[4 * j + 3])));
+      for (int j = 0; j < 8; ++j)
+        rowp[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                              __uint_as_float(r[4 * j + 3]));
+      if (h == 0) reinterpret_cast<float4*>(stage + (x * CH + l) * ACC_LD + 64)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      // valid row ranges: dq rows are query rows (chunk position - off), dk / dv rows are key positions
+      const long long q0 = (long long)pos0 - P.off;
+      const int qa = q0 < 0 ? (int)(-q0 < CH ? -q0 : CH) : 0;
+      const long long qlim = (long long)P.nq - q0;
+      const int qb = qlim < CH ? (qlim < 0 ? 0 : (int)qlim) : CH;
+      const long long klim = (long long)P.nk - pos0;
+      const int kb = klim < CH ? (klim < 0 ? 0 : (int)klim) : CH;
+      if (qb > qa)
+        bulk_reduce_add_f32(P.dq_acc + ((long long)head * P.nq + q0 + qa) * ACC_LD, stage + qa * ACC_LD, (uint32_t)(qb - qa) * (uint32_t)(ACC_LD * 4));
+      if (kb > 0) {
+        bulk_reduce_add_f32(P.dk_acc + ((long long)head * P.nk + pos0) * ACC_LD, stage + CH * ACC_LD, (uint32_t)kb * (uint32_t)(ACC_LD * 4));
+        bulk_reduce_add_f32(P.dv_acc + ((long long)head * P.nk + pos0) * ACC_LD, stage + 2 * CH * ACC_LD, (uint32_t)kb * (uint32_t)(ACC_LD * 4));
       }
+      bulk_commit_group();
+      bulk_wait_read_all();   // the staging rows stay valid until the copy engine has read them
     }
   } else if (tid == 0) {
     atomicExch(&g_tc_status, 60);

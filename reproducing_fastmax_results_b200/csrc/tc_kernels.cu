@@ -95,6 +95,7 @@ constexpr int I_OFF_Q = 0, I_OFF_K = REGION, I_OFF_VP = 2 * REGION, I_OFF_P = 2 
 constexpr int I_OFF_BAR = I_OFF_P + TILE;
 constexpr int I_SMEM_BYTES = I_OFF_BAR + 64 + 1024;
 static_assert(I_OFF_P % 1024 == 0, "operand tiles with the 128-byte swizzle need 1024-byte alignment");
+static_assert(CH * 68 * 4 <= I_OFF_BAR, "the output staging rows reuse the operand tiles");
 
 __global__ void __launch_bounds__(I_THREADS, 2)
 intra_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
@@ -194,25 +195,35 @@ intra_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant_
     ok = (__syncthreads_or(ok ? 0 : 1) == 0);
   }
   if (ok) {
+    // O'_c of this chunk -> staging rows (68 floats; the operand tiles are dead by now) -> one bulk reduce-add
     tc_fence_after_sync();
-    const long long ql = (long long)pos0 + l - P.off;
-    const bool valid = (ql >= 0 && ql < P.nq);
-    float* dst = P.oacc + ((long long)head * P.nq + ql) * 68 + 32 * h;
+    float* stage = reinterpret_cast<float*>(sm);
+    float4* rowp = reinterpret_cast<float4*>(stage + l * 68 + 32 * h);
     uint32_t r[32];
     tmem_ld32(lane_addr + 128u + 32u * h, r);
     tmem_ld_wait();
-    if (valid) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        atomicAdd(reinterpret_cast<float4*>(dst + 4 * j),
-                  make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                              __uint_as_float(r[4 * j + 3])));
-    }
+    for (int j = 0; j < 8; ++j)
+      rowp[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                            __uint_as_float(r[4 * j + 3]));
     if (h == 0) {
       uint32_t r8[8];
       tmem_ld8(lane_addr + 128u + 64u, r8);
       tmem_ld_wait();
-      if (valid) atomicAdd(dst + 64, __uint_as_float(r8[0]));
+      reinterpret_cast<float4*>(stage + l * 68 + 64)[0] = make_float4(__uint_as_float(r8[0]), 0.f, 0.f, 0.f);
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      const long long q0 = (long long)pos0 - P.off;  // query row of staging row 0
+      const int r0 = q0 < 0 ? (int)(-q0 < CH ? -q0 : CH) : 0;
+      const long long lim = (long long)P.nq - q0;
+      const int r1 = lim < CH ? (lim < 0 ? 0 : (int)lim) : CH;
+      if (r1 > r0) {
+        bulk_reduce_add_f32(P.oacc + ((long long)head * P.nq + q0 + r0) * 68, stage + r0 * 68, (uint32_t)(r1 - r0) * 272u);
+        bulk_commit_group();
+        bulk_wait_read_all();   // the staging rows stay valid until the copy engine has read them
+      }
     }
   } else if (tid == 0) {
     atomicExch(&g_tc_status, 50);

@@ -544,10 +544,12 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
 }
 
 // x (batch, head, token, 64) bf16, any strides -> xt [batch*head][64][ntp]: column p of xt holds token p - shift of x
-// (zero where there is none; ntp is a multiple of 64).  One block per (64-column group, batch*head).
+// (zero where there is none; ntp is a multiple of 64).  One block per (64-column group, batch*head).  The tile goes
+// through shared memory as 32-bit words (two dims each) with a row pitch of 33 words, so both the row-wise stores
+// and the column-wise loads spread over the banks.
 __global__ void __launch_bounds__(256) transpose_tokens_kernel(View x, __nv_bfloat16* __restrict__ xt, int n, int ntp, int heads,
                                                                int shift) {
-  __shared__ __nv_bfloat16 tile[64][72];
+  __shared__ uint32_t tile[64 * 33];
   const int head = blockIdx.y, t0 = blockIdx.x * 64;
   const int b = head / heads, h = head - b * heads;
   const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(x.ptr) + (long long)b * x.sb + (long long)h * x.sh;
@@ -556,17 +558,23 @@ __global__ void __launch_bounds__(256) transpose_tokens_kernel(View x, __nv_bflo
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     const int tok = t0 + r - shift;
     if (tok >= 0 && tok < n) v = *reinterpret_cast<const uint4*>(src + (long long)tok * x.sn + cv * 8);
-    *reinterpret_cast<uint4*>(&tile[r][cv * 8]) = v;
+    uint32_t* dstw = &tile[r * 33 + cv * 4];
+    dstw[0] = v.x; dstw[1] = v.y; dstw[2] = v.z; dstw[3] = v.w;
   }
   __syncthreads();
-  __nv_bfloat16* dst = xt + ((long long)head * 64) * ntp + t0;
-  for (int idx = threadIdx.x; idx < 512; idx += 256) {
-    const int d = idx >> 3, tc8 = idx & 7;
-    __align__(16) __nv_bfloat16 v[8];
+  // thread = (pair of dims dp, group of 8 tokens tg): eight words -> two output rows of eight tokens
+  const int dp = threadIdx.x >> 3, tg = threadIdx.x & 7;
+  uint32_t wv[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = tile[tc8 * 8 + e][d];
-    *reinterpret_cast<uint4*>(dst + (long long)d * ntp + tc8 * 8) = *reinterpret_cast<const uint4*>(v);
-  }
+  for (int e = 0; e < 8; ++e) wv[e] = tile[(tg * 8 + e) * 33 + dp];
+  uint4 lo, hi;   // dims 2 dp and 2 dp + 1
+  lo.x = __byte_perm(wv[0], wv[1], 0x5410); hi.x = __byte_perm(wv[0], wv[1], 0x7632);
+  lo.y = __byte_perm(wv[2], wv[3], 0x5410); hi.y = __byte_perm(wv[2], wv[3], 0x7632);
+  lo.z = __byte_perm(wv[4], wv[5], 0x5410); hi.z = __byte_perm(wv[4], wv[5], 0x7632);
+  lo.w = __byte_perm(wv[6], wv[7], 0x5410); hi.w = __byte_perm(wv[6], wv[7], 0x7632);
+  __nv_bfloat16* dst = xt + ((long long)head * 64 + 2 * dp) * ntp + t0 + tg * 8;
+  *reinterpret_cast<uint4*>(dst) = lo;
+  *reinterpret_cast<uint4*>(dst + ntp) = hi;
 }
 
 }  // namespace s2
