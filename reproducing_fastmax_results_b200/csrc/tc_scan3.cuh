@@ -230,11 +230,15 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
           S3_STAMP(11);
           tc_fence_after_sync();
           const float wgt = (a == b) ? P.c2 : 2.f * P.c2;
-          float za[8], zb[8], dza[8], dzb[8];
+          // packed float32 FMAs (two per instruction): pairs run over ri
+          float za[8], zb[8], dza[8];
+          float2 dzb2[4];
           unpack8(za4, wgt, za);
           unpack8(zb4, wgt, zb);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) { dza[j] = 0.f; dzb[j] = 0.f; }
+          for (int j = 0; j < 8; ++j) dza[j] = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dzb2[j] = make_float2(0.f, 0.f);
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
             uint32_t r[32];
@@ -247,14 +251,20 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
             }
 #pragma unroll
             for (int mi = 0; mi < 4; ++mi) {
+              float2 s2v = make_float2(0.f, 0.f);
+              const float2 zam = make_float2(za[4 * hf + mi], za[4 * hf + mi]);
 #pragma unroll
-              for (int ri = 0; ri < 8; ++ri) {
-                const float d = __uint_as_float(r[mi * 8 + ri]);
-                dza[4 * hf + mi] += d * zb[ri];
-                dzb[ri] += d * za[4 * hf + mi];
+              for (int rp = 0; rp < 4; ++rp) {
+                const float2 d = make_float2(__uint_as_float(r[mi * 8 + 2 * rp]), __uint_as_float(r[mi * 8 + 2 * rp + 1]));
+                s2v = __ffma2_rn(d, make_float2(zb[2 * rp], zb[2 * rp + 1]), s2v);
+                dzb2[rp] = __ffma2_rn(d, zam, dzb2[rp]);
               }
+              dza[4 * hf + mi] += s2v.x + s2v.y;
             }
           }
+          float dzb[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { dzb[2 * j] = dzb2[j].x; dzb[2 * j + 1] = dzb2[j].y; }
           // the slots are warp-uniform: selecting them with unrolled compares keeps the accumulators in registers
 #pragma unroll
           for (int sl = 0; sl < 5; ++sl) {
