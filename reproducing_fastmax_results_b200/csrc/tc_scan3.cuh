@@ -16,10 +16,11 @@
 // TMEM columns: 0..319 four state accumulators, 320..447 two dphi buffers, 448..511 two update slabs.
 // Warp roles (768 threads, six warp groups): 0-3 / 4-7 chain-rule groups (group g takes the units with sequence
 // parity g and dphi buffer g), 8-11 / 12-15 update-slab producers (set s makes half s of every tile into ring slot
-// s), 16-19 state conversion, 20 dphi issuer, 21 update issuer, 22 TMA loader, 23 drain.  The chain-rule groups raise
-// their register allowance with setmaxnreg (block accumulators and half a dphi tile in registers), the others lower
-// theirs.  The two groups add their dz blocks into a shared-memory staging tile; the drain warp adds it to the
-// float32 accumulator in global memory with one bulk reduce per chunk and zeroes it again.  Every wait is bounded (abort flag + error code).
+// s), 16-19 state conversion, 20 and 23 dphi issuers (one per chain-rule group), 21 update issuer, 22 TMA loader and
+// dz drain.  The chain-rule groups raise their register allowance with setmaxnreg (block accumulators and half a
+// dphi tile in registers), the others lower theirs.  The two groups add their dz blocks into a shared-memory
+// staging tile; the loader warp adds it to the float32 accumulator in global memory with one bulk reduce per chunk
+// and zeroes it again.  Every wait is bounded (abort flag + error code).
 #pragma once
 
 namespace s3 {
@@ -31,7 +32,7 @@ using s2::KT_BOX;
 using s2::KT_BUF;
 
 constexpr int THREADS = 768;
-constexpr int W_PROD = 8, W_CONS = 16, W_DPHI = 20, W_UPD = 21, W_TMA = 22, W_DRAIN = 23;
+constexpr int W_PROD = 8, W_CONS = 16, W_DPHI = 20, W_UPD = 21, W_TMA = 22, W_DPHI2 = 23;
 // setmaxnreg moves registers inside the pool the CTA was LAUNCHED with (80 per thread x 768 threads, i.e. 6 x 80 = 480 per
 // lane slot): an `inc` that the pool cannot satisfy blocks forever, so the four allowances below must add up to <= 480.
 constexpr int REG_LAUNCH = 80;   // what ptxas gives a 768-thread kernel; the host checks it (cudaFuncGetAttributes) before launching
@@ -132,11 +133,11 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[B_FULL + i], 4);     mbar_init(&bars[B_EMPTY + i], 1);
       mbar_init(&bars[B_XT_READY + i], 1); mbar_init(&bars[B_XT_FREE + i], 8);
-      mbar_init(&bars[B_VP_READY + i], 1); mbar_init(&bars[B_VP_FREE + i], 1);
-      mbar_init(&bars[B_DO_READY + i], 1); mbar_init(&bars[B_DO_FREE + i], 1);
+      mbar_init(&bars[B_VP_READY + i], 1); mbar_init(&bars[B_VP_FREE + i], DK ? 2 : 1);   // G: one commit per dphi issuer
+      mbar_init(&bars[B_DO_READY + i], 1); mbar_init(&bars[B_DO_FREE + i], DK ? 1 : 2);
       mbar_init(&bars[B_DPHI_DONE + i], 1); mbar_init(&bars[B_DPHI_FREE + i], 4);
     }
-    for (int i = 0; i < 4; ++i) { mbar_init(&bars[B_SB_READY + i], 4); mbar_init(&bars[B_S_DONE + i], 1); mbar_init(&bars[B_A_DONE + i], 1); }
+    for (int i = 0; i < 4; ++i) { mbar_init(&bars[B_SB_READY + i], 4); mbar_init(&bars[B_S_DONE + i], 1); mbar_init(&bars[B_A_DONE + i], 2); }
     mbar_init(&bars[B_STG_FREE], 1);
     mbar_init(&bars[B_STG_HALF], 4);   // group 0's warps
     mbar_init(&bars[B_STG_FULL], 4);   // group 1's warps
@@ -196,6 +197,25 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
         }
       }
     }
+    // this group's pair units of a chunk (the same in every chunk), 16 bits each: a | b << 4 | slot(a) << 8 | slot(b) << 12
+    uint64_t my_units = 0;
+    int n_mine = 0;
+    bool lin_mine = false;   // the group also owns the linear tile's unit (the last unit of the chunk): added at the drain
+    {
+      int mm = 0;
+      for (int t = 0; t < ntl; ++t) {
+        const bool lin = (tile0 + t == NTILES - 1);
+        const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
+        for (int u = 0; u < (lin ? 1 : 2); ++u, ++mm) {
+          if ((mm & 1) != grp) continue;
+          if (lin) { lin_mine = true; continue; }
+          const uint32_t a = (u ? (pr >> 8) : pr) & 15u, b = (u ? (pr >> 12) : (pr >> 4)) & 15u;
+          const uint32_t d16 = a | (b << 4) | (((slot_of >> (4 * a)) & 15u) << 8) | (((slot_of >> (4 * b)) & 15u) << 12);
+          my_units |= (uint64_t)d16 << (16 * n_mine);
+          ++n_mine;
+        }
+      }
+    }
     float acc[5][8];
     uint32_t cnt = 0;     // units this group has taken = phase count of its dphi buffer
     bool ok = true;
@@ -209,17 +229,11 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
       for (int sl = 0; sl < 5; ++sl)
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[sl][j] = 0.f;
-      bool lin_mine = false;   // this group owns the linear tile's unit (the last unit of the chunk): added at the drain
-      int mu = 0;              // index of the unit within the chunk: group g takes those with mu & 1 == g
-      for (int t = 0; t < ntl && ok; ++t) {
-        const bool lin = (tile0 + t == NTILES - 1);
-        const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
-        const int nu = lin ? 1 : 2;
-        for (int u = 0; u < nu; ++u, ++mu) {
-          if ((mu & 1) != grp) continue;
-          if (lin) { lin_mine = true; continue; }
-          const int a = (int)((u ? (pr >> 8) : pr) & 15u), b = (int)((u ? (pr >> 12) : (pr >> 4)) & 15u);
-          const int sa = (int)((slot_of >> (4 * a)) & 15u), sbk = (int)((slot_of >> (4 * b)) & 15u);
+      {
+#pragma unroll 1
+        for (int iu = 0; iu < n_mine; ++iu) {
+          const uint32_t d16 = (uint32_t)(my_units >> (16 * iu)) & 0xffffu;
+          const int a = (int)(d16 & 15u), b = (int)((d16 >> 4) & 15u), sa = (int)((d16 >> 8) & 15u), sbk = (int)(d16 >> 12);
           // the z blocks of this unit, before the wait so the loads fly meanwhile
           uint4 za4 = make_uint4(0u, 0u, 0u, 0u), zb4 = make_uint4(0u, 0u, 0u, 0u);
           if (valid) { za4 = zrow[a]; zb4 = zrow[b]; }
@@ -244,6 +258,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
             uint32_t r[32];
             tmem_ld32(dphi_addr + 32u * hf, r);
             tmem_ld_wait();
+            S3_STAMP(14 + 2 * hf);
             if (hf == 1) {  // the whole unit has been read: the buffer can take the next one
               tc_fence_before_sync();
               __syncwarp();
@@ -261,6 +276,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
               }
               dza[4 * hf + mi] += s2v.x + s2v.y;
             }
+            S3_STAMP(15 + 2 * hf);
           }
           float dzb[8];
 #pragma unroll
@@ -414,15 +430,18 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     }
   } else {
     reg_dec<REG_MISC>();
-    if (w == W_DPHI) {
-      // ================= dphi issuer: D_u = G_c Sb_t[unit u]^T, five K = 16 steps over the 80 columns =================
+    if (w == W_DPHI || w == W_DPHI2) {
+      // ================= dphi issuers: D_u = G_c Sb_t[unit u]^T, five K = 16 steps over the 80 columns =================
+      // One issuer per chain-rule group / dphi buffer: warp W_DPHI takes the units with an even index in the chunk,
+      // warp W_DPHI2 the odd ones, so a group's next tile is issued while the group still works on the current one.
       constexpr uint32_t IDESC = make_idesc_bf16(128, 64, 0, 0);   // A K-major, B K-major
-      uint32_t cnt0 = 0, cnt1 = 0;   // units issued into dphi buffer 0 / 1
+      const uint32_t db = (w == W_DPHI) ? 0u : 1u;
+      uint32_t cnt = 0;   // units issued into this buffer
       bool ok = true;
       for (int ci = 0; ci < nch && ok; ++ci) {
         S3_CHUNK(ci);
         const int buf = ci & 1;
-        int mu = 0;                  // index of the unit within the chunk: buffer (= chain group) mu & 1
+        int mu = 0;       // index of the unit within the chunk
         if (!WAIT(B_G_READY + buf, (uint32_t)(ci >> 1))) { FAIL(330); break; }
         const uint32_t g_addr = smem_u32(gtile + buf * TILE9);
         const uint64_t dA = make_smem_desc(g_addr, 2048, 128, 0);                       // column blocks 2 ks, 2 ks + 1
@@ -431,11 +450,10 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
           if (!WAIT(B_SB_READY + t, (uint32_t)(ci - 1))) { FAIL(331); ok = false; break; }
           const int nu = units_of(t);
           for (int u = 0; u < nu && ok; ++u, ++mu) {
-            const uint32_t db = (uint32_t)(mu & 1);
-            const uint32_t used = db ? cnt1 : cnt0;
+            if ((uint32_t)(mu & 1) != db) continue;
             S3_STAMP(20);
-            if (used > 0 && !WAIT(B_DPHI_FREE + db, used - 1u)) { FAIL(332); ok = false; break; }
-            if (db) ++cnt1; else ++cnt0;
+            if (cnt > 0 && !WAIT(B_DPHI_FREE + db, cnt - 1u)) { FAIL(332); ok = false; break; }
+            ++cnt;
             __syncwarp();
             S3_STAMP(21);
             tc_fence_after_sync();
@@ -446,13 +464,15 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
               for (int ks = 0; ks < 4; ++ks) mma_ss(d, dA + (uint64_t)(256 * ks), b0 + (uint64_t)(256 * ks), IDESC, ks > 0 ? 1u : 0u);
               mma_ss(d, dA_last, b0 + (uint64_t)(256 * 4), IDESC, 1u);
               mma_commit(&bars[B_DPHI_DONE + db]);
-              if (u == nu - 1) mma_commit(&bars[B_A_DONE + t]);
             }
             __syncwarp();
             S3_STAMP(22);
           }
+          // this issuer's MMAs on Sb_t are all issued (possibly none): its half of the tile's "no longer read" signal
+          if (ok && elect_one()) mma_commit(&bars[B_A_DONE + t]);
+          __syncwarp();
         }
-        if (ok && elect_one()) mma_commit(&bars[B_G_FREE + buf]);   // every dphi MMA of the chunk has read G
+        if (ok && elect_one()) mma_commit(&bars[B_G_FREE + buf]);   // this issuer's dphi MMAs of the chunk have read G
         __syncwarp();
       }
       if (ok && nch > 0 && !WAIT(B_G_FREE + ((nch - 1) & 1), (uint32_t)((nch - 1) >> 1))) FAIL(333);
@@ -498,12 +518,16 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
       }
       if (ok && nch > 0 && !WAIT(B_Y_FREE + ((nch - 1) & 1), (uint32_t)((nch - 1) >> 1))) FAIL(343);
       tc_fence_after_sync();
-    } else if (w == W_DRAIN) {
-      // ================= drain: staging rows -> global accumulator (one bulk reduce-add per chunk) =================
+    } else if (w == W_TMA) {
+      // ================= TMA loader + dz drain =================
+      // Besides streaming the tiles (two chunks ahead of the compute roles) this warp adds the staged dz rows of a
+      // finished chunk to the accumulator in global memory: one bulk reduce-add, then the rows are zeroed again.
       float* obase = P.out + (long long)head * P.nz * ACC_LD;
-      for (int ci = 1; ci < nch; ++ci) {
-        const uint32_t j = (uint32_t)(ci - 1);
-        if (!WAIT(B_STG_FULL, j)) { FAIL(360); break; }
+      bool ok = true;
+      uint32_t drained = 0;   // chain chunks ci = 1 .. drained have been drained
+      auto drain_one = [&]() -> bool {
+        const int ci = (int)drained + 1;
+        if (!WAIT(B_STG_FULL, drained)) { FAIL(360); return false; }
         __syncwarp();
         if (lane == 0) {
           const long long q0 = (long long)chunk_of(ci) * CH - P.z_shift;  // output row of staging row 0
@@ -518,11 +542,9 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
         for (int i = lane; i < STG_BYTES / 16; i += 32) reinterpret_cast<uint4*>(stg)[i] = make_uint4(0u, 0u, 0u, 0u);
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[B_STG_FREE]);
-      }
-      if (lane == 0) bulk_wait_all();  // the last reduce has landed before the CTA retires
-    } else if (w == W_TMA) {
-      // ================= TMA loader =================
-      bool ok = true;
+        ++drained;
+        return true;
+      };
       for (int ci = 0; ci < nch && ok; ++ci) {
         const int pos0 = chunk_of(ci) * CH, buf = ci & 1;
         const uint32_t k = (uint32_t)(ci >> 1);
@@ -551,7 +573,11 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
           for (int i = 0; i < 9; ++i) tma_load_4d(dbuf + i * BLK, &tmdo, &bars[B_DO_READY + buf], 8 * i, pos0 - P.do_shift, h_idx, b_idx);
         }
         __syncwarp();
+        // the chunk two behind the one just loaded has left the chain-rule groups (or soon will): drain it
+        if (ci >= 3) ok = drain_one();
       }
+      while (ok && (int)drained < nch - 1) ok = drain_one();
+      if (lane == 0) bulk_wait_all();  // the last reduce has landed before the CTA retires
     }
   }
 
