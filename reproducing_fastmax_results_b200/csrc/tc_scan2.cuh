@@ -261,7 +261,27 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
       if (tile0 + t < NTILES - 1) { pair_decode(2 * (tile0 + t), 8, a0, b0); pair_decode(2 * (tile0 + t) + 1, 8, a1, b1); }
       pairs |= (uint64_t)(a0 | (b0 << 4) | (a1 << 8) | (b1 << 12)) << (16 * t);
     }
-    int rem = 0;       // (index of the current tile's first slab) mod 3
+    // This set's slabs of a chunk, as tables (4 bits per slab: tile | apply << 2 | half << 3; count in bits 28..31):
+    // one for the first chunk (two update slabs per tile) and one per value of (index of the chunk's first slab) mod 3.
+    uint32_t tab_first = 0, tabs[3] = {0u, 0u, 0u};
+    {
+      uint32_t n = 0;
+      for (int i = 0; i < 2 * ntl; ++i)
+        if (i % NSETS == set) { tab_first |= (uint32_t)((i >> 1) | ((i & 1) << 3)) << (4 * n); ++n; }
+      tab_first |= n << 28;
+      for (int base = 0; base < NSETS; ++base) {
+        n = 0;
+        for (int i = 0; i < 4 * ntl; ++i) {
+          if ((base + i) % NSETS != set) continue;
+          bool is_q; int half;
+          slab_kind(false, (i >> 2) == ntl - 1, i & 3, is_q, half);
+          tabs[base] |= (uint32_t)((i >> 2) | ((is_q ? 1 : 0) << 2) | (half << 3)) << (4 * n);
+          ++n;
+        }
+        tabs[base] |= n << 28;
+      }
+    }
+    uint32_t base = 0; // (index of the current chunk's first slab) mod 3
     uint32_t k = 0;    // slabs this set has produced = phase count of its slot
     bool ok = true;
     for (int ci = 0; ci < nch && ok; ++ci) {
@@ -270,35 +290,31 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
       if (!WAIT(B_KT_READY + buf, (uint32_t)(ci >> 1)) || !WAIT(B_Q_READY + buf, (uint32_t)(ci >> 1))) { FAIL(200); break; }
       const uint8_t* raw = rawq + buf * REGION;
       const uint8_t* xt = kt + buf * KT_BUF;
-      const int nb = ci == 0 ? 2 : 4;
-      for (int t = 0; t < ntl && ok; ++t) {
-        const bool lin = (tile0 + t == NTILES - 1);
-        const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
-        int j = set - rem;
-        if (j < 0) j += NSETS;
+      const uint32_t tab = ci == 0 ? tab_first : (base == 0 ? tabs[0] : (base == 1 ? tabs[1] : tabs[2]));
+      const int cnt = (int)(tab >> 28);
 #pragma unroll 1
-        for (; j < nb; j += NSETS, ++k) {
-          bool is_q; int half;
-          slab_kind(ci == 0, t == ntl - 1, j, is_q, half);
-          S2_STAMP(40);
-          uint32_t r[32];
-          make_slab(r, is_q, half, lin, !lin_slice, row, raw, xt, pr);
-          S2_STAMP(41);
-          if (k > 0 && !WAIT(B_EMPTY + set, k - 1)) { FAIL(201); ok = false; break; }
-          __syncwarp();
-          S2_STAMP(42);
-          tc_fence_after_sync();
-          tmem_st32(slot_addr, r);
-          tmem_st_wait();
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars[(is_q ? B_FULL_Q : B_FULL_K) + set]);
-          S2_STAMP(43);
-        }
-        rem += nb - NSETS;            // (rem + nb) mod 3 for nb = 2 or 4
-        if (rem < 0) rem += NSETS;
-        if (rem >= NSETS) rem -= NSETS;
+      for (int e = 0; e < cnt; ++e, ++k) {
+        const uint32_t d4 = (tab >> (4 * e)) & 15u;
+        const int t = (int)(d4 & 3u), half = (int)(d4 >> 3);
+        const bool is_q = (d4 & 4u) != 0;
+        const bool lin = lin_slice && t == ntl - 1;
+        const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
+        S2_STAMP(40);
+        uint32_t r[32];
+        make_slab(r, is_q, half, lin, !lin_slice, row, raw, xt, pr);
+        S2_STAMP(41);
+        if (k > 0 && !WAIT(B_EMPTY + set, k - 1)) { FAIL(201); ok = false; break; }
+        __syncwarp();
+        S2_STAMP(42);
+        tc_fence_after_sync();
+        tmem_st32(slot_addr, r);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[(is_q ? B_FULL_Q : B_FULL_K) + set]);
+        S2_STAMP(43);
       }
+      base = (base + (uint32_t)((ci == 0 ? 2 : 4) * ntl)) % NSETS;
       if (ok) {
         __syncwarp();
         if (lane == 0) {
