@@ -408,7 +408,7 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   {
     LaunchScope ls(KK_TC_FWD, ss[0]);
     tc::s2::ApplyParams A{oacc, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, 0, P.nchunks, P.c0, P.c1, P.c2};
-    tc::s2::scan_apply_kernel<false><<<dim3(5, 1, bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmq, tmkt, tmv, A);
+    tc::s2::scan_apply_kernel<false><<<dim3(5 * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmq, tmkt, tmv, A);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
@@ -533,7 +533,7 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
     LaunchScope ls(KK_TC_BWD_Q, ss[1]);
     tc::s3::ChainParams C{dqa, View{a->q.ptr, a->q.stride_b, a->q.stride_h, a->q.stride_n}, pb->heads, pb->nq, pb->nk,
                           pb->nk - pb->nq, pb->nk - pb->nq, nch, c1, c2};
-    tc::s3::scan_chain_kernel<false><<<dim3(5, 1, bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, ss[1]>>>(tmkt, tmv, tmdo, C);
+    tc::s3::scan_chain_kernel<false><<<dim3(5 * bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, ss[1]>>>(tmkt, tmv, tmdo, C);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
@@ -542,14 +542,14 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
     LaunchScope ls(KK_TC_BWD_KV, ss[2]);
     tc::s3::ChainParams C{dka, View{a->k.ptr, a->k.stride_b, a->k.stride_h, a->k.stride_n}, pb->heads, pb->nk, pb->nk, 0,
                           pb->nk - pb->nq, nch, c1, c2};
-    tc::s3::scan_chain_kernel<true><<<dim3(5, 1, bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, ss[2]>>>(tmqt, tmv, tmdo, C);
+    tc::s3::scan_chain_kernel<true><<<dim3(5 * bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, ss[2]>>>(tmqt, tmv, tmdo, C);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
   {
     tc::s2::ApplyParams A{dva, pb->heads, pb->nk, pb->nk, 0, pb->nk - pb->nq, nch, c0, c1, c2};
     LaunchScope ls(KK_TC_BWD_DV, ss[0]);
-    tc::s2::scan_apply_kernel<true><<<dim3(5, 1, bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmk, tmqt, tmdo, A);
+    tc::s2::scan_apply_kernel<true><<<dim3(5 * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmk, tmqt, tmdo, A);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);

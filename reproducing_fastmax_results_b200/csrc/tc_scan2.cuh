@@ -198,7 +198,11 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BAR + 328);
 
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
-  const int slice = blockIdx.x, head = blockIdx.z;
+  // Blocks are dispatched in index order: all four-tile slices first, the three-tile slices (0.75 of the work) last,
+  // so the partly filled last wave of the grid is made of short CTAs.  gridDim.x = 5 * batch * heads.
+  const int n_full = 4 * (int)(gridDim.x / 5);
+  const int head = (int)blockIdx.x < n_full ? (int)blockIdx.x >> 2 : (int)blockIdx.x - n_full;
+  const int slice = (int)blockIdx.x < n_full ? (int)blockIdx.x & 3 : 4;
   const int b_idx = head / P.heads, h_idx = head - b_idx * P.heads;
   const int tile0 = slice * 4;
   const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
@@ -209,7 +213,7 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
   // development aid: cheap (shared-memory) time stamps of one thread per role of CTA (0, 0), chunks 8..11
   uint2* tl_ptr = nullptr;
   int tl_n = 0, tl_c = 0;
-  if (blockIdx.x == 0 && blockIdx.z == 0 && lane == 0 && (w == W_MMA || w == 0 || w == W_MMA2 || w == W_CONS))
+  if (blockIdx.x == 0 && lane == 0 && (w == W_MMA || w == 0 || w == W_MMA2 || w == W_CONS))
     tl_ptr = reinterpret_cast<uint2*>(sm + OFF_TL) + 256 * (w == W_MMA ? 0 : (w == 0 ? 1 : (w == W_MMA2 ? 2 : 3)));
 #define S2_STAMP(tag) do { if (tl_ptr && tl_c >= 8 && tl_c < 12 && tl_n < 256) tl_ptr[tl_n++] = make_uint2((uint32_t)(tag), (uint32_t)clock()); } while (0)
 #define S2_CHUNK(c) tl_c = (c)

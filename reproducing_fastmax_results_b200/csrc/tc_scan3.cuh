@@ -107,7 +107,11 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
   constexpr int B_Y_READY = DK ? B_DO_READY : B_VP_READY, B_Y_FREE = DK ? B_DO_FREE : B_VP_FREE;
 
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
-  const int slice = blockIdx.x, head = blockIdx.z;
+  // Blocks are dispatched in index order: all four-tile slices first, the three-tile slices (0.75 of the work) last,
+  // so the partly filled last wave of the grid is made of short CTAs.  gridDim.x = 5 * batch * heads.
+  const int n_full = 4 * (int)(gridDim.x / 5);
+  const int head = (int)blockIdx.x < n_full ? (int)blockIdx.x >> 2 : (int)blockIdx.x - n_full;
+  const int slice = (int)blockIdx.x < n_full ? (int)blockIdx.x & 3 : 4;
   const int b_idx = head / P.heads, h_idx = head - b_idx * P.heads;
   const int tile0 = slice * 4;
   const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
@@ -120,7 +124,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
   int tl_n = 0, tl_c = 0;
   {
     const int role = w == 0 ? 0 : w == W_PROD ? 1 : w == W_CONS ? 2 : w == W_DPHI ? 3 : w == W_UPD ? 4 : -1;
-    if (blockIdx.x == 0 && blockIdx.z == 0 && lane == 0 && role >= 0) tl_ptr = reinterpret_cast<uint2*>(sm + OFF_TL) + 200 * role;
+    if (blockIdx.x == 0 && lane == 0 && role >= 0) tl_ptr = reinterpret_cast<uint2*>(sm + OFF_TL) + 200 * role;
   }
 #define S3_STAMP(tag) do { if (tl_ptr && tl_c >= 8 && tl_c < 12 && tl_n < 200) tl_ptr[tl_n++] = make_uint2((uint32_t)(tag), (uint32_t)clock()); } while (0)
 #define S3_CHUNK(c) tl_c = (c)
