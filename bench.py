@@ -38,8 +38,12 @@ WORKLOADS = {
     "prof_bf16_causal_p2_B4_H16_N4096_D64": (4, 16, 4096, 64, 2, True, "bf16", 1.0),
     # BASELINE config 3: one long causal sequence, cut into contiguous pieces across the ranks (strong scaling)
     "cfg3_f32_causal_p2_B1_H8_N131072_D32": (1, 8, 131072, 32, 2, True, "f32", 1.0),
+    # incremental decoding: one new token per (batch, head) per step against the carried state (N = prefix length is
+    # irrelevant to the cost; 512 head states = 330 MB, larger than L2)
+    "decode_bf16_p2_B32_H16_D64": (32, 16, 1, 64, 2, True, "bf16", 1.0),
 }
 SEQUENCE_SHARDED = {"cfg3_f32_causal_p2_B1_H8_N131072_D32"}
+DECODE = {"decode_bf16_p2_B32_H16_D64"}
 DEFAULT = "cfg2_bf16_causal_p2_B8_H16_N4096_D64"
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch from the ncu captures summarised under profiles/ (taken
 # on the prof_ workload: 64 heads x 4096 tokens); bench.py scales them by head-tokens to its own workload.
@@ -159,11 +163,12 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------------
 # CPU arm: the oracle's restatement of the reference's factorised algorithm, on the host cores
 # ----------------------------------------------------------------------------------------------------
-def cpu_sample(workload, n_sample=512, heads=1, reps=1):
+def cpu_sample(workload, n_sample=512, heads=1):
     """Times forward+backward of the factorised CPU algorithm (cumsum of per-token moments, the
-    reference's attention_mechanisms implementation) on `heads` heads of n_sample tokens with the workload's
-    D, order and mask.  Memory of that algorithm is O(N D^3) per head, which bounds the sample.
-    Returns (seconds per repetition, head-tokens per repetition, threads)."""
+    reference's attention_mechanisms implementation) on `heads` heads of n_sample tokens, one head after the
+    other, with the workload's D, order and mask.  Memory of that algorithm is O(N D^3) per head, which bounds
+    the tokens of a head; the number of heads sets how long the sample runs.
+    Returns (seconds, head-tokens processed, threads)."""
     import torch
 
     from oracle import fastmax_oracle as orc
@@ -172,16 +177,22 @@ def cpu_sample(workload, n_sample=512, heads=1, reps=1):
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(0)
-    q, k, v, do = (torch.randn(1, heads, n_sample, D, generator=g) * scale for _ in range(4))
-    if dtype == "bf16":
-        q, k, v, do = (t.bfloat16().float() for t in (q, k, v, do))
     poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / (8.0 * math.sqrt(D)), order)
-    ts = []
-    for _ in range(reps):
+    total = 0.0
+    for _ in range(heads):
+        q, k, v, do = (torch.randn(1, 1, n_sample, D, generator=g) * scale for _ in range(4))
+        if dtype == "bf16":
+            q, k, v, do = (t.bfloat16().float() for t in (q, k, v, do))
         t0 = time.perf_counter()
         orc.fastmax_factorized_fwd_bwd(q, k, v, do, causal, poly)
-        ts.append(time.perf_counter() - t0)
-    return min(ts), heads * n_sample, threads
+        total += time.perf_counter() - t0
+    return total, heads * n_sample, threads
+
+
+def cpu_sample_text(workload, n_sample, heads):
+    B, H, N, D, order, causal, dtype, scale = WORKLOADS[workload]
+    return (f"factorised {'causal' if causal else 'non-causal'} order-{order} forward+backward (torch CPU, autograd) on "
+            f"{heads} of {B * H} heads, {n_sample} of {N} tokens each, D={D}; head-tokens / H = metric tokens")
 
 
 def run_reference_arm(args):
@@ -190,26 +201,26 @@ def run_reference_arm(args):
     if rank != 0:
         return 0
     B, H, N, D, order, causal, dtype, scale = WORKLOADS[args.workload]
-    n_sample = args.cpu_tokens
+    n_sample, heads = args.cpu_tokens, args.ref_heads
     for _ in range(args.warmup):
-        cpu_sample(args.workload, n_sample)
+        cpu_sample(args.workload, n_sample, 1)
     times = []
     threads = 1
+    head_tokens = heads * n_sample
     for _ in range(args.steps):
-        t, head_tokens, threads = cpu_sample(args.workload, n_sample)
+        t, head_tokens, threads = cpu_sample(args.workload, n_sample, heads)
         times.append(t)
     sec = sum(times) / len(times)
     # metric tokens carry all H heads: one head of n_sample tokens is n_sample / H metric tokens
-    value = (n_sample / H) / sec / 1e6
+    value = (head_tokens / H) / sec / 1e6
     line = {
         "impl": "reference",
         "metric": "fastmax_fwd_bwd_mtokens_per_s", "value": value, "unit": "Mtokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "sample": f"1 head x {n_sample} tokens per step"},
-        "cpu_baseline": {"value": value, "unit": "Mtokens/s", "cores": threads, "kind": "port",
-                         "sample": f"factorised causal order-{order} forward+backward (torch CPU, autograd) on 1 of "
-                                   f"{B * H} heads, {n_sample} of {N} tokens, D={D}; scaled by 1/H to metric tokens"},
+        "config": {"workload": args.workload, "sample": f"{heads} head(s) x {n_sample} tokens per step"},
+        "cpu_baseline": {"value": value, "unit": "Mtokens/s", "cores": threads, "kind": "port", "seconds": sec,
+                         "sample": cpu_sample_text(args.workload, n_sample, heads)},
         "e2e": {"value": value, "unit": "Mtokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -299,6 +310,75 @@ def run_sequence_sharded(args, torch, dist, dev, rank, world):
 
 
 # ----------------------------------------------------------------------------------------------------
+# GPU arm, decoding workload: one fastmax_decode_step per step; every rank decodes its own batch (weak scaling)
+# ----------------------------------------------------------------------------------------------------
+def run_decode(args, torch, dist, dev, rank, world):
+    from reproducing_fastmax_results_b200 import _lib
+
+    B, H, _, D, order, causal, dtype_name, scale = WORKLOADS[args.workload]
+    dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
+    inv_temp = 1.0 / (8.0 * math.sqrt(D))
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    ntok = 16
+    q, k, v = ((torch.randn(B, H, ntok, D, device=dev, generator=gen) * scale).to(dtype) for _ in range(3))
+    state = _lib.new_state(B, H, D, order, dev)
+    out = torch.empty(B, H, D, device=dev, dtype=dtype)
+    lib = _lib.load()
+    counter = [0]
+
+    def step():
+        t = counter[0] % ntok
+        counter[0] += 1
+        _lib.decode_step(q[:, :, t], k[:, :, t], v[:, :, t], state, inv_temp, order=order, out=out)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(torch.cuda.current_device())
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.fastmax_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    launches = lib.fastmax_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.destroy_process_group()
+    ms_step = float(t.item()) / args.steps
+    if rank == 0:
+        pk = peaks()
+        state_bytes = state.numel() * 4
+        gbs = 2.0 * state_bytes / (ms_step * 1e-3) / 1e9
+        line = {
+            "metric": "fastmax_decode_mtokens_per_s", "value": world * B / (ms_step * 1e-3) / 1e6, "unit": "Mtokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": dtype_name + " tokens, f32 state", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": B, "heads": H, "head_dim": D, "order": order,
+                       "parallelism": f"batch sharding, {world} rank(s), no collective",
+                       "l2": f"the states ({state_bytes >> 20} MiB per rank) exceed the 126 MB L2; no explicit flush"},
+            "roofline": {"kernel": "decode_step", "bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / pk["hbm_gbs"], "peak_source": pk["_source"],
+                         "note": "algorithmic bytes = one read and one write of every head's state; launch gaps between "
+                                 "the back-to-back steps are inside the time", "traffic": None},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    return 0
+
+
+# ----------------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------------
 def main():
@@ -308,7 +388,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
-    ap.add_argument("--cpu-tokens", type=int, default=512, help="tokens of the bounded CPU-baseline sample")
+    ap.add_argument("--cpu-tokens", type=int, default=512, help="tokens per head of the bounded CPU-baseline sample")
+    ap.add_argument("--cpu-heads", type=int, default=24, help="heads of the CPU-baseline sample (about 10 s of CPU work)")
+    ap.add_argument("--ref-heads", type=int, default=6, help="--impl reference: heads per step (a few seconds each)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-tensor-cores", action="store_true", help="force the CUDA-core kernels")
@@ -339,6 +421,8 @@ def main():
 
     if args.workload in SEQUENCE_SHARDED:
         return run_sequence_sharded(args, torch, dist, dev, rank, world)
+    if args.workload in DECODE:
+        return run_decode(args, torch, dist, dev, rank, world)
     B, H, N, D, order, causal, dtype_name, scale = WORKLOADS[args.workload]
     dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
     inv_temp = 1.0 / (8.0 * math.sqrt(D))
@@ -459,32 +543,45 @@ def main():
             hdk.copy_(dk_.grad, non_blocking=True)
             hdv.copy_(dv_.grad, non_blocking=True)
 
-        for _ in range(max(1, min(args.warmup, 3))):
-            e2e_step()
-        barrier()
-        e2e_steps = max(3, min(args.steps, 10))
-        a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(e2e_steps):
-            e2e_step()
-        b2.record()
-        barrier()
-        tt = torch.tensor([a.elapsed_time(b2)], device=dev, dtype=torch.float64)
-        if dist is not None:
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e_ms = float(tt.item()) / e2e_steps
+        from reproducing_fastmax_results_b200.host_pipeline import HostFastmax
+
+        host_op = HostFastmax(mask=causal, temperature=temperature, p=order, device=dev)
+
+        def e2e_pipelined():
+            host_op.forward_backward(hq, hk, hv, hdo, ho, hdq, hdk, hdv)
+
+        def time_e2e(fn):
+            for _ in range(max(1, min(args.warmup, 3))):
+                fn()
+            barrier()
+            n = max(3, min(args.steps, 10))
+            a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b2.record()
+            barrier()
+            tt = torch.tensor([a.elapsed_time(b2)], device=dev, dtype=torch.float64)
+            if dist is not None:
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return float(tt.item()) / n, n
+
+        single_ms, _ = time_e2e(e2e_step)
+        e2e_ms, e2e_steps = time_e2e(e2e_pipelined)
         nbytes = q.numel() * q.element_size()
         e2e = {"value": tokens_per_step / (e2e_ms * 1e-3) / 1e6, "unit": "Mtokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "steps": e2e_steps,
-               "api": "reproducing_fastmax_results_b200.FastMax.apply + backward, pinned host q,k,v,dO in; o,dq,dk,dv out"}
+               "api": "reproducing_fastmax_results_b200.host_pipeline.HostFastmax.forward_backward: pinned host q,k,v,dO in; "
+                      "o,dq,dk,dv out to pinned host; batch slices pipelined over copy-in / compute / copy-out streams",
+               "single_call": {"value": tokens_per_step / (single_ms * 1e-3) / 1e6, "ms_per_step": single_ms,
+                               "api": "FastMax.apply + backward on the whole batch between one copy-in and one copy-out"}}
 
     cpu = None
     if rank == 0 and not args.no_cpu and world >= 1:
-        sec, head_tokens, threads = cpu_sample(args.workload, args.cpu_tokens)
-        cpu = {"value": (args.cpu_tokens / H) / sec / 1e6, "unit": "Mtokens/s", "cores": threads, "kind": "port",
-               "seconds": sec,
-               "sample": f"factorised causal order-{order} forward+backward (torch CPU, autograd) on 1 of {B * H} heads, "
-                         f"{args.cpu_tokens} of {N} tokens, D={D}; scaled by 1/H to metric tokens"}
+        cpu_sample(args.workload, args.cpu_tokens, 1)  # page the CPU kernels in
+        sec, head_tokens, threads = cpu_sample(args.workload, args.cpu_tokens, args.cpu_heads)
+        cpu = {"value": (head_tokens / H) / sec / 1e6, "unit": "Mtokens/s", "cores": threads, "kind": "port",
+               "seconds": sec, "sample": cpu_sample_text(args.workload, args.cpu_tokens, args.cpu_heads)}
 
     if rank == 0:
         line = {

@@ -138,6 +138,28 @@ size_t fastmax_backward_workspace(const fastmax_problem* pb, const fastmax_backw
 int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args* args,
                          void* workspace, size_t workspace_bytes, void* cuda_stream);
 
+/* ---- incremental decoding --------------------------------------------------------------------------
+ * One new token per (batch, head) against the carried moment state:
+ *     state += Phi(k)^T [v | 1];   o' = Phi(q) . state (polynomial weights applied here);   o = o'[:d] / o'[d]
+ * Replaces re-running the whole token window through forwardpass for every generated token, which is what the
+ * reference's generation loop does (transformer/eval.py:8-32 calls the model on tokens[:, -max_tokens:] per new
+ * token): the cost per token becomes one read and one write of the state, independent of the prefix length.
+ *   pb: nq = nk = 1; batch, heads, d, order, dtype, a0..a2 and inv_temperature as in the forward call; `causal`
+ *       is not used (the new query sees every earlier key and its own).
+ *   q, k, v, o: one token per (batch, head): stride_b and stride_h are used, stride_n is not.
+ *   g (optional, ptr may be NULL): float32, one value per (batch, head), strides in floats.
+ *   state: float32 [batch*heads][fastmax_state_rows][fastmax_state_ld], 16-byte aligned, updated IN PLACE.  Start
+ *       it from zeros, or from the state_out of a fastmax_forward call over the prompt.
+ * Needs no workspace.  One launch (clusters of eight thread blocks per head). */
+typedef struct {
+  fastmax_tensor q, k, v;
+  fastmax_tensor o;
+  fastmax_tensor g;
+  float* state;
+} fastmax_decode_args;
+
+int32_t fastmax_decode_step(const fastmax_problem* pb, const fastmax_decode_args* args, void* cuda_stream);
+
 /* ---- q/k normalisation ----------------------------------------------------------------------------
  * Replaces calc_norms / find_max / apply_norm (fastmax_cuda_forward.cu:294-338, 424-433) with the
  * normalisation the reference's oracle defines (attention_mechanisms/fastattention_einops.py:327-334):

@@ -21,9 +21,10 @@ EXPORTED_SYMBOLS = [
     "fastmax_forward_workspace", "fastmax_forward",
     "fastmax_static_scratch_bytes", "fastmax_forward_static_scratch",
     "fastmax_backward_workspace", "fastmax_backward",
+    "fastmax_decode_step",
     "fastmax_normalize_forward", "fastmax_normalize_backward",
     "fastmax_status_string", "fastmax_last_cuda_error", "fastmax_last_cuda_error_string",
-    "fastmax_version", "fastmax_launch_count", "fastmax_check_status",
+    "fastmax_version", "fastmax_launch_count", "fastmax_check_status", "fastmax_debug_wait_histogram",
     "fastmax_profile_enable", "fastmax_profile_kinds", "fastmax_profile_kind_name", "fastmax_profile_collect",
 ]
 
@@ -50,6 +51,10 @@ class BackwardArgs(C.Structure):
     _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("o", Tensor), ("g", Tensor), ("d_out", Tensor),
                 ("dq", Tensor), ("dk", Tensor), ("dv", Tensor),
                 ("state_in", C.c_void_p), ("dstate_in", C.c_void_p), ("dstate_out", C.c_void_p)]
+
+
+class DecodeArgs(C.Structure):
+    _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("o", Tensor), ("g", Tensor), ("state", C.c_void_p)]
 
 
 class FastmaxError(RuntimeError):
@@ -89,6 +94,8 @@ def load():
     lib.fastmax_backward_workspace.argtypes = [C.POINTER(Problem), C.POINTER(BackwardArgs)]
     lib.fastmax_backward.restype = C.c_int32
     lib.fastmax_backward.argtypes = [C.POINTER(Problem), C.POINTER(BackwardArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.fastmax_decode_step.restype = C.c_int32
+    lib.fastmax_decode_step.argtypes = [C.POINTER(Problem), C.POINTER(DecodeArgs), C.c_void_p]
     lib.fastmax_normalize_forward.restype = C.c_int32
     lib.fastmax_normalize_forward.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                               C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p, C.c_void_p]
@@ -102,6 +109,9 @@ def load():
     lib.fastmax_last_cuda_error_string.restype = C.c_char_p
     lib.fastmax_version.restype = C.c_char_p
     lib.fastmax_launch_count.restype = C.c_uint64
+    lib.fastmax_check_status.restype = C.c_int32
+    lib.fastmax_debug_wait_histogram.restype = C.c_int32
+    lib.fastmax_debug_wait_histogram.argtypes = [C.POINTER(C.c_int32), C.c_int32]
     lib.fastmax_profile_enable.argtypes = [C.c_int32]
     lib.fastmax_profile_kind_name.restype = C.c_char_p
     lib.fastmax_profile_kind_name.argtypes = [C.c_int32]
@@ -233,6 +243,41 @@ def backward(q, k, v, o, g, d_out, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, ord
     return dq, dk, dv, dsout
 
 
+def new_state(batch, heads, d, order=2, device="cuda"):
+    """Zero moment state in the exchange layout: float32 (batch, heads, fastmax_state_rows, fastmax_state_ld)."""
+    import torch
+
+    lib = load()
+    return torch.zeros((batch, heads, lib.fastmax_state_rows(d, order), lib.fastmax_state_ld(d)), dtype=torch.float32,
+                       device=device)
+
+
+def decode_step(q, k, v, state, inv_temp, a0=1.0, a1=1.0, a2=0.5, order=2, out=None):
+    """Calls fastmax_decode_step: q, k, v are (b, h, d) or (b, h, 1, d) CUDA tensors holding ONE new token per
+    head; `state` (from new_state() or forward(..., want_state=True)) is updated in place.  Returns (o, g) with
+    o shaped like q and g float32 (b, h)."""
+    import torch
+
+    lib = load()
+    q3, k3, v3 = (t.reshape(t.shape[0], t.shape[1], t.shape[-1]) if t.dim() == 4 else t for t in (q, k, v))
+    for t in (q3, k3, v3):
+        assert t.dim() == 3 and t.stride(2) == 1
+    assert state.dtype == torch.float32 and state.is_contiguous()
+    b, h, d = q3.shape
+    assert tuple(state.shape) == (b, h, lib.fastmax_state_rows(d, order), lib.fastmax_state_ld(d)), state.shape
+    o = torch.empty(q.shape, dtype=q.dtype, device=q.device) if out is None else out
+    o3 = o.reshape(b, h, d) if o.dim() == 4 else o
+    assert o3.data_ptr() == o.data_ptr() and o3.stride(2) == 1
+    g = torch.empty((b, h), dtype=torch.float32, device=q.device)
+    pb = Problem(b, h, 1, 1, d, order, 1, dtype_code(q), a0, a1, a2, inv_temp, 0, 0)
+    args = DecodeArgs()
+    args.q, args.k, args.v, args.o = (Tensor(t.data_ptr(), t.stride(0), t.stride(1), 0) for t in (q3, k3, v3, o3))
+    args.g = Tensor(g.data_ptr(), g.stride(0), g.stride(1), 0)
+    args.state = state.data_ptr()
+    check(lib.fastmax_decode_step(C.byref(pb), C.byref(args), _stream()), "fastmax_decode_step")
+    return o, g
+
+
 def normalize_forward(x, lim=1.0):
     import torch
 
@@ -264,6 +309,14 @@ def check_status():
 
     torch.cuda.synchronize()
     check(load().fastmax_check_status(), "fastmax_check_status")
+
+
+def wait_histogram():
+    """Returns {wait-site code modulo 256: thread blocks that gave up there first} and clears the counters."""
+    lib = load()
+    h = (C.c_int32 * 256)()
+    check(lib.fastmax_debug_wait_histogram(h, 256), "fastmax_debug_wait_histogram")
+    return {i: int(c) for i, c in enumerate(h) if c}
 
 
 def profile(enable):

@@ -27,7 +27,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",
 ]
-CU_SOURCES = ["fastmax_abi.cu", "scan_d16.cu", "scan_d32.cu", "scan_d64.cu", "tc_kernels.cu", "noalloc.cu"]
+CU_SOURCES = ["fastmax_abi.cu", "scan_d16.cu", "scan_d32.cu", "scan_d64.cu", "tc_kernels.cu", "noalloc.cu", "decode.cu"]
 
 
 def _digest(paths):

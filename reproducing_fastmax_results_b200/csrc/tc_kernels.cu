@@ -359,7 +359,7 @@ static cudaError_t join_streams(SideStreams* p, cudaStream_t st, int n) {
 static bool tc_forward_supported(const fastmax_problem* pb, const fastmax_forward_args* a) {
   if (pb->flags & FASTMAX_FLAG_NO_TENSOR_CORES) return false;
   if (pb->dtype != FASTMAX_BF16 || pb->d != 64 || pb->order != 2 || !pb->causal) return false;
-  if (!a->o.ptr || a->state_in || a->state_out) return false;
+  if (!a->o.ptr || a->state_in) return false;   // state_out alone is fine: the scan writes its final state out
   if (pb->nq <= 0 || pb->nk <= 0) return false;
   if ((long long)pb->batch * pb->heads * 5 < 64) return false;  // too few CTAs: the segmented engine does better
   return true;
@@ -407,7 +407,7 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   SideStreams* side = fork_streams(pb, st, 2, ss);
   {
     LaunchScope ls(KK_TC_FWD, ss[0]);
-    tc::s2::ApplyParams A{oacc, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, 0, P.nchunks, P.c0, P.c1, P.c2};
+    tc::s2::ApplyParams A{oacc, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, 0, P.nchunks, P.c0, P.c1, P.c2, a->state_out};
     tc::s2::scan_apply_kernel<false><<<dim3(5 * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmq, tmkt, tmv, A);
   }
   e = cudaGetLastError();

@@ -73,6 +73,7 @@ struct ApplyParams {
   int y_shift;         // Y row of chunk position p is p - y_shift (forward: 0; dv scan: nk - nq)
   int nchunks;
   float c0, c1, c2;
+  float* state_out;    // forward only, optional: moment state of all keys, float32 [BH][64 * 36 + 65][68] (exchange layout)
 };
 
 // A bounded wait gave up: count the wait site (first failure of the CTA only), raise the CTA's abort flag, set the
@@ -198,11 +199,9 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BAR + 328);
 
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
-  // Blocks are dispatched in index order: all four-tile slices first, the three-tile slices (0.75 of the work) last,
-  // so the partly filled last wave of the grid is made of short CTAs.  gridDim.x = 5 * batch * heads.
-  const int n_full = 4 * (int)(gridDim.x / 5);
-  const int head = (int)blockIdx.x < n_full ? (int)blockIdx.x >> 2 : (int)blockIdx.x - n_full;
-  const int slice = (int)blockIdx.x < n_full ? (int)blockIdx.x & 3 : 4;
+  // The five slices of a head are neighbours in the grid, so they run at about the same time and share the head's
+  // q / k / v tiles through L2.  gridDim.x = 5 * batch * heads.
+  const int head = (int)blockIdx.x / 5, slice = (int)blockIdx.x - 5 * head;
   const int b_idx = head / P.heads, h_idx = head - b_idx * P.heads;
   const int tile0 = slice * 4;
   const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
@@ -428,6 +427,42 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars[B_SB_READY + t]);
           S2_STAMP(72);
+        }
+      }
+    }
+    if (!DV && P.state_out != nullptr && ok) {
+      // The caller wants the moment state of all keys: S_t is complete once the last chunk's update has finished.
+      // Tile rows are the state's rows (two 64-feature pair units per tile, then the linear rows and the constant);
+      // the values are un-weighted sums, which is the exchange format.  Features were rounded to bf16 before the
+      // products were summed in float32.
+      constexpr int ST_ROWS = 64 * 36 + 65, ST_LD = 68;
+      float* sbase = P.state_out + (long long)head * ST_ROWS * ST_LD;
+      for (int t = 0; t < ntl; ++t) {
+        if (nch > 0 && !WAIT(B_S_DONE + t, (uint32_t)(nch - 1))) { FAIL(224); break; }
+        __syncwarp();
+        tc_fence_after_sync();
+        uint32_t ra[32], rb[32], rc[8];
+        if (nch > 0) {
+          tmem_ld32(lane_addr + 80u * t, ra);
+          tmem_ld32(lane_addr + 80u * t + 32u, rb);
+          tmem_ld8(lane_addr + 80u * t + 64u, rc);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ra[j] = rb[j] = 0u;
+          rc[0] = 0u;
+        }
+        const int srow = 128 * (tile0 + t) + l;
+        if (srow < ST_ROWS) {
+          float4* dst = reinterpret_cast<float4*>(sbase + (long long)srow * ST_LD);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            dst[j] = make_float4(__uint_as_float(ra[4 * j]), __uint_as_float(ra[4 * j + 1]), __uint_as_float(ra[4 * j + 2]),
+                                 __uint_as_float(ra[4 * j + 3]));
+            dst[8 + j] = make_float4(__uint_as_float(rb[4 * j]), __uint_as_float(rb[4 * j + 1]), __uint_as_float(rb[4 * j + 2]),
+                                     __uint_as_float(rb[4 * j + 3]));
+          }
+          dst[16] = make_float4(__uint_as_float(rc[0]), 0.f, 0.f, 0.f);
         }
       }
     }

@@ -107,11 +107,9 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
   constexpr int B_Y_READY = DK ? B_DO_READY : B_VP_READY, B_Y_FREE = DK ? B_DO_FREE : B_VP_FREE;
 
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
-  // Blocks are dispatched in index order: all four-tile slices first, the three-tile slices (0.75 of the work) last,
-  // so the partly filled last wave of the grid is made of short CTAs.  gridDim.x = 5 * batch * heads.
-  const int n_full = 4 * (int)(gridDim.x / 5);
-  const int head = (int)blockIdx.x < n_full ? (int)blockIdx.x >> 2 : (int)blockIdx.x - n_full;
-  const int slice = (int)blockIdx.x < n_full ? (int)blockIdx.x & 3 : 4;
+  // The five slices of a head are neighbours in the grid, so they run at about the same time and share the head's
+  // q / k / v tiles through L2.  gridDim.x = 5 * batch * heads.
+  const int head = (int)blockIdx.x / 5, slice = (int)blockIdx.x - 5 * head;
   const int b_idx = head / P.heads, h_idx = head - b_idx * P.heads;
   const int tile0 = slice * 4;
   const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;

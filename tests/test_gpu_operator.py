@@ -99,3 +99,29 @@ def test_fastmax_bf16_transposed_views_and_module():
     assert orc.max_norm_err(host(k.grad), dk_ref) < 2e-2
     assert orc.max_norm_err(host(v.grad), dv_ref) < 2e-2
     assert pkg.FASTMultiHeadAttention(use_custom_gradient=False)(q, k, v) == 0
+
+
+def test_host_pipeline_matches_the_single_call():
+    """HostFastmax streams batch slices from pinned host memory through the GPU; every (batch, head) is
+    independent, so the results equal one call over the whole batch (up to the order of float32 adds)."""
+    from reproducing_fastmax_results_b200 import _lib as L
+    from reproducing_fastmax_results_b200.host_pipeline import HostFastmax
+
+    B, H, N, D = 5, 16, 260, 64
+    g = torch.Generator().manual_seed(11)
+    hq, hk, hv, hdo = (torch.randn(B, H, N, D, generator=g).bfloat16().pin_memory() for _ in range(4))
+    outs = [torch.empty_like(hq).pin_memory() for _ in range(4)]
+    temperature = 2.0 * math.sqrt(D)
+    for pieces in (None, 2):
+        op = HostFastmax(mask=True, temperature=temperature, p=2, pieces=pieces)
+        for _ in range(2):   # the second call reuses the device buffers
+            for t in outs:
+                t.zero_()
+            op.forward_backward(hq, hk, hv, hdo, *outs)
+        q, k, v, do = (t.cuda() for t in (hq, hk, hv, hdo))
+        o, gg, _ = L.forward(q, k, v, True, 1.0 / temperature, order=2)
+        ref = (o,) + tuple(L.backward(q, k, v, o, gg, do, True, 1.0 / temperature, order=2)[:3])
+        torch.cuda.synchronize()
+        for got, want in zip(outs, ref):
+            w = want.float().cpu()
+            assert float((got.float() - w).abs().max()) <= 2e-2 * float(w.abs().max())

@@ -73,3 +73,94 @@ def test_tensorcore_backward_matches_oracle(shape):
     dq_ref, dk_ref, dv_ref = orc.fastmax_naive_grads(host(q), host(k), host(v), host(do), True, poly)
     errs = {n: orc.max_norm_err(host(a), b) for n, a, b in (("dq", dq, dq_ref), ("dk", dk, dk_ref), ("dv", dv, dv_ref))}
     assert max(errs.values()) < 2e-2, errs
+
+
+def test_single_stream_flag_gives_the_same_results():
+    """FASTMAX_FLAG_SINGLE_STREAM keeps every launch on the caller's stream; the default runs the independent
+    scans side by side on internal streams.  Both orders of the float32 reduce-adds must agree to rounding."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, N, D = 2, 8, 700, 64
+    rng = np.random.default_rng(17)
+    q, k, v, do = (torch.from_numpy(rng.standard_normal((B, H, N, D)).astype(np.float32)).cuda().bfloat16() for _ in range(4))
+    it = 1.0 / (2.0 * math.sqrt(D))
+    outs = []
+    for flags in (0, L.FLAG_SINGLE_STREAM):
+        o, g, _ = L.forward(q, k, v, True, it, order=2, flags=flags)
+        dq, dk, dv, _ = L.backward(q, k, v, o, g, do, True, it, order=2, flags=flags)
+        torch.cuda.synchronize()
+        L.check_status()
+        outs.append([host(t) for t in (o, dq, dk, dv)])
+    for a, b in zip(*outs):
+        assert orc.max_norm_err(a, b) < 5e-3
+
+
+def test_wait_histogram_is_empty_after_clean_runs():
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    lib = L.load()
+    x = torch.randn(1, 16, 300, 64, device="cuda").bfloat16()
+    o, g, _ = L.forward(x, x, x, True, 0.1, order=2)
+    torch.cuda.synchronize()
+    assert lib.fastmax_check_status() == 0
+    assert L.wait_histogram() == {}
+    assert lib.fastmax_debug_wait_histogram(None, 256) == 1  # FASTMAX_ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("shape", [(1, 13, 129, 129), (1, 16, 257, 385), (3, 5, 1024, 1024)])
+def test_tensorcore_more_shapes_forward_backward(shape):
+    """Chunk-boundary sizes, a key prefix that is not a multiple of the chunk, and head counts that are not a
+    multiple of anything."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, nq, nk = shape
+    D = 64
+    rng = np.random.default_rng(nq * 3 + nk)
+    q, do = (torch.from_numpy(rng.standard_normal((B, H, nq, D)).astype(np.float32)).cuda().bfloat16() for _ in range(2))
+    k, v = (torch.from_numpy(rng.standard_normal((B, H, nk, D)).astype(np.float32)).cuda().bfloat16() for _ in range(2))
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / (2.0 * math.sqrt(D)), 2)
+    L.profile_collect()
+    L.profile(True)
+    o, g, _ = L.forward(q, k, v, True, poly.inv_temp, order=2)
+    dq, dk, dv, _ = L.backward(q, k, v, o, g, do, True, poly.inv_temp, order=2)
+    L.check_status()
+    L.profile(False)
+    kinds = L.profile_collect()
+    for name in ("tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_scan_bwd_dv"):
+        assert name in kinds, f"{name} did not run: {kinds}"
+    o_ref, _ = orc.fastmax_naive(host(q), host(k), host(v), True, poly)
+    dq_ref, dk_ref, dv_ref = orc.fastmax_naive_grads(host(q), host(k), host(v), host(do), True, poly)
+    errs = {n: orc.max_norm_err(host(a), b) for n, a, b in (("o", o, o_ref), ("dq", dq, dq_ref), ("dk", dk, dk_ref), ("dv", dv, dv_ref))}
+    assert max(errs.values()) < 2e-2, errs
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 300, 300), (1, 16, 128, 200)])
+def test_tensorcore_forward_writes_its_final_state(shape):
+    """state_out without state_in stays on the tensor-memory path: the scan stores the moments of all keys."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, nq, nk = shape
+    D = 64
+    rng = np.random.default_rng(nq + 7 * nk)
+    q = torch.from_numpy(rng.standard_normal((B, H, nq, D)).astype(np.float32)).cuda().bfloat16()
+    k, v = (torch.from_numpy(rng.standard_normal((B, H, nk, D)).astype(np.float32)).cuda().bfloat16() for _ in range(2))
+    it = 1.0 / (2.0 * math.sqrt(D))
+    L.profile_collect()
+    L.profile(True)
+    o, g, state = L.forward(q, k, v, True, it, order=2, want_state=True)
+    L.check_status()
+    L.profile(False)
+    assert "tc_scan_fwd" in L.profile_collect()
+    o_plain, g_plain, _ = L.forward(q, k, v, True, it, order=2)
+    _, _, state_f32 = L.forward(q, k, v, True, it, order=2, want_state=True, flags=L.FLAG_NO_TENSOR_CORES)
+    torch.cuda.synchronize()
+    assert orc.max_norm_err(host(o), host(o_plain)) < 2e-3
+    assert state.shape == state_f32.shape == (B, H, 64 * 36 + 65, 68)
+    # against the exact float32 engine: only the bf16 rounding of the features separates the two
+    for b in range(B):
+        for h in range(0, H, 3):
+            got, ref = host(state[b, h, :, :65]), host(state_f32[b, h, :, :65])
+            assert orc.max_norm_err(got, ref) < 5e-3
+            # linear rows and the constant row carry no product rounding at all
+            assert orc.max_norm_err(got[-65:], ref[-65:]) < 1e-5
+    assert float(state[..., 65:].abs().max()) == 0.0
