@@ -49,7 +49,7 @@ DEFAULT = "cfg2_bf16_causal_p2_B8_H16_N4096_D64"
 # on the prof_ workload: 64 heads x 4096 tokens); bench.py scales them by head-tokens to its own workload.
 DRAM_TRAFFIC = {
     name: {"bytes_per_launch": b, "head_tokens": 64 * 4096, "source": "profiles/ncu_tc_scans_prof_workload.md"}
-    for name, b in (("tc_scan_fwd", 204.99e6), ("tc_scan_bwd_q", 256.05e6), ("tc_scan_bwd_kv", 258.17e6), ("tc_scan_bwd_dv", 215.86e6))
+    for name, b in (("tc_scan_fwd", 208.65e6), ("tc_scan_bwd_q", 257.25e6), ("tc_scan_bwd_kv", 258.31e6), ("tc_scan_bwd_dv", 218.70e6))
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 

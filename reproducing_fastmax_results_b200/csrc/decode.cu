@@ -5,10 +5,12 @@
 //     o   =   o'[:D] / o'[D],   g = o'[D]
 //
 // The state of a head (D=64, order 2: 2369 rows x 68 floats = 644 KB) is read once and written once; nothing
-// else moves, so the kernel is bound by HBM: 2 x state bytes per step.  A cluster of eight thread blocks shares
-// one head, each block streams an eighth of the rows with 128-bit accesses (thread = one float4 column of a
-// row, several rows in flight), the partial outputs meet in the first block's shared memory over the
-// cluster's distributed shared memory, and that block divides and stores the token's output.
+// else moves, so the kernel is bound by HBM: 2 x state bytes per step.  A cluster of 1, 2, 4 or 8 thread blocks
+// shares one head (the host picks the smallest cluster that still gives the GPU about a thousand blocks: few, long
+// blocks stream best, but there must be enough of them to fill 148 SMs several times over), each block streams its
+// share of the rows with 128-bit accesses (thread = one float4 column of a row, four rows in flight), the partial
+// outputs meet in the first block's shared memory over the cluster's distributed shared memory, and that block
+// divides and stores the token's output.
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -25,9 +27,9 @@ int report_cuda_error(cudaError_t e);
 
 namespace dec {
 
-constexpr int CL = 8;    // thread blocks per head (one cluster)
-constexpr int RG = 16;   // rows a block works on at a time
-constexpr int UNROLL = 4;
+constexpr int MAX_CL = 8;   // largest cluster: thread blocks that share one head
+constexpr int RG = 16;      // rows a block works on at a time
+constexpr int UNROLL = 4;   // rows a thread has in flight
 
 struct DecodeParams {
   View q, k, v, o, g;
@@ -50,7 +52,7 @@ template <>
 __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
 template <typename T, int D, int ORDER>
-__global__ void __cluster_dims__(CL, 1, 1) __launch_bounds__(((D + 4) / 4) * RG)
+__global__ void __launch_bounds__(((D + 4) / 4) * RG)
 decode_step_kernel(const DecodeParams P) {
   using G = Geo<D>;
   constexpr int C4 = (D + 4) / 4;          // float4 columns of a state row
@@ -60,12 +62,13 @@ decode_step_kernel(const DecodeParams P) {
   __shared__ float sq[D], sk[D];
   __shared__ float4 sv[C4];
   __shared__ float4 red[RG][C4];
-  __shared__ float4 part[CL][C4];          // block 0 of the cluster: one row per block
+  __shared__ float4 part[MAX_CL][C4];      // block 0 of the cluster: one row per block
   __shared__ unsigned char tab_a[G::NPAIRS], tab_b[G::NPAIRS];
 
   cg::cluster_group cluster = cg::this_cluster();
   const int tid = threadIdx.x;
   const int rank = (int)cluster.block_rank();
+  const int CL = (int)gridDim.x;            // the cluster spans the grid's x extent
   const int head = blockIdx.y;
   const int bi = head / P.heads, hi = head - bi * P.heads;
 
@@ -163,7 +166,6 @@ decode_step_kernel(const DecodeParams P) {
   float* fin = reinterpret_cast<float*>(&red[0][0]);   // [C4 * 4]: o'[0..D-1], g, padding
   if (tid < C4) {
     float4 t = part[0][tid];
-#pragma unroll
     for (int j = 1; j < CL; ++j) {
       const float4 x = part[j][tid];
       t.x += x.x, t.y += x.y, t.z += x.z, t.w += x.w;
@@ -185,12 +187,22 @@ decode_step_kernel(const DecodeParams P) {
 template <typename T, int D>
 static cudaError_t launch(int order, const DecodeParams& P, int bh, cudaStream_t st) {
   constexpr int NT = ((D + 4) / 4) * RG;
-  const dim3 grid(CL, bh);
-  if (order == 2)
-    decode_step_kernel<T, D, 2><<<grid, NT, 0, st>>>(P);
-  else
-    decode_step_kernel<T, D, 1><<<grid, NT, 0, st>>>(P);
-  return cudaGetLastError();
+  int cl = 1;
+  while (cl < MAX_CL && (long long)cl * bh < 1024) cl *= 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cl, bh);
+  cfg.blockDim = dim3(NT);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cl;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (order == 2) return cudaLaunchKernelEx(&cfg, decode_step_kernel<T, D, 2>, P);
+  return cudaLaunchKernelEx(&cfg, decode_step_kernel<T, D, 1>, P);
 }
 
 template <typename T>
