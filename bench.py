@@ -355,8 +355,24 @@ def run_decode(args, torch, dist, dev, rank, world):
     t = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.destroy_process_group()
     ms_step = float(t.item()) / args.steps
+    # the same steps replayed from a CUDA graph (what a generation loop would do): no host launch gaps
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(ntok):
+            step()
+    reps = max(1, args.steps // ntok)
+    graph.replay()
+    torch.cuda.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for _ in range(reps):
+        graph.replay()
+    g1.record()
+    torch.cuda.synchronize()
+    ms_graph = g0.elapsed_time(g1) / (reps * ntok)
     if rank == 0:
         pk = peaks()
         state_bytes = state.numel() * 4
@@ -371,10 +387,15 @@ def run_decode(args, torch, dist, dev, rank, world):
             "roofline": {"kernel": "decode_step", "bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs / pk["hbm_gbs"], "peak_source": pk["_source"],
                          "note": "algorithmic bytes = one read and one write of every head's state; launch gaps between "
-                                 "the back-to-back steps are inside the time", "traffic": None},
+                                 "the back-to-back steps are inside the time",
+                         "traffic": 604.3e6 * state_bytes / 329.9e6, "traffic_source": "profiles/ncu_decode_step.md",
+                         "cuda_graph": {"ms_per_step": ms_graph, "achieved": 2.0 * state_bytes / (ms_graph * 1e-3) / 1e9,
+                                        "frac": 2.0 * state_bytes / (ms_graph * 1e-3) / 1e9 / pk["hbm_gbs"]}},
             "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
     return 0
 
 

@@ -125,3 +125,38 @@ def test_host_pipeline_matches_the_single_call():
         for got, want in zip(outs, ref):
             w = want.float().cpu()
             assert float((got.float() - w).abs().max()) <= 2e-2 * float(w.abs().max())
+
+
+def test_forward_backward_replay_from_a_cuda_graph():
+    """The launch sequences contain no synchronisation and no allocation of their own, so a caller can capture
+    them (internal side streams included: they fork from and join back into the capturing stream) and replay."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, N, D = 2, 16, 384, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q, k, v, do = (torch.randn(B, H, N, D, device="cuda", generator=g).bfloat16() for _ in range(4))
+    it = 1.0 / (2.0 * math.sqrt(D))
+
+    def run():
+        o, gg, _ = L.forward(q, k, v, True, it, order=2)
+        return (o,) + tuple(L.backward(q, k, v, o, gg, do, True, it, order=2)[:3])
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):   # warm-up outside the capture: lazy initialisation (streams, tensor-map encoder)
+        ref = [t.clone() for t in run()]
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = run()
+    for _ in range(2):
+        q.copy_(torch.randn(B, H, N, D, device="cuda", generator=g).bfloat16())   # new inputs in the captured buffers
+        graph.replay()
+        torch.cuda.synchronize()
+        L.check_status()
+        want = run()
+        torch.cuda.synchronize()
+        for a, b in zip(outs, want):
+            assert float((a.float() - b.float()).abs().max()) <= 5e-3 * float(b.float().abs().max()) + 1e-6
+    assert float((ref[0].float() - outs[0].float()).abs().max()) > 0.0   # the replays really used the new q
