@@ -38,6 +38,8 @@ WORKLOADS = {
     "prof_bf16_causal_p2_B4_H16_N4096_D64": (4, 16, 4096, 64, 2, True, "bf16", 1.0),
     # BASELINE config 3: one long causal sequence, cut into contiguous pieces across the ranks (strong scaling)
     "cfg3_f32_causal_p2_B1_H8_N131072_D32": (1, 8, 131072, 32, 2, True, "f32", 1.0),
+    # BASELINE config 4: order 1, non-causal, wide batch, forward (run with --mode fwd): HBM-bound
+    "cfg4_bf16_noncausal_p1_B64_H12_N1024_D64": (64, 12, 1024, 64, 1, False, "bf16", 0.5),
     # incremental decoding: one new token per (batch, head) per step against the carried state (N = prefix length is
     # irrelevant to the cost; 512 head states = 330 MB, larger than L2)
     "decode_bf16_p2_B32_H16_D64": (32, 16, 1, 64, 2, True, "bf16", 1.0),
@@ -193,6 +195,31 @@ def cpu_sample_text(workload, n_sample, heads):
     B, H, N, D, order, causal, dtype, scale = WORKLOADS[workload]
     return (f"factorised {'causal' if causal else 'non-causal'} order-{order} forward+backward (torch CPU, autograd) on "
             f"{heads} of {B * H} heads, {n_sample} of {N} tokens each, D={D}; head-tokens / H = metric tokens")
+
+
+def bind_host_near_gpu(torch, index):
+    """Pins this process to the CPU cores that sit on the GPU's PCIe root (sysfs local_cpulist), so that the pinned
+    host buffers it allocates afterwards are first touched on that NUMA node.  Returns the core list or None."""
+    try:
+        props = torch.cuda.get_device_properties(index)
+        bdf = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bdf}/local_cpulist") as f:
+            text = f.read().strip()
+        cores = set()
+        for part in text.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                cores.update(range(int(a), int(b) + 1))
+            elif part:
+                cores.add(int(part))
+        allowed = os.sched_getaffinity(0)
+        cores &= allowed
+        if cores and cores != allowed:
+            os.sched_setaffinity(0, cores)
+            return text
+    except Exception:
+        pass
+    return None
 
 
 def run_reference_arm(args):
@@ -357,8 +384,6 @@ def run_decode(args, torch, dist, dev, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t.item()) / args.steps
     # the same steps replayed from a CUDA graph (what a generation loop would do): no host launch gaps
-    side = torch.cuda.Stream(dev)
-    side.wait_stream(torch.cuda.current_stream())
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         for _ in range(ntok):
@@ -536,6 +561,13 @@ def main():
                        DRAM_TRAFFIC[dominant]["bytes_per_launch"] * (B * H * N) / DRAM_TRAFFIC[dominant]["head_tokens"],
             "traffic_source": DRAM_TRAFFIC.get(dominant, {}).get("source"),
         }
+    if order == 1:   # 33 flop per byte: bound by HBM; the whole call against its algorithmic bytes
+        esz = 2 if dtype_name == "bf16" else 4
+        bytes_alg = (4 if args.mode == "fwd" else 12) * B * H * N * D * esz + 4 * B * H * N
+        gbs = bytes_alg / (ms_step / world * 1e-3) / 1e9 if world == 1 else bytes_alg / (ms_step * 1e-3) / 1e9
+        roofline = {"kernel": "whole call (%s)" % ", ".join(sorted(kernels)), "bound": "hbm", "achieved": gbs,
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "peak_source": pk["_source"],
+                    "note": "algorithmic bytes of the call (read q, k, v; write o and g) per rank / step time", "traffic": None}
     step_counted = sum(counted_flops(n)[0] * kernels[n]["launches_per_step"] for n in kernels)
     whole = {
         "flops_alg_per_step": 6.0 * U,
@@ -548,9 +580,12 @@ def main():
     # ---- end to end: public operator, pinned host buffers, H2D + D2H inside the timed region ----
     e2e = None
     if not args.no_e2e and args.mode == "fwd_bwd":
+        all_cores = os.sched_getaffinity(0)
+        numa = bind_host_near_gpu(torch, local_rank)   # first touch of the pinned buffers on the GPU's NUMA node
         hq, hk, hv, hdo = (x.cpu().pin_memory() for x in (q, k, v, do))
-        ho = torch.empty_like(hq).pin_memory()
-        hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(3))
+        ho = torch.zeros_like(hq).pin_memory()
+        hdq, hdk, hdv = (torch.zeros_like(hq).pin_memory() for _ in range(3))
+        os.sched_setaffinity(0, all_cores)
         temperature = 8.0 * math.sqrt(D)
 
         def e2e_step():
@@ -594,6 +629,7 @@ def main():
                "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "steps": e2e_steps,
                "api": "reproducing_fastmax_results_b200.host_pipeline.HostFastmax.forward_backward: pinned host q,k,v,dO in; "
                       "o,dq,dk,dv out to pinned host; batch slices pipelined over copy-in / compute / copy-out streams",
+               "host_cores": numa or "unchanged",
                "single_call": {"value": tokens_per_step / (single_ms * 1e-3) / 1e6, "ms_per_step": single_ms,
                                "api": "FastMax.apply + backward on the whole batch between one copy-in and one copy-out"}}
 
@@ -612,7 +648,8 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": dtype_name + " inputs, f32 accumulate", "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": B, "heads": H, "seq_len": N, "head_dim": D,
                        "order": order, "causal": causal, "parallelism": f"batch x head sharding, {world} rank(s), no collective",
-                       "l2": "inputs (268 MB) + workspace exceed the 126 MB L2; no explicit flush"},
+                       "l2": "inputs (%d MB) + workspace exceed the 126 MB L2; no explicit flush"
+                             % (4 * q.numel() * q.element_size() >> 20)},
             "roofline": roofline, "whole_step": whole, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks,
         }

@@ -236,6 +236,7 @@ intra_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant_
 #include "tc_bwd.cuh"
 #include "tc_scan2.cuh"
 #include "tc_scan3.cuh"
+#include "tc_p1.cuh"
 
 }  // namespace tc
 
@@ -371,7 +372,37 @@ size_t tc_forward_workspace(const fastmax_problem* pb, const fastmax_forward_arg
          transposed_bytes(pb->batch * pb->heads, pb->nk);
 }
 
+// Order 1 without a mask: one kernel, no workspace (tc_p1.cuh).
+static bool tc_p1_supported(const fastmax_problem* pb, const fastmax_forward_args* a) {
+  if (pb->flags & FASTMAX_FLAG_NO_TENSOR_CORES) return false;
+  if (pb->dtype != FASTMAX_BF16 || pb->d != 64 || pb->order != 1 || pb->causal) return false;
+  if (!a->o.ptr || a->state_in || a->state_out) return false;
+  if (pb->nq <= 0 || pb->nk <= 0) return false;
+  if ((long long)pb->batch * pb->heads < 64) return false;   // one CTA per head: fewer would leave most SMs idle
+  return true;
+}
+
+static int tc_p1_forward(const fastmax_problem* pb, const fastmax_forward_args* a, cudaStream_t st) {
+  CUtensorMap tmq, tmk, tmv;
+  if (!make_map(&tmq, a->q, pb->batch, pb->heads, pb->nq, 64, tc::CH, true) ||
+      !make_map(&tmk, a->k, pb->batch, pb->heads, pb->nk, 64, tc::CH, true) ||
+      !make_map(&tmv, a->v, pb->batch, pb->heads, pb->nk, 8, tc::CH, false))
+    return FASTMAX_TC_NOT_HANDLED;
+  cudaError_t e = cudaFuncSetAttribute(tc::p1::p1_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::p1::SMEM_BYTES);
+  if (e != cudaSuccess) return report_cuda_error(e);
+  tc::p1::P1Params P{View{a->o.ptr, a->o.stride_b, a->o.stride_h, a->o.stride_n},
+                     View{a->g.ptr, a->g.stride_b, a->g.stride_h, a->g.stride_n},
+                     pb->heads, pb->nq, pb->nk, pb->a0, pb->a1 * pb->inv_temperature};
+  {
+    LaunchScope ls(KK_P1_FWD, st);
+    tc::p1::p1_forward_kernel<<<dim3(pb->batch * pb->heads), tc::p1::THREADS, tc::p1::SMEM_BYTES, st>>>(tmq, tmk, tmv, P);
+  }
+  e = cudaGetLastError();
+  return e == cudaSuccess ? FASTMAX_OK : report_cuda_error(e);
+}
+
 int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (tc_p1_supported(pb, a)) return tc_p1_forward(pb, a, st);
   if (!tc_forward_supported(pb, a)) return FASTMAX_TC_NOT_HANDLED;
   if (ws_bytes < tc_forward_workspace(pb, a)) return FASTMAX_ERR_WORKSPACE;
   CUtensorMap tmq, tmk, tmv;

@@ -164,3 +164,52 @@ def test_tensorcore_forward_writes_its_final_state(shape):
             # linear rows and the constant row carry no product rounding at all
             assert orc.max_norm_err(got[-65:], ref[-65:]) < 1e-5
     assert float(state[..., 65:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("shape", [(4, 16, 300, 300), (2, 40, 128, 1024), (1, 64, 1000, 77), (64, 12, 1024, 1024)])
+def test_order1_noncausal_forward_on_tensor_memory(shape):
+    """Order 1 without a mask (BASELINE's wide-batch configuration): one streaming kernel per call."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, nq, nk = shape
+    D = 64
+    g = torch.Generator(device="cuda").manual_seed(nq + nk)
+    q = (torch.randn(B, H, nq, D, device="cuda", generator=g) * 0.5).bfloat16()
+    k, v = ((torch.randn(B, H, nk, D, device="cuda", generator=g) * 0.5).bfloat16() for _ in range(2))
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / (8.0 * math.sqrt(D)), 1)
+    L.profile_collect()
+    L.profile(True)
+    o, gg, _ = L.forward(q, k, v, False, poly.inv_temp, order=1)
+    L.check_status()
+    L.profile(False)
+    kinds = L.profile_collect()
+    assert set(kinds) == {"p1_fwd"}, kinds
+    o32, g32, _ = L.forward(q, k, v, False, poly.inv_temp, order=1, flags=L.FLAG_NO_TENSOR_CORES)
+    torch.cuda.synchronize()
+    assert orc.max_norm_err(host(o), host(o32)) < 2e-2
+    assert orc.max_norm_err(host(gg), host(g32)) < 2e-3
+    heads = [(0, 0), (B - 1, H - 1)]
+    for b, h in heads:   # a few heads against the oracle itself
+        o_ref, g_ref = orc.fastmax_naive(host(q[b, h]), host(k[b, h]), host(v[b, h]), False, poly)
+        assert orc.max_norm_err(host(o[b, h]), o_ref) < 2e-2
+        assert orc.max_norm_err(host(gg[b, h]), g_ref) < 2e-3
+
+
+def test_order1_strided_views_and_other_coefficients():
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, N, D = 2, 48, 200, 64
+    g = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.randn(B, N, 3, H, D, device="cuda", generator=g).bfloat16()   # fused projection layout
+    q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    poly = orc.Poly(0.7, 1.3, 0.5, 0.11, 1)
+    L.profile_collect()
+    L.profile(True)
+    o, gg, _ = L.forward(q, k, v, False, poly.inv_temp, poly.a0, poly.a1, poly.a2, order=1)
+    L.check_status()
+    L.profile(False)
+    assert "p1_fwd" in L.profile_collect()
+    for b, h in [(0, 5), (1, 47)]:
+        o_ref, g_ref = orc.fastmax_naive(host(q[b, h]), host(k[b, h]), host(v[b, h]), False, poly)
+        assert orc.max_norm_err(host(o[b, h]), o_ref) < 2e-2
+        assert orc.max_norm_err(host(gg[b, h]), g_ref) < 2e-3
