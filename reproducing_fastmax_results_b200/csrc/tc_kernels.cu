@@ -383,19 +383,19 @@ static bool tc_p1_supported(const fastmax_problem* pb, const fastmax_forward_arg
 }
 
 static int tc_p1_forward(const fastmax_problem* pb, const fastmax_forward_args* a, cudaStream_t st) {
-  CUtensorMap tmq, tmk, tmv;
+  CUtensorMap tmq, tmk, tmv, tmo;
   if (!make_map(&tmq, a->q, pb->batch, pb->heads, pb->nq, 64, tc::CH, true) ||
       !make_map(&tmk, a->k, pb->batch, pb->heads, pb->nk, 64, tc::CH, true) ||
-      !make_map(&tmv, a->v, pb->batch, pb->heads, pb->nk, 8, tc::CH, false))
+      !make_map(&tmv, a->v, pb->batch, pb->heads, pb->nk, 8, tc::CH, false) ||
+      !make_map(&tmo, a->o, pb->batch, pb->heads, pb->nq, 64, 32, true))   // output: 32-row boxes, one per epilogue warp
     return FASTMAX_TC_NOT_HANDLED;
   cudaError_t e = cudaFuncSetAttribute(tc::p1::p1_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::p1::SMEM_BYTES);
   if (e != cudaSuccess) return report_cuda_error(e);
-  tc::p1::P1Params P{View{a->o.ptr, a->o.stride_b, a->o.stride_h, a->o.stride_n},
-                     View{a->g.ptr, a->g.stride_b, a->g.stride_h, a->g.stride_n},
+  tc::p1::P1Params P{View{a->g.ptr, a->g.stride_b, a->g.stride_h, a->g.stride_n},
                      pb->heads, pb->nq, pb->nk, pb->a0, pb->a1 * pb->inv_temperature};
   {
     LaunchScope ls(KK_P1_FWD, st);
-    tc::p1::p1_forward_kernel<<<dim3(pb->batch * pb->heads), tc::p1::THREADS, tc::p1::SMEM_BYTES, st>>>(tmq, tmk, tmv, P);
+    tc::p1::p1_forward_kernel<<<dim3(pb->batch * pb->heads), tc::p1::THREADS, tc::p1::SMEM_BYTES, st>>>(tmq, tmk, tmv, tmo, P);
   }
   e = cudaGetLastError();
   return e == cudaSuccess ? FASTMAX_OK : report_cuda_error(e);

@@ -6,9 +6,10 @@
 //
 // 33 flop per byte: the call is bound by HBM (read q, k, v once, write o and g once).  One CTA per (batch, head)
 // streams the head's K and V chunks through a two-deep TMA ring into the moment MMAs, rounds c1 S to bf16 into a
-// K-major operand tile, then streams the Q chunks through the same ring; the output rows leave straight from
-// registers (one 128-byte row per thread).  Two CTAs fit on an SM, so one head's phase change hides behind the
-// other's streaming.
+// K-major operand tile, then streams the Q chunks through the same ring; every epilogue warp stages its 32 output
+// rows in shared memory and hands them to the copy engine (tiled bulk store: whole 128-byte lines, rows past the
+// last query clipped by the tensor map).  Two CTAs fit on an SM, so one head's phase change hides behind the other's
+// streaming.
 // Warp roles (160 threads): 0-3 epilogue (TMEM lane = moment row, then = token), 4 TMA loads + MMA issue.
 // TMEM columns (256 allocated): 0..63 S^T, 64..79 s0, 96..175 and 176..255 the two output accumulators.
 #pragma once
@@ -22,24 +23,25 @@ constexpr int OFF_SB = OFF_V + 2 * 10 * BLK;  // 73728: c1 S as a K-major B oper
 constexpr int OFF_ONES = OFF_SB + 80 * 128;   // 83968: 1 KB of bf16 ones (B operand of the s0 MMA)
 constexpr int OFF_T0 = OFF_ONES + 1024;       // 80 floats: a0 s0
 constexpr int OFF_BAR = OFF_T0 + 512;
-constexpr int OFF_END = OFF_BAR + 256;
+constexpr int OFF_OST = OFF_BAR + 512;        // 86016: output staging, one 32-row x 128-byte swizzled box per epilogue warp
+constexpr int OFF_END = OFF_OST + 4 * 4096;
 // rows 80..127 of the moment MMA's A operand read the 12 KB that follow a [V | 1] buffer (the other buffer, the
 // S tile, the ones): finite or not, they only reach TMEM lanes 80..127, which nobody reads
 static_assert(OFF_V + 10 * BLK + 16 * BLK <= OFF_END + 1024, "the moment MMA's A operand stays inside the allocation");
 constexpr int SMEM_BYTES = OFF_END + 1024 + 1024;
-static_assert(OFF_SB % 1024 == 0 && OFF_V % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+static_assert(OFF_SB % 1024 == 0 && OFF_V % 1024 == 0 && OFF_OST % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 constexpr uint32_t COL_S = 0u, COL_S0 = 64u, COL_O = 96u;
 constexpr int B_X_READY = 0, B_X_FREE = 2, B_S_DONE = 4, B_SB_READY = 5, B_O_DONE = 6, B_O_FREE = 8, B_COUNT = 10;
 
 struct P1Params {
-  View o, g;
+  View g;
   int heads, nq, nk;
   float c0, c1;   // a0, a1 / temperature
 };
 
 __global__ void __launch_bounds__(THREADS, 2)
 p1_forward_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
-                  const __grid_constant__ CUtensorMap tmv, const P1Params P) {
+                  const __grid_constant__ CUtensorMap tmv, const __grid_constant__ CUtensorMap tmo, const P1Params P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* sm = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -210,8 +212,8 @@ p1_forward_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant
       if (l < 80) t0[l] = 0.f;   // no keys: every output is 0 / 0 as the definition says
       __syncwarp();
     }
-    __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(P.o.ptr)) + (long long)b_idx * P.o.sb + (long long)h_idx * P.o.sh;
     float* gbase = P.g.ptr ? reinterpret_cast<float*>(const_cast<void*>(P.g.ptr)) + (long long)b_idx * P.g.sb + (long long)h_idx * P.g.sh : nullptr;
+    uint8_t* ost = sm + OFF_OST + w * 4096;   // this warp's staging box: row = lane
     for (int c = 0; c < nqc && ok; ++c) {
       const uint32_t ob = (uint32_t)c & 1u;
       if (!WAIT(B_O_DONE + ob, (uint32_t)(c >> 1))) { FAIL(412); break; }
@@ -224,23 +226,33 @@ p1_forward_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant
       tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[B_O_FREE + ob]);
+      if (lane == 0) {
+        mbar_arrive(&bars[B_O_FREE + ob]);
+        bulk_wait_read_all();   // the previous chunk's store has read the staging box
+      }
+      __syncwarp();
       const long long row = (long long)c * CH + l;
-      if (row < P.nq) {
-        const float gsum = __uint_as_float(r8[0]) + t0[64];
-        const float inv = 1.f / gsum;
-        uint4* dst = reinterpret_cast<uint4*>(obase + row * P.o.sn);
+      const float gsum = __uint_as_float(r8[0]) + t0[64];
+      const float inv = 1.f / gsum;
+      const int sw = lane & 7;
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-          const uint32_t* r = c8 < 4 ? &ra[8 * c8] : &rb[8 * (c8 - 4)];
-          float x[8];
+      for (int c8 = 0; c8 < 8; ++c8) {
+        const uint32_t* r = c8 < 4 ? &ra[8 * c8] : &rb[8 * (c8 - 4)];
+        float x[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) x[e] = (__uint_as_float(r[e]) + t0[8 * c8 + e]) * inv;
-          dst[c8] = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
-        }
-        if (gbase) gbase[row * P.g.sn] = gsum;
+        for (int e = 0; e < 8; ++e) x[e] = (__uint_as_float(r[e]) + t0[8 * c8 + e]) * inv;
+        *reinterpret_cast<uint4*>(ost + lane * 128 + ((c8 ^ sw) << 4)) =
+            make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+      }
+      if (gbase && row < P.nq) gbase[row * P.g.sn] = gsum;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && (long long)c * CH + w * 32 < P.nq) {
+        tma_store_4d(&tmo, ost, 0, c * CH + w * 32, h_idx, b_idx);
+        bulk_commit_group();
       }
     }
+    if (lane == 0) bulk_wait_all();   // the last store has landed before the CTA retires
   }
 
   tc_fence_before_sync();

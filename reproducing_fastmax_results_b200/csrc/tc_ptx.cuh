@@ -85,6 +85,15 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tensor_m
       : "memory");
 }
 
+// Tiled bulk tensor store shared -> global (bulk-group completion).  Rows of the box that fall outside the tensor
+// are not written.  Never called with a negative coordinate.
+__device__ __forceinline__ void tma_store_4d(const void* tensor_map, const void* smem_src, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tensor_map, uint64_t* bar, int c0, int c1, int c2) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
