@@ -28,7 +28,7 @@
 // exactly (x_a is doubled); slices of pair tiles only then scale their output by c2 once, in float32, when it is
 // drained.  The slice that holds the linear/constant tile puts the weights into the bf16 state copy instead.
 // The output partial of the slice is staged in shared memory and added to the float32 accumulator in global
-// memory with ONE bulk reduce (cp.reduce.async.bulk) per chunk.
+// memory with one bulk reduce (cp.reduce.async.bulk) per consumer warp and chunk (its 32 rows).
 // TMEM columns: 0..319 four state accumulators, 320..399 output accumulator, 400..495 the ring.
 // Warp roles (608 threads): 0-3, 4-7, 8-11 producer sets, 12-15 consumers (state -> bf16 copy, output drain),
 // 16 apply issuer, 17 update issuer, 18 TMA loader.  Every wait is bounded (abort flag + error code).
@@ -62,7 +62,7 @@ constexpr uint32_t COL_O = 320u, COL_A = 400u;
 // barriers
 constexpr int B_FULL_Q = 0, B_FULL_K = 3, B_EMPTY = 6, B_Q_READY = 9, B_Q_FREE = 11, B_KT_READY = 13, B_KT_FREE = 15,
               B_VP_READY = 17, B_VP_FREE = 19, B_SB_READY = 21, B_S_DONE = 25, B_A_DONE = 29, B_O_DONE = 33, B_O_FREE = 34,
-              B_OST_FREE = 35, B_OST_FULL = 36, B_COUNT = 37;
+              B_COUNT = 35;
 
 struct ApplyParams {
   float* out;          // forward: O' accumulator [BH][nz][68]; dv scan: dV accumulator [BH][nz][ACC_LD = 68]
@@ -232,8 +232,6 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
     for (int i = 0; i < 4; ++i) { mbar_init(&bars[B_SB_READY + i], 4); mbar_init(&bars[B_S_DONE + i], 1); mbar_init(&bars[B_A_DONE + i], 1); }
     mbar_init(&bars[B_O_DONE], 1);
     mbar_init(&bars[B_O_FREE], 4);
-    mbar_init(&bars[B_OST_FREE], 1);
-    mbar_init(&bars[B_OST_FULL], 4);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -351,12 +349,11 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars[B_O_FREE]);
-          // partial of this slice -> staging rows in shared memory -> ONE bulk reduce-add into the float32
-          // accumulator (the chunk's rows are contiguous there); the copy engine does the adds, fully coalesced.
-          if (ci >= 2) {  // the previous chunk's reduce has read the staging rows
-            if (w == W_CONS && lane == 0) { bulk_wait_read_all(); mbar_arrive(&bars[B_OST_FREE]); }
-            if (!WAIT(B_OST_FREE, (uint32_t)(ci - 2))) { FAIL(222); ok = false; break; }
-          }
+          // partial of this slice -> staging rows in shared memory -> bulk reduce-adds into the float32 accumulator
+          // (the chunk's rows are contiguous there); the copy engine does the adds, fully coalesced.  Every warp
+          // owns its 32 rows from TMEM to the reduce, so the four warps never wait for one another here.
+          if (lane == 0) bulk_wait_read_all();   // this warp's previous reduce has read its staging rows
+          __syncwarp();
           {
             float4* rowp = reinterpret_cast<float4*>(ost + l * OUT_LD);
 #pragma unroll
@@ -370,15 +367,14 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&bars[B_OST_FULL]);
-          if (w == W_CONS) {  // the leader warp waits for all four warps' rows, one lane issues the reduce
-            if (!WAIT(B_OST_FULL, (uint32_t)(ci - 1))) { FAIL(223); ok = false; break; }
-          }
-          if (w == W_CONS && lane == 0) {
+          if (lane == 0) {
             const long long q0 = (long long)c * CH - P.z_shift;  // output row of staging row 0
-            const int r0 = q0 < 0 ? (int)(-q0 < CH ? -q0 : CH) : 0;
+            const int wr0 = (w & 3) * 32;                        // this warp's staging rows
+            int r0 = q0 < 0 ? (int)(-q0 < CH ? -q0 : CH) : 0;
             const long long lim = (long long)P.nz - q0;
-            const int r1 = lim < CH ? (lim < 0 ? 0 : (int)lim) : CH;
+            int r1 = lim < CH ? (lim < 0 ? 0 : (int)lim) : CH;
+            r0 = r0 > wr0 ? r0 : wr0;
+            r1 = r1 < wr0 + 32 ? r1 : wr0 + 32;
             if (r1 > r0) {
               bulk_reduce_add_f32(obase + (q0 + r0) * OUT_LD, ost + r0 * OUT_LD, (uint32_t)(r1 - r0) * (uint32_t)(OUT_LD * 4));
               bulk_commit_group();
@@ -466,7 +462,7 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
         }
       }
     }
-    if (w == W_CONS && lane == 0) bulk_wait_all();  // the last reduce has landed before the CTA retires
+    if (lane == 0) bulk_wait_all();  // this warp's last reduce has landed before the CTA retires
   } else if (w == W_MMA || w == W_MMA2) {
     // ================= MMA issuers =================
     // Warp W_MMA issues the apply MMAs (apply slabs -> output), warp W_MMA2 the update MMAs (update slabs -> S_t); the
