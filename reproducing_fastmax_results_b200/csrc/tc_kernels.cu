@@ -313,7 +313,7 @@ static cudaError_t launch_transpose(const fastmax_tensor& x, int batch, int head
 // stream with an event and joined back into it, so the call as a whole is still ordered on the caller's stream.
 struct SideStreams {
   cudaStream_t s[3] = {nullptr, nullptr, nullptr};
-  cudaEvent_t fork = nullptr, join[3] = {nullptr, nullptr, nullptr};
+  cudaEvent_t fork = nullptr, mid = nullptr, join[3] = {nullptr, nullptr, nullptr};
   bool ok = false;
 };
 static SideStreams* side_streams() {
@@ -326,7 +326,8 @@ static SideStreams* side_streams() {
   SideStreams& p = pool[dev];
   if (!tried[dev]) {
     tried[dev] = true;
-    bool good = cudaEventCreateWithFlags(&p.fork, cudaEventDisableTiming) == cudaSuccess;
+    bool good = cudaEventCreateWithFlags(&p.fork, cudaEventDisableTiming) == cudaSuccess &&
+                cudaEventCreateWithFlags(&p.mid, cudaEventDisableTiming) == cudaSuccess;
     for (int i = 0; i < 3 && good; ++i)
       good = cudaStreamCreateWithFlags(&p.s[i], cudaStreamNonBlocking) == cudaSuccess &&
              cudaEventCreateWithFlags(&p.join[i], cudaEventDisableTiming) == cudaSuccess;
@@ -556,10 +557,20 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(tc::intra_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::IB_SMEM_BYTES);
   if (e != cudaSuccess) return report_cuda_error(e);
-  // Four independent kernels (they ADD into different or the same accumulators with reduce operations): the three
-  // scans go side by side, the intra-chunk kernel follows the dv scan on the caller's stream.
+  // Four independent kernels (they ADD into the accumulators with reduce operations): the intra-chunk kernel and
+  // the dv scan on the caller's stream, the dq and dk scans on side streams.  An accumulator is cast to its output
+  // as soon as its scan and the intra-chunk kernel are done, on the stream of its scan, so the casts overlap the
+  // tails of the scans that are still running.
   cudaStream_t ss[3];
   SideStreams* side = fork_streams(pb, st, 3, ss);
+  {
+    tc::IntraBwdParams I{dqa, dka, dva, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, c0, c1, c2};
+    LaunchScope ls(KK_TC_INTRA_BWD, ss[0]);
+    tc::intra_bwd_kernel<<<dim3(nch, 1, bh), tc::IB_THREADS, tc::IB_SMEM_BYTES, ss[0]>>>(tmq, tmk, tmv, tmdo, I);
+  }
+  e = cudaGetLastError();
+  if (e == cudaSuccess && side) e = cudaEventRecord(side->mid, ss[0]);
+  if (e != cudaSuccess) return report_cuda_error(e);
   {
     LaunchScope ls(KK_TC_BWD_Q, ss[1]);
     tc::s3::ChainParams C{dqa, View{a->q.ptr, a->q.stride_b, a->q.stride_h, a->q.stride_n}, pb->heads, pb->nq, pb->nk,
@@ -583,19 +594,17 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
     tc::s2::scan_apply_kernel<true><<<dim3(5 * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmk, tmqt, tmdo, A);
   }
   e = cudaGetLastError();
-  if (e != cudaSuccess) return report_cuda_error(e);
-  {
-    tc::IntraBwdParams I{dqa, dka, dva, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, c0, c1, c2};
-    LaunchScope ls(KK_TC_INTRA_BWD, ss[0]);
-    tc::intra_bwd_kernel<<<dim3(nch, 1, bh), tc::IB_THREADS, tc::IB_SMEM_BYTES, ss[0]>>>(tmq, tmk, tmv, tmdo, I);
+  if (e == cudaSuccess && side) {   // the side streams' casts also need the intra-chunk kernel's contributions
+    e = cudaStreamWaitEvent(ss[1], side->mid, 0);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ss[2], side->mid, 0);
   }
-  e = cudaGetLastError();
-  if (e == cudaSuccess) e = join_streams(side, st, 3);
   if (e != cudaSuccess) return report_cuda_error(e);
-  int rc = launch_cast_out(pb, dqa, pb->nq, &a->dq, st, tc::ACC_LD);
-  if (rc == FASTMAX_OK) rc = launch_cast_out(pb, dka, pb->nk, &a->dk, st, tc::ACC_LD);
-  if (rc == FASTMAX_OK) rc = launch_cast_out(pb, dva, pb->nk, &a->dv, st, tc::ACC_LD);
-  return rc;
+  int rc = launch_cast_out(pb, dqa, pb->nq, &a->dq, ss[1], tc::ACC_LD);
+  if (rc == FASTMAX_OK) rc = launch_cast_out(pb, dka, pb->nk, &a->dk, ss[2], tc::ACC_LD);
+  if (rc == FASTMAX_OK) rc = launch_cast_out(pb, dva, pb->nk, &a->dv, ss[0], tc::ACC_LD);
+  if (rc != FASTMAX_OK) return rc;
+  e = join_streams(side, st, 3);
+  return e == cudaSuccess ? FASTMAX_OK : report_cuda_error(e);
 }
 
 #ifdef FM_TC_TIMELINE
