@@ -105,6 +105,44 @@ __global__ void finalize_fwd_vec_kernel(const float* __restrict__ acc, int ld, i
     *(reinterpret_cast<float*>(const_cast<void*>(g.ptr)) + (long long)b * g.sb + (long long)h * g.sh + (long long)l * g.sn) = den;
 }
 
+// bf16 outputs, eight columns per thread: two 128-bit streaming loads of the float32 accumulator row, one 128-bit
+// store (the accumulators are read exactly once, so they bypass L1 and are marked evict-first).
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__global__ void finalize_fwd_bf16x8_kernel(const float* __restrict__ acc, int ld, int d, int nq, int heads, View o, View g) {
+  const int head = blockIdx.y;
+  const int d8 = d >> 3;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= nq * d8) return;
+  const int l = t / d8, c = (t - l * d8) << 3;
+  const float* r = acc + ((long long)head * nq + l) * ld;
+  const float4 v0 = __ldcs(reinterpret_cast<const float4*>(r + c));
+  const float4 v1 = __ldcs(reinterpret_cast<const float4*>(r + c + 4));
+  const float den = __ldcs(r + d);
+  const float inv = 1.f / den;
+  const int b = head / heads, h = head - b * heads;
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(o.ptr)) + (long long)b * o.sb + (long long)h * o.sh + (long long)l * o.sn;
+  *reinterpret_cast<uint4*>(op + c) = make_uint4(pack2_bf16(v0.x * inv, v0.y * inv), pack2_bf16(v0.z * inv, v0.w * inv),
+                                                 pack2_bf16(v1.x * inv, v1.y * inv), pack2_bf16(v1.z * inv, v1.w * inv));
+  if (c == 0 && g.ptr != nullptr)
+    *(reinterpret_cast<float*>(const_cast<void*>(g.ptr)) + (long long)b * g.sb + (long long)h * g.sh + (long long)l * g.sn) = den;
+}
+__global__ void cast_out_bf16x8_kernel(const float* __restrict__ acc, int d, int n, int heads, View out, int acc_ld) {
+  const int head = blockIdx.y;
+  const int d8 = d >> 3;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n * d8) return;
+  const int l = t / d8, c = (t - l * d8) << 3;
+  const float* r = acc + ((long long)head * n + l) * acc_ld + c;
+  const float4 v0 = __ldcs(reinterpret_cast<const float4*>(r));
+  const float4 v1 = __ldcs(reinterpret_cast<const float4*>(r + 4));
+  const int b = head / heads, h = head - b * heads;
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(out.ptr)) + (long long)b * out.sb + (long long)h * out.sh + (long long)l * out.sn;
+  *reinterpret_cast<uint4*>(op + c) = make_uint4(pack2_bf16(v0.x, v0.y), pack2_bf16(v0.z, v0.w), pack2_bf16(v1.x, v1.y), pack2_bf16(v1.z, v1.w));
+}
+
 template <typename T>
 __global__ void cast_out_vec_kernel(const float* __restrict__ acc, int d, int n, int heads, View out, int acc_ld) {
   const int head = blockIdx.y;

@@ -223,11 +223,26 @@ static bool vec4_ok(const fastmax_tensor& t, int dtype) {
          ((size_t)t.stride_n * es) % al == 0;
 }
 
+// a bf16 view whose rows can take 8-element (128-bit) stores
+static bool bf16x8_ok(const fastmax_tensor& t, int dtype, int d) {
+  return dtype == FASTMAX_BF16 && (d & 7) == 0 && ((uintptr_t)t.ptr & 15) == 0 && (t.stride_b & 7) == 0 && (t.stride_h & 7) == 0 &&
+         (t.stride_n & 7) == 0;
+}
+
 int launch_cast_out(const fastmax_problem* pb, const float* acc, int n, const fastmax_tensor* out, cudaStream_t st, int acc_ld) {
   if (acc_ld <= 0) acc_ld = pb->d;
   const long long total = (long long)pb->batch * pb->heads * n * pb->d;
   if (total == 0) return FASTMAX_OK;
   const int threads = 256;
+  if (bf16x8_ok(*out, pb->dtype, pb->d) && (acc_ld & 3) == 0 && (long long)n * pb->d / 8 < (1ll << 30)) {
+    dim3 grid((unsigned)(((long long)n * (pb->d / 8) + threads - 1) / threads), (unsigned)(pb->batch * pb->heads));
+    {
+      LaunchScope ls(KK_CAST, st);
+      cast_out_bf16x8_kernel<<<grid, threads, 0, st>>>(acc, pb->d, n, pb->heads, to_view(*out), acc_ld);
+    }
+    FM_CUDA(cudaGetLastError());
+    return FASTMAX_OK;
+  }
   if (vec4_ok(*out, pb->dtype) && (long long)n * pb->d / 4 < (1ll << 30)) {
     dim3 grid((unsigned)(((long long)n * (pb->d / 4) + threads - 1) / threads), (unsigned)(pb->batch * pb->heads));
     {
@@ -257,6 +272,15 @@ int launch_finalize_fwd(const fastmax_problem* pb, const fastmax_forward_args* a
   const int ld = state_ld(pb->d);
   long long total = (long long)bh * pb->nq * pb->d;
   int threads = 256;
+  if (bf16x8_ok(a->o, pb->dtype, pb->d) && (long long)pb->nq * pb->d / 8 < (1ll << 30)) {
+    dim3 grid((unsigned)(((long long)pb->nq * (pb->d / 8) + threads - 1) / threads), (unsigned)bh);
+    {
+      LaunchScope ls(KK_FINALIZE, st);
+      finalize_fwd_bf16x8_kernel<<<grid, threads, 0, st>>>(oacc, ld, pb->d, pb->nq, pb->heads, to_view(a->o), to_view(a->g));
+    }
+    FM_CUDA(cudaGetLastError());
+    return FASTMAX_OK;
+  }
   if (vec4_ok(a->o, pb->dtype) && (long long)pb->nq * pb->d / 4 < (1ll << 30)) {
     dim3 grid((unsigned)(((long long)pb->nq * (pb->d / 4) + threads - 1) / threads), (unsigned)bh);
     {

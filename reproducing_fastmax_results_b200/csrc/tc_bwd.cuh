@@ -170,14 +170,16 @@ intra_bwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant_
       const int qb = qlim < CH ? (qlim < 0 ? 0 : (int)qlim) : CH;
       const long long klim = (long long)P.nk - pos0;
       const int kb = klim < CH ? (klim < 0 ? 0 : (int)klim) : CH;
+      // Plain stores, not reduce-adds: this kernel runs BEFORE the scans of the call (stream order) and its chunks
+      // cover every row of the three accumulators exactly once, so it also initialises them; the scans add on top.
       if (qb > qa)
-        bulk_reduce_add_f32(P.dq_acc + ((long long)head * P.nq + q0 + qa) * ACC_LD, stage + qa * ACC_LD, (uint32_t)(qb - qa) * (uint32_t)(ACC_LD * 4));
+        bulk_store(P.dq_acc + ((long long)head * P.nq + q0 + qa) * ACC_LD, stage + qa * ACC_LD, (uint32_t)(qb - qa) * (uint32_t)(ACC_LD * 4));
       if (kb > 0) {
-        bulk_reduce_add_f32(P.dk_acc + ((long long)head * P.nk + pos0) * ACC_LD, stage + CH * ACC_LD, (uint32_t)kb * (uint32_t)(ACC_LD * 4));
-        bulk_reduce_add_f32(P.dv_acc + ((long long)head * P.nk + pos0) * ACC_LD, stage + 2 * CH * ACC_LD, (uint32_t)kb * (uint32_t)(ACC_LD * 4));
+        bulk_store(P.dk_acc + ((long long)head * P.nk + pos0) * ACC_LD, stage + CH * ACC_LD, (uint32_t)kb * (uint32_t)(ACC_LD * 4));
+        bulk_store(P.dv_acc + ((long long)head * P.nk + pos0) * ACC_LD, stage + 2 * CH * ACC_LD, (uint32_t)kb * (uint32_t)(ACC_LD * 4));
       }
       bulk_commit_group();
-      bulk_wait_read_all();   // the staging rows stay valid until the copy engine has read them
+      bulk_wait_all();   // the rows are in global memory before the CTA retires (the scans' adds come later)
     }
   } else if (tid == 0) {
     atomicExch(&g_tc_status, 60);

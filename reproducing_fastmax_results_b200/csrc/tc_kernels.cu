@@ -512,8 +512,7 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
       !make_map_t(&tmqt, qt, bh, pb->nk, tokens_padded(pb->nk)) ||
       !make_map_t(&tmkt, kt, bh, pb->nk, tokens_padded(pb->nk)))
     return FASTMAX_TC_NOT_HANDLED;
-  cudaError_t e = cudaMemsetAsync(dqa, 0, L.total - L.dq, st);
-  if (e != cudaSuccess) return report_cuda_error(e);
+  cudaError_t e = cudaSuccess;   // (no memset of the accumulators: the intra-chunk kernel writes every row first)
   {
     const long long nrows = (long long)bh * pb->nq;
     const int threads = 256;
@@ -557,9 +556,10 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(tc::intra_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::IB_SMEM_BYTES);
   if (e != cudaSuccess) return report_cuda_error(e);
-  // Four independent kernels (they ADD into the accumulators with reduce operations): the intra-chunk kernel and
-  // the dv scan on the caller's stream, the dq and dk scans on side streams.  An accumulator is cast to its output
-  // as soon as its scan and the intra-chunk kernel are done, on the stream of its scan, so the casts overlap the
+  // The intra-chunk kernel goes first: it STORES its part into every row of the three accumulators (no memset).  It
+  // fills all SMs by itself (one CTA per SM), so nothing is lost by letting the scans wait for it.  The three scans
+  // then ADD on top with reduce operations, side by side: dv on the caller's stream, dq and dk on side streams.  An
+  // accumulator is cast to its output as soon as its scan is done, on that scan's stream, so the casts overlap the
   // tails of the scans that are still running.
   cudaStream_t ss[3];
   SideStreams* side = fork_streams(pb, st, 3, ss);
@@ -569,7 +569,11 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
     tc::intra_bwd_kernel<<<dim3(nch, 1, bh), tc::IB_THREADS, tc::IB_SMEM_BYTES, ss[0]>>>(tmq, tmk, tmv, tmdo, I);
   }
   e = cudaGetLastError();
-  if (e == cudaSuccess && side) e = cudaEventRecord(side->mid, ss[0]);
+  if (e == cudaSuccess && side) {
+    e = cudaEventRecord(side->mid, ss[0]);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ss[1], side->mid, 0);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ss[2], side->mid, 0);
+  }
   if (e != cudaSuccess) return report_cuda_error(e);
   {
     LaunchScope ls(KK_TC_BWD_Q, ss[1]);
@@ -594,10 +598,6 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
     tc::s2::scan_apply_kernel<true><<<dim3(5 * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmk, tmqt, tmdo, A);
   }
   e = cudaGetLastError();
-  if (e == cudaSuccess && side) {   // the side streams' casts also need the intra-chunk kernel's contributions
-    e = cudaStreamWaitEvent(ss[1], side->mid, 0);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(ss[2], side->mid, 0);
-  }
   if (e != cudaSuccess) return report_cuda_error(e);
   int rc = launch_cast_out(pb, dqa, pb->nq, &a->dq, ss[1], tc::ACC_LD);
   if (rc == FASTMAX_OK) rc = launch_cast_out(pb, dka, pb->nk, &a->dk, ss[2], tc::ACC_LD);
