@@ -313,7 +313,7 @@ static cudaError_t launch_transpose(const fastmax_tensor& x, int batch, int head
 // stream with an event and joined back into it, so the call as a whole is still ordered on the caller's stream.
 struct SideStreams {
   cudaStream_t s[3] = {nullptr, nullptr, nullptr};
-  cudaEvent_t fork = nullptr, mid = nullptr, join[3] = {nullptr, nullptr, nullptr};
+  cudaEvent_t fork = nullptr, mid = nullptr, aux = nullptr, join[3] = {nullptr, nullptr, nullptr};
   bool ok = false;
 };
 static SideStreams* side_streams() {
@@ -327,7 +327,8 @@ static SideStreams* side_streams() {
   if (!tried[dev]) {
     tried[dev] = true;
     bool good = cudaEventCreateWithFlags(&p.fork, cudaEventDisableTiming) == cudaSuccess &&
-                cudaEventCreateWithFlags(&p.mid, cudaEventDisableTiming) == cudaSuccess;
+                cudaEventCreateWithFlags(&p.mid, cudaEventDisableTiming) == cudaSuccess &&
+                cudaEventCreateWithFlags(&p.aux, cudaEventDisableTiming) == cudaSuccess;
     for (int i = 0; i < 3 && good; ++i)
       good = cudaStreamCreateWithFlags(&p.s[i], cudaStreamNonBlocking) == cudaSuccess &&
              cudaEventCreateWithFlags(&p.join[i], cudaEventDisableTiming) == cudaSuccess;
@@ -533,8 +534,6 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
                                                              pb->nq, pb->heads, nrows);
   }
   e = cudaGetLastError();
-  if (e == cudaSuccess) e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, pb->nk - pb->nq, qt, st);
-  if (e == cudaSuccess) e = launch_transpose(a->k, pb->batch, pb->heads, pb->nk, 0, kt, st);
   if (e != cudaSuccess) return report_cuda_error(e);
   // The chain-rule scans rebalance registers between their warp groups with setmaxnreg; that only terminates if
   // the CTA was launched with the register count the budget in tc_scan3.cuh assumes.  Otherwise the CUDA-core
@@ -561,8 +560,16 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   // then ADD on top with reduce operations, side by side: dv on the caller's stream, dq and dk on side streams.  An
   // accumulator is cast to its output as soon as its scan is done, on that scan's stream, so the casts overlap the
   // tails of the scans that are still running.
+  // The transposed copies are only read by the scans: they are made on the side streams while the intra-chunk
+  // kernel (which leaves the memory system idle) runs.
   cudaStream_t ss[3];
   SideStreams* side = fork_streams(pb, st, 3, ss);
+  if (side) {
+    e = launch_transpose(a->k, pb->batch, pb->heads, pb->nk, 0, kt, ss[1]);
+    if (e == cudaSuccess) e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, pb->nk - pb->nq, qt, ss[2]);
+    if (e == cudaSuccess) e = cudaEventRecord(side->aux, ss[2]);   // the dv scan on the caller's stream reads q^T too
+    if (e != cudaSuccess) return report_cuda_error(e);
+  }
   {
     tc::IntraBwdParams I{dqa, dka, dva, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, c0, c1, c2};
     LaunchScope ls(KK_TC_INTRA_BWD, ss[0]);
@@ -573,6 +580,10 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
     e = cudaEventRecord(side->mid, ss[0]);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(ss[1], side->mid, 0);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(ss[2], side->mid, 0);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ss[0], side->aux, 0);
+  } else if (e == cudaSuccess) {   // one stream: the copies simply follow
+    e = launch_transpose(a->k, pb->batch, pb->heads, pb->nk, 0, kt, st);
+    if (e == cudaSuccess) e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, pb->nk - pb->nq, qt, st);
   }
   if (e != cudaSuccess) return report_cuda_error(e);
   {
