@@ -455,6 +455,18 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   return launch_finalize_fwd(pb, a, oacc, st);
 }
 
+static int device_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 static bool tc_backward_supported(const fastmax_problem* pb, const fastmax_backward_args* a) {
   if (pb->flags & FASTMAX_FLAG_NO_TENSOR_CORES) return false;
   if (pb->dtype != FASTMAX_BF16 || pb->d != 64 || pb->order != 2 || !pb->causal) return false;
@@ -553,7 +565,7 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(tc::s3::scan_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s3::SMEM_BYTES);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(tc::intra_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::IB_SMEM_BYTES);
+    e = cudaFuncSetAttribute(tc::intra_bwd_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::IP_SMEM_BYTES);
   if (e != cudaSuccess) return report_cuda_error(e);
   // The intra-chunk kernel goes first: it STORES its part into every row of the three accumulators (no memset).  It
   // fills all SMs by itself (one CTA per SM), so nothing is lost by letting the scans wait for it.  The three scans
@@ -573,7 +585,9 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   {
     tc::IntraBwdParams I{dqa, dka, dva, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, c0, c1, c2};
     LaunchScope ls(KK_TC_INTRA_BWD, ss[0]);
-    tc::intra_bwd_kernel<<<dim3(nch, 1, bh), tc::IB_THREADS, tc::IB_SMEM_BYTES, ss[0]>>>(tmq, tmk, tmv, tmdo, I);
+    const int nitems = nch * bh;
+    const int ctas = nitems < device_sms() ? nitems : device_sms();   // persistent: one CTA per SM walks the items
+    tc::intra_bwd_pipe_kernel<<<dim3(ctas), tc::IP_THREADS, tc::IP_SMEM_BYTES, ss[0]>>>(tmq, tmk, tmv, tmdo, I, nch, nitems);
   }
   e = cudaGetLastError();
   if (e == cudaSuccess && side) {
