@@ -56,6 +56,27 @@ DRAM_TRAFFIC = {
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
+# The contract is ONE JSON line on stdout.  Native libraries write there too (NCCL prints its version banner on file
+# descriptor 1 when the process group comes up), so descriptor 1 is pointed at stderr for the whole run and the
+# result line goes to a private copy of the original stdout.
+_RESULT_FD = None
+
+
+def claim_stdout():
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    if _RESULT_FD is None:
+        print(json.dumps(line), flush=True)
+    else:
+        os.write(_RESULT_FD, (json.dumps(line) + "\n").encode())
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -250,7 +271,7 @@ def run_reference_arm(args):
                          "sample": cpu_sample_text(args.workload, n_sample, heads)},
         "e2e": {"value": value, "unit": "Mtokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
     return 0
 
 
@@ -330,7 +351,7 @@ def run_sequence_sharded(args, torch, dist, dev, rank, world):
                                  "TF32 operands miss the 1e-4 tolerance", "traffic": None},
             "kernels": kernels, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
     return 0
@@ -418,7 +439,7 @@ def run_decode(args, torch, dist, dev, rank, world):
                                         "frac": 2.0 * state_bytes / (ms_graph * 1e-3) / 1e9 / pk["hbm_gbs"]}},
             "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
     return 0
@@ -443,6 +464,7 @@ def main():
     ap.add_argument("--mode", default="fwd_bwd", choices=["fwd_bwd", "fwd"],
                     help="fwd: time the forward call only (profiling aid; the headline metric is fwd_bwd)")
     args = ap.parse_args()
+    claim_stdout()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = max(args.warmup, 1)
     if args.impl == "reference":
@@ -462,7 +484,6 @@ def main():
     if world > 1:
         import torch.distributed as dist
 
-        os.environ.setdefault("NCCL_DEBUG", "WARN")  # keep NCCL's version banner off stdout: rank 0 prints ONE JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     if args.workload in SEQUENCE_SHARDED:
@@ -653,7 +674,7 @@ def main():
             "roofline": roofline, "whole_step": whole, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
     return 0
