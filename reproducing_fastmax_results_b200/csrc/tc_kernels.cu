@@ -312,6 +312,7 @@ static cudaError_t launch_transpose(const fastmax_tensor& x, int batch, int head
 // SMs; side by side their last waves overlap).  Created once per device, on first use; forked from the caller's
 // stream with an event and joined back into it, so the call as a whole is still ordered on the caller's stream.
 struct SideStreams {
+  std::mutex use;   // held by a call from its fork to its join: the events and streams below are shared per device
   cudaStream_t s[3] = {nullptr, nullptr, nullptr};
   cudaEvent_t fork = nullptr, mid = nullptr, aux = nullptr, join[3] = {nullptr, nullptr, nullptr};
   bool ok = false;
@@ -338,11 +339,17 @@ static SideStreams* side_streams() {
 }
 // Streams for `n` independent kernels: out[0] is the caller's stream; out[1..] are side streams that wait for
 // everything enqueued on the caller's stream so far (or the caller's stream itself when side streams are off).
-static SideStreams* fork_streams(const fastmax_problem* pb, cudaStream_t st, int n, cudaStream_t* out) {
+// `lock` keeps the device's side streams for this call until it goes out of scope in the caller (after the join has
+// been enqueued): a stream wait takes the event's record of that moment, so two host threads interleaving their
+// record / wait pairs on the shared events would order their kernels wrongly.
+static SideStreams* fork_streams(const fastmax_problem* pb, cudaStream_t st, int n, cudaStream_t* out,
+                                 std::unique_lock<std::mutex>& lock) {
   for (int i = 0; i < n; ++i) out[i] = st;
   if ((pb->flags & FASTMAX_FLAG_SINGLE_STREAM) || profiling_on()) return nullptr;
   SideStreams* p = side_streams();
-  if (!p || cudaEventRecord(p->fork, st) != cudaSuccess) return nullptr;
+  if (!p) return nullptr;
+  lock = std::unique_lock<std::mutex>(p->use);
+  if (cudaEventRecord(p->fork, st) != cudaSuccess) return nullptr;
   for (int i = 1; i < n; ++i) {
     if (cudaStreamWaitEvent(p->s[i - 1], p->fork, 0) != cudaSuccess) return nullptr;
     out[i] = p->s[i - 1];
@@ -437,7 +444,8 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   if (e != cudaSuccess) return report_cuda_error(e);
   // the scan and the intra-chunk kernel both ADD into the O' accumulator: independent, side by side
   cudaStream_t ss[2];
-  SideStreams* side = fork_streams(pb, st, 2, ss);
+  std::unique_lock<std::mutex> side_lock;
+  SideStreams* side = fork_streams(pb, st, 2, ss, side_lock);
   {
     LaunchScope ls(KK_TC_FWD, ss[0]);
     tc::s2::ApplyParams A{oacc, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, 0, P.nchunks, P.c0, P.c1, P.c2, a->state_out};
@@ -575,7 +583,8 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   // The transposed copies are only read by the scans: they are made on the side streams while the intra-chunk
   // kernel (which leaves the memory system idle) runs.
   cudaStream_t ss[3];
-  SideStreams* side = fork_streams(pb, st, 3, ss);
+  std::unique_lock<std::mutex> side_lock;
+  SideStreams* side = fork_streams(pb, st, 3, ss, side_lock);
   if (side) {
     e = launch_transpose(a->k, pb->batch, pb->heads, pb->nk, 0, kt, ss[1]);
     if (e == cudaSuccess) e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, pb->nk - pb->nq, qt, ss[2]);

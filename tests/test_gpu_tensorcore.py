@@ -213,3 +213,48 @@ def test_order1_strided_views_and_other_coefficients():
         o_ref, g_ref = orc.fastmax_naive(host(q[b, h]), host(k[b, h]), host(v[b, h]), False, poly)
         assert orc.max_norm_err(host(o[b, h]), o_ref) < 2e-2
         assert orc.max_norm_err(host(gg[b, h]), g_ref) < 2e-3
+
+
+def test_two_host_threads_on_their_own_streams():
+    """Two host threads issue calls on the same device at the same time, each on its own stream.  The library's
+    internal side streams and events are shared per device; the calls must still be ordered correctly."""
+    import threading
+
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, N, D = 2, 16, 640, 64
+    it = 1.0 / (2.0 * math.sqrt(D))
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    sets = [[torch.randn(B, H, N, D, device="cuda", generator=gen).bfloat16() for _ in range(4)] for _ in range(2)]
+
+    def run(x):
+        q, k, v, do = x
+        o, g, _ = L.forward(q, k, v, True, it, order=2)
+        return (o,) + tuple(L.backward(q, k, v, o, g, do, True, it, order=2)[:3])
+
+    refs = [[t.clone() for t in run(x)] for x in sets]
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker(i):
+        try:
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                for _ in range(8):
+                    outs = run(sets[i])
+                    stream.synchronize()
+                    for a, b in zip(outs, refs[i]):
+                        err = float((a.float() - b.float()).abs().max()) / float(b.float().abs().max())
+                        if not err < 5e-3:
+                            errors.append((i, err))
+        except Exception as e:  # noqa: BLE001 - reported through the list
+            errors.append((i, repr(e)))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    torch.cuda.synchronize()
+    L.check_status()
+    assert not errors, errors
