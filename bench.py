@@ -655,7 +655,7 @@ def main():
                                "api": "FastMax.apply + backward on the whole batch between one copy-in and one copy-out"}}
 
     cpu = None
-    if rank == 0 and not args.no_cpu and world >= 1:
+    if rank == 0 and not args.no_cpu and world == 1:   # the CPU leg runs at N = 1 only
         cpu_sample(args.workload, args.cpu_tokens, 1)  # page the CPU kernels in
         sec, head_tokens, threads = cpu_sample(args.workload, args.cpu_tokens, args.cpu_heads)
         cpu = {"value": (head_tokens / H) / sec / 1e6, "unit": "Mtokens/s", "cores": threads, "kind": "port",
