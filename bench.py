@@ -43,8 +43,11 @@ WORKLOADS = {
     # incremental decoding: one new token per (batch, head) per step against the carried state (N = prefix length is
     # irrelevant to the cost; 512 head states = 330 MB, larger than L2)
     "decode_bf16_p2_B32_H16_D64": (32, 16, 1, 64, 2, True, "bf16", 1.0),
+    # the q / k normalisation stage alone (forward of one tensor and its backward), config-2 sized: HBM-bound
+    "norm_bf16_B8_H16_N4096_D64": (8, 16, 4096, 64, 2, True, "bf16", 1.0),
 }
 SEQUENCE_SHARDED = {"cfg3_f32_causal_p2_B1_H8_N131072_D32"}
+NORMALIZE = {"norm_bf16_B8_H16_N4096_D64"}
 DECODE = {"decode_bf16_p2_B32_H16_D64"}
 DEFAULT = "cfg2_bf16_causal_p2_B8_H16_N4096_D64"
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch from the ncu captures summarised under profiles/ (taken
@@ -446,6 +449,79 @@ def run_decode(args, torch, dist, dev, rank, world):
 
 
 # ----------------------------------------------------------------------------------------------------
+# GPU arm, normalisation workload: y = lim (x - mean_d x) / max_token ||x - mean_d x|| of one tensor and its backward
+# ----------------------------------------------------------------------------------------------------
+def run_normalize(args, torch, dist, dev, rank, world):
+    from reproducing_fastmax_results_b200 import _lib
+
+    B, H, N, D, order, causal, dtype_name, scale = WORKLOADS[args.workload]
+    dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    x, dy = ((torch.randn(B, H, N, D, device=dev, generator=gen) * scale).to(dtype) for _ in range(2))
+    lib = _lib.load()
+
+    def step():
+        y, stats = _lib.normalize_forward(x)
+        return _lib.normalize_backward(y, dy, stats)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(torch.cuda.current_device())
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.fastmax_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    launches = lib.fastmax_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    _lib.profile(True)
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    _lib.profile(False)
+    kernels = {name: {"ms_per_launch": ms / cnt, "launches_per_step": cnt / args.steps, "ms_per_step": ms / args.steps}
+               for name, (ms, cnt) in _lib.profile_collect().items()}
+    if rank == 0:
+        pk = peaks()
+        nbytes = x.numel() * x.element_size()
+        bytes_alg = 5 * nbytes   # forward: read x, write y; backward: read y and dy, write dx
+        gbs = bytes_alg / (ms_step * 1e-3) / 1e9
+        emit({
+            "metric": "fastmax_normalize_fwd_bwd_mtokens_per_s", "value": world * B * N / (ms_step * 1e-3) / 1e6,
+            "unit": "Mtokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_name + " tensors, f32 statistics",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": B, "heads": H, "seq_len": N, "head_dim": D,
+                       "parallelism": f"batch x head sharding, {world} rank(s), no collective",
+                       "l2": "x, y, dy, dx are %d MB each; no explicit flush" % (nbytes >> 20)},
+            "roofline": {"kernel": "normalize forward + backward (%s)" % ", ".join(sorted(kernels)), "bound": "hbm",
+                         "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                         "peak_source": pk["_source"],
+                         "note": "algorithmic bytes: forward reads x and writes y, backward reads y and dy and writes dx; the "
+                                 "second read of x by the forward's statistics pass is not algorithmic", "traffic": None},
+            "kernels": kernels, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks,
+        })
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+# ----------------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------------
 def main():
@@ -490,6 +566,8 @@ def main():
         return run_sequence_sharded(args, torch, dist, dev, rank, world)
     if args.workload in DECODE:
         return run_decode(args, torch, dist, dev, rank, world)
+    if args.workload in NORMALIZE:
+        return run_normalize(args, torch, dist, dev, rank, world)
     B, H, N, D, order, causal, dtype_name, scale = WORKLOADS[args.workload]
     dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
     inv_temp = 1.0 / (8.0 * math.sqrt(D))

@@ -250,6 +250,178 @@ __global__ void norm_apply_kernel(View x, View y, int d, int n, int heads, const
   for (int c = lane; c < d; c += 32) yp[c] = from_float<T>((to_float<T>(xp[c]) - mean) * sc);
 }
 
+// ---- 128-bit variants of the four normalisation kernels (head dim a multiple of 8, 16-byte aligned rows) ----
+// LPR = d / 8 lanes share a row, every lane moves eight elements per access, a warp covers 32 / LPR rows.  Row sums
+// go over the LPR lanes with shuffles; when all rows of a warp belong to one head (the usual case) the warp issues
+// ONE atomic for its rows instead of one per row.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 r = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack2_bf16(v[0], v[1]), pack2_bf16(v[2], v[3]), pack2_bf16(v[4], v[5]), pack2_bf16(v[6], v[7]));
+}
+template <int LPR>
+__device__ __forceinline__ float row_sum(float x) {
+#pragma unroll
+  for (int k = LPR / 2; k > 0; k >>= 1) x += __shfl_xor_sync(0xffffffffu, x, k);
+  return x;
+}
+// row of this thread: blockIdx.y is the (batch, head), blockIdx.x walks the head's tokens, so a warp never spans heads
+// and no division is needed
+struct RowOfLane {
+  int l, head, b, h, c;
+  bool valid, one_head;
+};
+constexpr int NORM_ITERS = 8;   // row tiles per block of the two reducing kernels: one atomic per 8 x 256 threads
+template <int LPR>
+__device__ __forceinline__ RowOfLane row_of_lane(int n, int heads, int it = 0, int iters = 1) {
+  RowOfLane r;
+  const int t = (blockIdx.x * iters + it) * blockDim.x + threadIdx.x;
+  r.l = t / LPR;
+  r.c = (t - r.l * LPR) * 8;
+  r.valid = r.l < n;
+  if (!r.valid) r.l = 0;
+  r.head = blockIdx.y;
+  r.b = r.head / heads;
+  r.h = r.head - r.b * heads;
+  r.one_head = true;
+  return r;
+}
+
+template <typename T, int LPR>
+__global__ void norm_stats_vec_kernel(View x, int n, int heads, unsigned long long* stats, long long nrows) {
+  constexpr int D = 8 * LPR;
+  __shared__ unsigned long long part[8];
+  unsigned long long best = 0ull;
+  int head = 0;
+  for (int it = 0; it < NORM_ITERS; ++it) {
+    const RowOfLane r = row_of_lane<LPR>(n, heads, it, NORM_ITERS);
+    head = r.head;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    if (r.valid) load8<T>(reinterpret_cast<const T*>(x.ptr) + (long long)r.b * x.sb + (long long)r.h * x.sh + (long long)r.l * x.sn + r.c, v);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += v[i];
+    const float mean = row_sum<LPR>(s) / (float)D;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q += (v[i] - mean) * (v[i] - mean);
+    q = row_sum<LPR>(q);
+    if (r.valid && r.c == 0) {
+      const unsigned long long packed = ((unsigned long long)__float_as_uint(q) << 32) | (unsigned long long)(0xffffffffu - (unsigned)r.l);
+      best = packed > best ? packed : best;
+    }
+  }
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) {
+    const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, k);
+    best = o > best ? o : best;
+  }
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) best = part[i] > best ? part[i] : best;
+    if (best != 0ull) atomicMax(stats + head, best);
+  }
+}
+
+template <typename T, int LPR>
+__global__ void norm_apply_vec_kernel(View x, View y, int n, int heads, const unsigned long long* stats, float lim, long long nrows) {
+  constexpr int D = 8 * LPR;
+  const RowOfLane r = row_of_lane<LPR>(n, heads);
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = 0.f;
+  if (r.valid) load8<T>(reinterpret_cast<const T*>(x.ptr) + (long long)r.b * x.sb + (long long)r.h * x.sh + (long long)r.l * x.sn + r.c, v);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s += v[i];
+  const float mean = row_sum<LPR>(s) / (float)D;
+  if (!r.valid) return;
+  const float sc = lim / sqrtf(__uint_as_float((unsigned)(stats[r.head] >> 32)));
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = (v[i] - mean) * sc;
+  store8<T>(reinterpret_cast<T*>(const_cast<void*>(y.ptr)) + (long long)r.b * y.sb + (long long)r.h * y.sh + (long long)r.l * y.sn + r.c, v);
+}
+
+template <typename T, int LPR>
+__global__ void norm_bwd_dot_vec_kernel(View y, View dy, int n, int heads, float* scratch, long long nrows) {
+  __shared__ float part[8];
+  float q = 0.f;
+  int head = 0;
+  for (int it = 0; it < NORM_ITERS; ++it) {
+    const RowOfLane r = row_of_lane<LPR>(n, heads, it, NORM_ITERS);
+    head = r.head;
+    if (r.valid) {
+      float a[8], g[8];
+      load8<T>(reinterpret_cast<const T*>(y.ptr) + (long long)r.b * y.sb + (long long)r.h * y.sh + (long long)r.l * y.sn + r.c, a);
+      load8<T>(reinterpret_cast<const T*>(dy.ptr) + (long long)r.b * dy.sb + (long long)r.h * dy.sh + (long long)r.l * dy.sn + r.c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q += a[i] * g[i];
+    }
+  }
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) q += __shfl_xor_sync(0xffffffffu, q, k);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = q;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) q += part[i];
+    atomicAdd(scratch + head, q);
+  }
+}
+
+template <typename T, int LPR>
+__global__ void norm_bwd_apply_vec_kernel(View y, View dy, View dx, int n, int heads, const unsigned long long* stats,
+                                          const float* scratch, float lim, long long nrows) {
+  constexpr int D = 8 * LPR;
+  const RowOfLane r = row_of_lane<LPR>(n, heads);
+  float a[8], g[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a[i] = g[i] = 0.f;
+  if (r.valid) {
+    load8<T>(reinterpret_cast<const T*>(y.ptr) + (long long)r.b * y.sb + (long long)r.h * y.sh + (long long)r.l * y.sn + r.c, a);
+    load8<T>(reinterpret_cast<const T*>(dy.ptr) + (long long)r.b * dy.sb + (long long)r.h * dy.sh + (long long)r.l * dy.sn + r.c, g);
+  }
+  float sg = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sg += g[i];
+  const float gmean = row_sum<LPR>(sg) / (float)D;
+  if (!r.valid) return;
+  const unsigned long long st = stats[r.head];
+  const float m = sqrtf(__uint_as_float((unsigned)(st >> 32)));
+  const int am = (int)(0xffffffffu - (unsigned)(st & 0xffffffffu));
+  const float sc = lim / m;
+  const float extra = (r.l == am) ? -scratch[r.head] / (lim * m) : 0.f;
+  float o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = sc * (g[i] - gmean) + extra * a[i];
+  store8<T>(reinterpret_cast<T*>(const_cast<void*>(dx.ptr)) + (long long)r.b * dx.sb + (long long)r.h * dx.sh + (long long)r.l * dx.sn + r.c, o);
+}
+
 // per head: scratch[head] = sum_{l,c} dy * y      (y = normalised output; x - mean = y * m / lim)
 template <typename T>
 __global__ void norm_bwd_dot_kernel(View y, View dy, int d, int n, int heads, float* scratch, long long nrows) {

@@ -3,6 +3,7 @@
 #include <atomic>
 #include <mutex>
 #include <vector>
+#include <initializer_list>
 #include <cstdio>
 #include <cstring>
 
@@ -648,6 +649,30 @@ int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args*
 // ---------------------------------------------------------------------------------------------------
 // normalisation
 // ---------------------------------------------------------------------------------------------------
+// 128-bit normalisation kernels: head dim 16 / 32 / 64 and every view aligned for 16-byte row pieces
+static bool norm_vec_ok(int d, int dtype, std::initializer_list<const fastmax_tensor*> views) {
+  if (d != 16 && d != 32 && d != 64) return false;
+  const size_t es = dtype == FASTMAX_F32 ? 4 : 2;
+  for (const fastmax_tensor* t : views)
+    if (((uintptr_t)t->ptr & 15) || ((size_t)t->stride_b * es) % 16 || ((size_t)t->stride_h * es) % 16 || ((size_t)t->stride_n * es) % 16)
+      return false;
+  return true;
+}
+#define FM_NORM_VEC(KERNEL, ITERS, ...)                                                                 \
+  do {                                                                                                  \
+    const dim3 vblocks((unsigned)(((long long)n * (d / 8) + threads * (ITERS) - 1) / (threads * (ITERS))),  \
+                       (unsigned)(batch * heads));                                                      \
+    if (dtype == FASTMAX_F32) {                                                                         \
+      if (d == 64) KERNEL<float, 8><<<vblocks, threads, 0, st>>>(__VA_ARGS__);                          \
+      else if (d == 32) KERNEL<float, 4><<<vblocks, threads, 0, st>>>(__VA_ARGS__);                     \
+      else KERNEL<float, 2><<<vblocks, threads, 0, st>>>(__VA_ARGS__);                                  \
+    } else {                                                                                            \
+      if (d == 64) KERNEL<__nv_bfloat16, 8><<<vblocks, threads, 0, st>>>(__VA_ARGS__);                  \
+      else if (d == 32) KERNEL<__nv_bfloat16, 4><<<vblocks, threads, 0, st>>>(__VA_ARGS__);             \
+      else KERNEL<__nv_bfloat16, 2><<<vblocks, threads, 0, st>>>(__VA_ARGS__);                          \
+    }                                                                                                   \
+  } while (0)
+
 int32_t fastmax_normalize_forward(int32_t batch, int32_t heads, int32_t n, int32_t d, int32_t dtype, float lim,
                                   const fastmax_tensor* x, const fastmax_tensor* y, uint64_t* stats, void* stream) {
   if (!x || !y || !x->ptr || !y->ptr || !stats || batch <= 0 || heads <= 0 || n < 0 || d <= 0 || !(lim > 0.f))
@@ -660,6 +685,18 @@ int32_t fastmax_normalize_forward(int32_t batch, int32_t heads, int32_t n, int32
   int threads = 256;
   unsigned blocks = (unsigned)((nrows * 32 + threads - 1) / threads);
   unsigned long long* sp = reinterpret_cast<unsigned long long*>(stats);
+  if (norm_vec_ok(d, dtype, {x, y}) && (long long)batch * heads <= 65535) {
+    {
+      LaunchScope ls(KK_NORMALIZE, st);
+      FM_NORM_VEC(norm_stats_vec_kernel, NORM_ITERS, to_view(*x), n, heads, sp, nrows);
+    }
+    {
+      LaunchScope ls(KK_NORMALIZE, st);
+      FM_NORM_VEC(norm_apply_vec_kernel, 1, to_view(*x), to_view(*y), n, heads, sp, lim, nrows);
+    }
+    FM_CUDA(cudaGetLastError());
+    return FASTMAX_OK;
+  }
   {
     LaunchScope ls(KK_NORMALIZE, st);
     if (dtype == FASTMAX_F32)
@@ -692,6 +729,18 @@ int32_t fastmax_normalize_backward(int32_t batch, int32_t heads, int32_t n, int3
   int threads = 256;
   unsigned blocks = (unsigned)((nrows * 32 + threads - 1) / threads);
   const unsigned long long* sp = reinterpret_cast<const unsigned long long*>(stats);
+  if (norm_vec_ok(d, dtype, {y, dy, dx}) && (long long)batch * heads <= 65535) {
+    {
+      LaunchScope ls(KK_NORMALIZE, st);
+      FM_NORM_VEC(norm_bwd_dot_vec_kernel, NORM_ITERS, to_view(*y), to_view(*dy), n, heads, scratch, nrows);
+    }
+    {
+      LaunchScope ls(KK_NORMALIZE, st);
+      FM_NORM_VEC(norm_bwd_apply_vec_kernel, 1, to_view(*y), to_view(*dy), to_view(*dx), n, heads, sp, scratch, lim, nrows);
+    }
+    FM_CUDA(cudaGetLastError());
+    return FASTMAX_OK;
+  }
   {
     LaunchScope ls(KK_NORMALIZE, st);
     if (dtype == FASTMAX_F32)
