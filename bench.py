@@ -33,7 +33,6 @@ if ROOT not in sys.path:
 WORKLOADS = {
     # name: (B, H, N, D, order, causal, dtype, input scale)
     "cfg2_bf16_causal_p2_B8_H16_N4096_D64": (8, 16, 4096, 64, 2, True, "bf16", 1.0),
-    "small_bf16_causal_p2_B2_H4_N1024_D64": (2, 4, 1024, 64, 2, True, "bf16", 1.0),
     # profiling case: same per-CTA work as config 2, a few GB on the device, inputs (134 MB) larger than L2
     "prof_bf16_causal_p2_B4_H16_N4096_D64": (4, 16, 4096, 64, 2, True, "bf16", 1.0),
     # BASELINE config 3: one long causal sequence, cut into contiguous pieces across the ranks (strong scaling)
@@ -50,12 +49,19 @@ SEQUENCE_SHARDED = {"cfg3_f32_causal_p2_B1_H8_N131072_D32"}
 NORMALIZE = {"norm_bf16_B8_H16_N4096_D64"}
 DECODE = {"decode_bf16_p2_B32_H16_D64"}
 DEFAULT = "cfg2_bf16_causal_p2_B8_H16_N4096_D64"
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch from the ncu captures summarised under profiles/ (taken
-# on the prof_ workload: 64 heads x 4096 tokens); bench.py scales them by head-tokens to its own workload.
-DRAM_TRAFFIC = {
-    name: {"bytes_per_launch": b, "head_tokens": 64 * 4096, "source": "profiles/ncu_tc_scans_prof_workload.md"}
-    for name, b in (("tc_scan_fwd", 208.65e6), ("tc_scan_bwd_q", 257.25e6), ("tc_scan_bwd_kv", 258.31e6), ("tc_scan_bwd_dv", 218.70e6))
-}
+def dram_traffic():
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the scan kernels, from the machine-readable record
+    written with the ncu capture (profiles/dram_traffic.json: kernel -> bytes per launch, the head-tokens of the
+    captured workload and the summary file that documents the capture).  bench.py scales by head-tokens."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f)["kernels"]
+    except (OSError, KeyError, ValueError):
+        return {}
+
+
+DRAM_TRAFFIC = dram_traffic()
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -221,6 +227,70 @@ def cpu_sample_text(workload, n_sample, heads):
             f"{heads} of {B * H} heads, {n_sample} of {N} tokens each, D={D}; head-tokens / H = metric tokens")
 
 
+REFERENCE_EINOPS = os.path.join(ROOT, "oracle", "_ref", "fastattention_einops.py")
+
+
+def reference_einops():
+    """The reference's own CPU implementation (attention_mechanisms/fastattention_einops.py, placed unmodified under
+    oracle/_ref/ by baseline/vendor_reference.py), or None when it has not been placed."""
+    if not os.path.exists(REFERENCE_EINOPS):
+        return None
+    import importlib.util
+
+    name = "fastmax_reference_einops"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, REFERENCE_EINOPS)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def cpu_sample_reference(workload, n_sample=512, heads=1):
+    """Forward + backward of the reference's einops Fastmax (its factorised forward and hand-derived factorised
+    backward, fastattention_einops.py:42-182) on `heads` heads of n_sample tokens, one after the other.
+    Returns (seconds, head-tokens, threads)."""
+    import torch
+
+    ein = reference_einops()
+    B, H, N, D, order, causal, dtype, scale = WORKLOADS[workload]
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    total = 0.0
+    for _ in range(heads):
+        q, k, v, do = (torch.randn(1, 1, n_sample, D, generator=g) * scale for _ in range(4))
+        if dtype == "bf16":
+            q, k, v, do = (t.bfloat16().float() for t in (q, k, v, do))
+        q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+        t0 = time.perf_counter()
+        o = ein.fastmax(q, k, v, mask=causal, normalize_term=8, tensors_normalized=False, p=order)
+        o.backward(do)
+        total += time.perf_counter() - t0
+    return total, heads * n_sample, threads
+
+
+def cpu_baseline_record(workload, n_sample, heads):
+    """CPU figure for the JSON line: the reference's einops code when it is present (kind "reference"), with the oracle's
+    restatement as a second figure; the restatement alone (kind "port") otherwise."""
+    B, H, N, D, order, causal, dtype, scale = WORKLOADS[workload]
+    cpu_sample(workload, min(n_sample, 256), 1)  # page the CPU kernels in
+    sec_p, ht_p, threads = cpu_sample(workload, n_sample, heads if reference_einops() is None else max(1, heads // 4))
+    port = {"value": (ht_p / H) / sec_p / 1e6, "unit": "Mtokens/s", "cores": threads, "kind": "port", "seconds": sec_p,
+            "sample": cpu_sample_text(workload, n_sample, ht_p // n_sample)}
+    if reference_einops() is None:
+        return port
+    ref_heads = max(1, heads // 12)
+    cpu_sample_reference(workload, 64, 1)
+    sec, ht, threads = cpu_sample_reference(workload, n_sample, ref_heads)
+    return {"value": (ht / H) / sec / 1e6, "unit": "Mtokens/s", "cores": threads, "kind": "reference", "seconds": sec,
+            "sample": f"the reference's fastattention_einops.fastmax (mask={causal}, p={order}, normalize_term=8) forward + backward "
+                      f"on {ref_heads} of {B * H} heads, {n_sample} of {N} tokens each, D={D} (its memory is O(N D^3) per head); "
+                      "head-tokens / H = metric tokens",
+            "port": port}
+
+
 def bind_host_near_gpu(torch, index):
     """Pins this process to the CPU cores that sit on the GPU's PCIe root (sysfs local_cpulist), so that the pinned
     host buffers it allocates afterwards are first touched on that NUMA node.  Returns the core list or None."""
@@ -247,31 +317,37 @@ def bind_host_near_gpu(torch, index):
 
 
 def run_reference_arm(args):
-    """`--impl reference`: the reference's CPU algorithm (oracle port) timed on the host, rank 0 only."""
+    """`--impl reference`: the reference's CPU implementation of the path timed on the host, rank 0 only: its own
+    fastattention_einops.py when present under oracle/_ref/, else the oracle's restatement (kind "port")."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
     B, H, N, D, order, causal, dtype, scale = WORKLOADS[args.workload]
-    n_sample, heads = args.cpu_tokens, args.ref_heads
-    for _ in range(args.warmup):
-        cpu_sample(args.workload, n_sample, 1)
+    use_ref = reference_einops() is not None
+    n_sample = args.ref_tokens if use_ref else args.cpu_tokens
+    heads = 1 if use_ref else args.ref_heads
+    sample = cpu_sample_reference if use_ref else cpu_sample
+    for _ in range(min(args.warmup, 1)):
+        sample(args.workload, n_sample, 1)
     times = []
     threads = 1
     head_tokens = heads * n_sample
     for _ in range(args.steps):
-        t, head_tokens, threads = cpu_sample(args.workload, n_sample, heads)
+        t, head_tokens, threads = sample(args.workload, n_sample, heads)
         times.append(t)
     sec = sum(times) / len(times)
     # metric tokens carry all H heads: one head of n_sample tokens is n_sample / H metric tokens
     value = (head_tokens / H) / sec / 1e6
+    text = (f"fastattention_einops.fastmax forward + backward, {heads} of {B * H} heads x {n_sample} of {N} tokens per step"
+            if use_ref else cpu_sample_text(args.workload, n_sample, heads))
     line = {
         "impl": "reference",
         "metric": "fastmax_fwd_bwd_mtokens_per_s", "value": value, "unit": "Mtokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "sample": f"{heads} head(s) x {n_sample} tokens per step"},
-        "cpu_baseline": {"value": value, "unit": "Mtokens/s", "cores": threads, "kind": "port", "seconds": sec,
-                         "sample": cpu_sample_text(args.workload, n_sample, heads)},
+        "cpu_baseline": {"value": value, "unit": "Mtokens/s", "cores": threads, "kind": "reference" if use_ref else "port",
+                         "seconds": sec, "sample": text},
         "e2e": {"value": value, "unit": "Mtokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     emit(line)
@@ -282,27 +358,67 @@ def run_reference_arm(args):
 # GPU arm, sequence-sharded workload: every rank owns N/world consecutive tokens of all heads; the ranks
 # exchange the moment states (forward: exclusive prefix, backward: exclusive suffix) with one all_gather each.
 # ----------------------------------------------------------------------------------------------------
-def run_sequence_sharded(args, torch, dist, dev, rank, world):
+def _exact_rows_fp64(torch, q_rows, rows, k, v, inv_temp, o_rows=None, g_rows=None, do_rows=None):
+    """Exact float64 evaluation on the device of sampled causal query rows (global positions `rows`) against ALL keys
+    k, v (b, h, N, d): returns o rows, and dq rows when o/g/dO rows are given.  O(N d) per row, no N x N matrix."""
+    kd, vd = k.double(), v.double()
+    qd = q_rows.double()                                                  # (b, h, r, d)
+    s = torch.einsum("bhrd,bhnd->bhrn", qd, kd) * inv_temp
+    vis = (torch.arange(k.shape[2], device=k.device)[None, :] <= rows[:, None]).double()
+    a = (1.0 + s + 0.5 * s * s) * vis
+    g = a.sum(-1)
+    o = torch.einsum("bhrn,bhnd->bhrd", a, vd) / g[..., None]
+    if do_rows is None:
+        return o, None
+    dod = do_rows.double()
+    dog = dod / g[..., None]
+    dg = -(dod * o).sum(-1) / g
+    da = torch.einsum("bhrd,bhnd->bhrn", dog, vd) + dg[..., None]
+    ds = da * (1.0 + s) * vis
+    return o, torch.einsum("bhrn,bhnd->bhrd", ds, kd) * inv_temp
+
+
+def _exact_cols_fp64(torch, k_cols, v_cols, cols, q, o, g, do, inv_temp):
+    """Exact float64 dk, dv of sampled key positions `cols` against ALL queries (b, h, N, d)."""
+    qd, od, dod, gd = q.double(), o.double(), do.double(), g.double()
+    kd, vd = k_cols.double(), v_cols.double()
+    s = torch.einsum("bhnd,bhcd->bhnc", qd, kd) * inv_temp
+    vis = (cols[None, :] <= torch.arange(q.shape[2], device=q.device)[:, None]).double()
+    a = (1.0 + s + 0.5 * s * s) * vis
+    dog = dod / gd[..., None]
+    dg = -(dod * od).sum(-1) / gd
+    da = torch.einsum("bhnd,bhcd->bhnc", dog, vd) + dg[..., None]
+    ds = da * (1.0 + s) * vis
+    dk = torch.einsum("bhnc,bhnd->bhcd", ds, qd) * inv_temp
+    dv = torch.einsum("bhnc,bhnd->bhcd", a, dog)
+    return dk, dv
+
+
+def measure_sequence_sharded(workload, steps, warmup, torch, dist, dev, rank, world, check=True):
+    """Forward + backward of one long causal sequence cut into `world` contiguous pieces (strong scaling): ms per
+    step (max over ranks), the time inside the two all_gathers, per-kernel times, and the largest max-normalised
+    error of sampled rows of o, dq, dk, dv on any rank against an exact float64 evaluation on the device."""
     from reproducing_fastmax_results_b200 import _lib, sequence_parallel as sp
 
-    B, H, N, D, order, causal, dtype_name, scale = WORKLOADS[args.workload]
+    B, H, N, D, order, causal, dtype_name, scale = WORKLOADS[workload]
     dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
     n_local = N // world
+    inv_temp = 1.0 / (8.0 * math.sqrt(D))
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     q, k, v, do = ((torch.randn(B, H, n_local, D, device=dev, generator=gen) * scale).to(dtype) for _ in range(4))
-    eng = sp.CudaEngine(1.0 / (8.0 * math.sqrt(D)), p=order)
+    eng = sp.CudaEngine(inv_temp, p=order)
     lib = _lib.load()
 
     def step():
         o, g, prefix = sp.forward(eng, q, k, v)
-        return sp.backward(eng, q, k, v, o, g, do, prefix)
+        return (o, g) + tuple(sp.backward(eng, q, k, v, o, g, do, prefix))
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     barrier()
     sampler = ClockSampler(torch.cuda.current_device())
@@ -312,7 +428,7 @@ def run_sequence_sharded(args, torch, dist, dev, rank, world):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     ev0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     ev1.record()
     barrier()
@@ -321,29 +437,83 @@ def run_sequence_sharded(args, torch, dist, dev, rank, world):
     t = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
-    value = B * N / (ms_step * 1e-3) / 1e6
+    ms_step = float(t.item()) / steps
+    # the exchange alone: both all_gathers of a step on states of the real size, device-timed
+    exchange_ms = 0.0
+    if dist is not None:
+        st = eng.key_state(k, v)
+        for _ in range(2):
+            sp.exclusive_prefix(st), sp.exclusive_suffix(st)
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(steps):
+            sp.exclusive_prefix(st), sp.exclusive_suffix(st)
+        a1.record()
+        barrier()
+        te = torch.tensor([a0.elapsed_time(a1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        exchange_ms = float(te.item()) / steps
     _lib.profile(True)
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     torch.cuda.synchronize()
     _lib.profile(False)
-    kernels = {name: {"ms_per_launch": ms / cnt, "launches_per_step": cnt / args.steps, "ms_per_step": ms / args.steps}
+    kernels = {name: {"ms_per_launch": ms / cnt, "launches_per_step": cnt / steps, "ms_per_step": ms / steps}
                for name, (ms, cnt) in _lib.profile_collect().items()}
+    parity = None
+    if check:
+        o, g, dq, dk, dv = step()
+        full = []
+        for x in (q, k, v, do, o, g):
+            if dist is None:
+                full.append(x)
+            else:
+                parts = [torch.empty_like(x) for _ in range(world)]
+                dist.all_gather(parts, x.contiguous())
+                full.append(torch.cat(parts, dim=2))
+        fq, fk, fv, fdo, fo, fg = full
+        sg = torch.Generator(device=dev).manual_seed(99)
+        local = torch.randint(0, n_local, (6,), device=dev, generator=sg)
+        local = torch.cat([local, torch.tensor([0, n_local - 1], device=dev)])
+        rows = local + rank * n_local
+        o_ref, dq_ref = _exact_rows_fp64(torch, q[:, :, local], rows, fk, fv, inv_temp, o[:, :, local], g[:, :, local],
+                                         do[:, :, local])
+        dk_ref, dv_ref = _exact_cols_fp64(torch, k[:, :, local], v[:, :, local], rows, fq, fo, fg, fdo, inv_temp)
+        # max-normalised against the largest magnitude of the WHOLE local tensor (rows alone may sit near zero)
+        def err(x, ref, whole):
+            return float(((x.double() - ref).abs().max() / whole.double().abs().max()).item())
+        e = max(err(o[:, :, local], o_ref, o), err(dq[:, :, local], dq_ref, dq), err(dk[:, :, local], dk_ref, dk),
+                err(dv[:, :, local], dv_ref, dv))
+        te = torch.tensor([e], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        parity = {"max_normalised_error_all_ranks": float(te.item()), "tolerance": 1e-4 if dtype_name == "f32" else 2e-2,
+                  "rows_per_rank": int(rows.numel()),
+                  "how": "sampled rows of o, dq and sampled key positions of dk, dv on every rank against an exact float64 "
+                         "row evaluation over the gathered sequence, on the device"}
+    rows_state = (64 * (D // 8) * (D // 8 + 1) // 2) + D + 1
+    return {"ms_per_step": ms_step, "value": B * N / (ms_step * 1e-3) / 1e6, "unit": "Mtokens/s", "exchange_ms_per_step": exchange_ms,
+            "state_bytes_per_rank": B * H * rows_state * (D + 4) * 4, "tokens_per_rank": n_local, "kernels": kernels,
+            "gpu_launches": int(launches), "clocks": clocks, "parity": parity, "engines": sorted(kernels)}
+
+
+def run_sequence_sharded(args, torch, dist, dev, rank, world):
+    B, H, N, D, order, causal, dtype_name, scale = WORKLOADS[args.workload]
+    r = measure_sequence_sharded(args.workload, args.steps, args.warmup, torch, dist, dev, rank, world)
+    ms_step, value, kernels = r["ms_per_step"], r["value"], r["kernels"]
     if rank == 0:
         pk = peaks()
         U = algorithmic_flops(B, H, N, D, order)
         m_full = 1 + D + (D * D if order == 2 else 0)
         executed = 6.0 * U * executed_units(D, order) / m_full / world  # per rank (the exchange replaces no flops)
-        rows = (64 * (D // 8) * (D // 8 + 1) // 2) + D + 1
-        state_bytes = B * H * rows * (D + 4) * 4
         line = {
             "metric": "fastmax_fwd_bwd_mtokens_per_s", "value": value, "unit": "Mtokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": dtype_name + " inputs, f32 accumulate", "data": "synthetic",
-            "config": {"workload": args.workload, "batch": B, "heads": H, "seq_len": N, "tokens_per_rank": n_local,
+            "config": {"workload": args.workload, "batch": B, "heads": H, "seq_len": N, "tokens_per_rank": r["tokens_per_rank"],
                        "head_dim": D, "order": order, "causal": causal,
-                       "parallelism": f"sequence pieces over {world} rank(s); all_gather of {state_bytes} state bytes per rank, "
+                       "parallelism": f"sequence pieces over {world} rank(s); all_gather of {r['state_bytes_per_rank']} state bytes per rank, "
                                       "once forward (exclusive prefix) and once backward (exclusive suffix)",
                        "l2": "inputs exceed the 126 MB L2 at 1-2 ranks; no explicit flush"},
             "roofline": {"kernel": "whole step (fp32 CUDA-core engine)", "bound": "tensor",
@@ -352,7 +522,8 @@ def run_sequence_sharded(args, torch, dist, dev, rank, world):
                          "peak_source": pk["_source"] + " bf16 sustained / 2 (TF32 runs at half the bf16 rate; no TF32 peak was measured)",
                          "note": "executed flops of one rank over the step time; the fp32 engine runs on the FFMA pipe because "
                                  "TF32 operands miss the 1e-4 tolerance", "traffic": None},
-            "kernels": kernels, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks,
+            "exchange_ms_per_step": r["exchange_ms_per_step"], "parity": r["parity"],
+            "kernels": kernels, "cpu_baseline": None, "e2e": None, "gpu_launches": r["gpu_launches"], "clocks": r["clocks"],
         }
         emit(line)
     if dist is not None:
@@ -522,6 +693,176 @@ def run_normalize(args, torch, dist, dev, rank, world):
 
 
 # ----------------------------------------------------------------------------------------------------
+# GPU arm, BASELINE config 5: the REFERENCE's transformer (transformer/model.py, vendored unmodified but for the one
+# documented edit, see baseline/vendor_reference.py) trained on seeded random token ids; the attention operator under
+# it is this library.  Data parallel over the ranks with torch DDP (gradient all-reduce over NCCL), weak scaling.
+# ----------------------------------------------------------------------------------------------------
+CFG5 = dict(out_dim=50257, max_tokens=1024, d_model=512, d_mlp=2048, heads_per_block=8, num_blocks=6, dropout_rate=0.0,
+            use_masking=True, vocab_size=50257, fastmax=True, p=2)
+
+
+def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq=1024):
+    import contextlib
+
+    from baseline import reference_model
+    import reproducing_fastmax_results_b200 as pkg
+    from reproducing_fastmax_results_b200 import _lib
+
+    if not reference_model.available():
+        return {"unavailable": "baseline/_ref/transformer is not populated (python baseline/vendor_reference.py <reference>)"}
+    model = reference_model.load()
+    out = {"model": "reference transformer/model.py Transformer(%s)" % ", ".join(f"{k}={v}" for k, v in CFG5.items()),
+           "batch_per_replica": batch, "seq_len": seq, "optimizer": "AdamW lr 3e-4", "scaling": "weak",
+           "data": "seeded uniform-random token ids, targets = ids shifted by one"}
+    lib = _lib.load()
+    variants = {
+        # the model exactly as the reference runs it: float32, its own autograd Function over fastmax_cuda.forwardpass
+        "f32_reference_function": dict(autocast=False, swap=False),
+        # same call site (model.py:303), module-level fastmax_custom replaced by this package's zero-copy FastMax,
+        # bf16 autocast: q, k, v reach the tensor-memory kernels as strided bf16 views
+        "bf16_autocast_zero_copy": dict(autocast=True, swap=True),
+    }
+    for vname, vcfg in variants.items():
+        torch.manual_seed(0)
+        net = model.Transformer(**CFG5).to(dev)
+        nparams = sum(p.numel() for p in net.parameters())
+        ddp = net
+        if world > 1:
+            from torch.nn.parallel import DistributedDataParallel as DDP
+
+            ddp = DDP(net, device_ids=[dev.index])
+        opt = torch.optim.AdamW(net.parameters(), lr=3e-4)
+        gen = torch.Generator(device=dev).manual_seed(rank)
+        ids = torch.randint(0, CFG5["vocab_size"], (batch, seq + 1), device=dev, generator=gen)
+        saved = model.fastmax_custom
+        if vcfg["swap"]:
+            model.fastmax_custom = pkg.fastmax_custom
+        try:
+            def step(sync=True):
+                ctx = contextlib.nullcontext() if (sync or world == 1) else ddp.no_sync()
+                with ctx:
+                    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=vcfg["autocast"]):
+                        logits = ddp(ids[:, :-1])
+                    loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), ids[:, 1:].reshape(-1))
+                    opt.zero_grad(set_to_none=True)
+                    loss.backward()
+                opt.step()
+                return loss
+
+            def timed(n, sync=True):
+                if dist is not None:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(n):
+                    loss = step(sync)
+                b.record()
+                if dist is not None:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+                if dist is not None:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                return float(t.item()) / n, float(loss)
+
+            import io
+
+            with contextlib.redirect_stdout(io.StringIO()):   # the reference prints a dtype notice per call under bf16
+                loss0 = float(step())
+                for _ in range(warmup - 1):
+                    step()
+                l0 = lib.fastmax_launch_count()
+                ms, loss1 = timed(steps)
+                launches = lib.fastmax_launch_count() - l0
+                ms_nosync = timed(steps, sync=False)[0] if world > 1 else None
+                _lib.profile_collect()
+                _lib.profile(True)
+                step()
+                torch.cuda.synchronize()
+                _lib.profile(False)
+            prof = _lib.profile_collect()
+            lib_ms = sum(m for m, _ in prof.values())
+            out[vname] = {
+                "value": world * batch * seq / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "parameters": nparams,
+                "loss_first_step": loss0, "loss_last_step": loss1, "library_launches_per_step": launches / steps,
+                "library_ms_per_step": lib_ms, "library_share_of_step": lib_ms / ms,
+                "library_kernels": {k: round(m, 4) for k, (m, _) in sorted(prof.items())},
+                "gradient_allreduce": None if world == 1 else {
+                    "bytes_per_step": 4 * nparams, "ms_per_step_without_gradient_sync": ms_nosync,
+                    "exposed_ms_per_step": ms - ms_nosync,
+                    "note": "DDP buckets the all-reduce under the backward pass; exposed = step time minus the same step "
+                            "run under no_sync()"},
+            }
+        finally:
+            model.fastmax_custom = saved
+        del net, ddp, opt
+        torch.cuda.empty_cache()
+    return out
+
+
+def measure_cfg2_strong(torch, dist, dev, rank, world, steps=10, warmup=3):
+    """The FIXED config-2 problem (B8 H16 N4096 D64 bf16, causal, order 2) split over the ranks by batch (128 / world
+    heads each, no collective): strong scaling, device-timed, max over ranks."""
+    from reproducing_fastmax_results_b200 import _lib
+
+    B, H, N, D, order, causal, dtype_name, scale = WORKLOADS[DEFAULT]
+    if B % world:
+        return {"unavailable": f"batch {B} does not divide over {world} ranks"}
+    b = B // world
+    gen = torch.Generator(device=dev).manual_seed(4321 + rank)
+    q, k, v, do = ((torch.randn(b, H, N, D, device=dev, generator=gen) * scale).bfloat16() for _ in range(4))
+    inv_temp = 1.0 / (8.0 * math.sqrt(D))
+
+    def step():
+        o, g, _ = _lib.forward(q, k, v, causal, inv_temp, order=order)
+        return _lib.backward(q, k, v, o, g, do, causal, inv_temp, order=order)
+
+    for _ in range(warmup):
+        step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        step()
+    e.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(e)], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / steps
+    _lib.profile_collect()
+    _lib.profile(True)
+    step()
+    torch.cuda.synchronize()
+    _lib.profile(False)
+    return {"ms_per_step": ms, "value": B * N / (ms * 1e-3) / 1e6, "unit": "Mtokens/s", "scaling": "strong",
+            "heads_per_rank": b * H, "engines": sorted(_lib.profile_collect())}
+
+
+def other_workloads(args, torch, dist, dev, rank, world):
+    """Bounded extra measurements reported beside the headline (same process group, after its timed region)."""
+    out = {}
+    legs = [("cfg2_strong", lambda: measure_cfg2_strong(torch, dist, dev, rank, world)),
+            ("cfg3", lambda: measure_sequence_sharded("cfg3_f32_causal_p2_B1_H8_N131072_D32", 3, 3, torch, dist, dev, rank, world)),
+            ("cfg5", lambda: measure_cfg5(torch, dist, dev, rank, world))]
+    for name, fn in legs:
+        t0 = time.perf_counter()
+        try:
+            out[name] = fn()
+        except Exception as e:   # a leg that fails is reported, the headline line still goes out
+            out[name] = {"error": f"{type(e).__name__}: {e}"[:400]}
+        if isinstance(out[name], dict):
+            out[name]["wall_s"] = round(time.perf_counter() - t0, 2)
+        torch.cuda.empty_cache()
+    return out
+
+
+# ----------------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------------
 def main():
@@ -534,8 +875,12 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=512, help="tokens per head of the bounded CPU-baseline sample")
     ap.add_argument("--cpu-heads", type=int, default=24, help="heads of the CPU-baseline sample (about 10 s of CPU work)")
     ap.add_argument("--ref-heads", type=int, default=6, help="--impl reference: heads per step (a few seconds each)")
+    ap.add_argument("--ref-tokens", type=int, default=256,
+                    help="--impl reference on the reference's einops code: tokens of the one head per step (seconds each; its "
+                         "time and memory grow linearly with the tokens, so tokens/s does not depend on this)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-other", action="store_true", help="skip the other_workloads legs (cfg2 strong scaling, cfg3, cfg5)")
     ap.add_argument("--no-tensor-cores", action="store_true", help="force the CUDA-core kernels")
     ap.add_argument("--mode", default="fwd_bwd", choices=["fwd_bwd", "fwd"],
                     help="fwd: time the forward call only (profiling aid; the headline metric is fwd_bwd)")
@@ -560,7 +905,9 @@ def main():
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
 
     if args.workload in SEQUENCE_SHARDED:
         return run_sequence_sharded(args, torch, dist, dev, rank, world)
@@ -734,10 +1081,14 @@ def main():
 
     cpu = None
     if rank == 0 and not args.no_cpu and world == 1:   # the CPU leg runs at N = 1 only
-        cpu_sample(args.workload, args.cpu_tokens, 1)  # page the CPU kernels in
-        sec, head_tokens, threads = cpu_sample(args.workload, args.cpu_tokens, args.cpu_heads)
-        cpu = {"value": (head_tokens / H) / sec / 1e6, "unit": "Mtokens/s", "cores": threads, "kind": "port",
-               "seconds": sec, "sample": cpu_sample_text(args.workload, args.cpu_tokens, args.cpu_heads)}
+        cpu = cpu_baseline_record(args.workload, args.cpu_tokens, args.cpu_heads)
+
+    input_mb = 4 * q.numel() * q.element_size() >> 20
+    others = None
+    if args.workload == DEFAULT and args.mode == "fwd_bwd" and not args.no_other and not args.no_tensor_cores:
+        del q, k, v, do
+        torch.cuda.empty_cache()
+        others = other_workloads(args, torch, dist, dev, rank, world)
 
     if rank == 0:
         line = {
@@ -748,9 +1099,9 @@ def main():
             "config": {"workload": args.workload, "batch_per_gpu": B, "heads": H, "seq_len": N, "head_dim": D,
                        "order": order, "causal": causal, "parallelism": f"batch x head sharding, {world} rank(s), no collective",
                        "l2": "inputs (%d MB) + workspace exceed the 126 MB L2; no explicit flush"
-                             % (4 * q.numel() * q.element_size() >> 20)},
+                             % input_mb},
             "roofline": roofline, "whole_step": whole, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": int(launches), "clocks": clocks,
+            "gpu_launches": int(launches), "clocks": clocks, "other_workloads": others,
         }
         emit(line)
     if dist is not None:

@@ -189,6 +189,12 @@ int32_t fastmax_check_status(void);
  * (i = the site's code modulo 256; the codes are listed beside the waits in csrc/tc_*.cuh).  Synchronous; clears
  * the counters.  No counterpart in the reference. */
 int32_t fastmax_debug_wait_histogram(int32_t* out, int32_t n);
+/* Exercises the failure path of the bounded device-side waits without touching a production kernel: launches one
+ * tiny thread block on `cuda_stream` that waits about a millisecond on a barrier nobody signals, gives up, and
+ * reports it the way a production kernel would.  After synchronising, fastmax_check_status() returns
+ * FASTMAX_ERR_DEVICE_TIMEOUT once (then FASTMAX_OK again) and fastmax_debug_wait_histogram() shows one block at
+ * wait site 99.  The context stays usable; nothing faults, traps or hangs.  No counterpart in the reference. */
+int32_t fastmax_debug_wait_selftest(void* cuda_stream);
 /* Number of kernel launches issued by this library in this process (all entry points, all threads). */
 uint64_t fastmax_launch_count(void);
 

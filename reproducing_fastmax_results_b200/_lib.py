@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = [
     "fastmax_normalize_forward", "fastmax_normalize_backward",
     "fastmax_status_string", "fastmax_last_cuda_error", "fastmax_last_cuda_error_string",
     "fastmax_version", "fastmax_launch_count", "fastmax_check_status", "fastmax_debug_wait_histogram",
+    "fastmax_debug_wait_selftest",
     "fastmax_profile_enable", "fastmax_profile_kinds", "fastmax_profile_kind_name", "fastmax_profile_collect",
 ]
 
@@ -112,6 +113,8 @@ def load():
     lib.fastmax_check_status.restype = C.c_int32
     lib.fastmax_debug_wait_histogram.restype = C.c_int32
     lib.fastmax_debug_wait_histogram.argtypes = [C.POINTER(C.c_int32), C.c_int32]
+    lib.fastmax_debug_wait_selftest.restype = C.c_int32
+    lib.fastmax_debug_wait_selftest.argtypes = [C.c_void_p]
     lib.fastmax_profile_enable.argtypes = [C.c_int32]
     lib.fastmax_profile_kind_name.restype = C.c_char_p
     lib.fastmax_profile_kind_name.argtypes = [C.c_int32]
@@ -173,8 +176,9 @@ def _workspace(nbytes, device):
 
 
 def forward(q, k, v, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, order=2, state_in=None, want_state=False,
-            want_output=True, flags=0):
-    """Calls fastmax_forward on (b,h,n,d) CUDA tensors.  Returns (o, g, state_out)."""
+            want_output=True, flags=0, out=None):
+    """Calls fastmax_forward on (b,h,n,d) CUDA tensors.  Returns (o, g, state_out).  `out`: optional (b,h,n,d) tensor
+    of any strides (unit stride on d) that receives o, e.g. the transposed view of a (b, n, h*d) buffer."""
     import torch
 
     lib = load()
@@ -183,7 +187,8 @@ def forward(q, k, v, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, order=2, state_in
     args.q, args.k, args.v = view_bhnd(q), view_bhnd(k), view_bhnd(v)
     o = g = sout = None
     if want_output:
-        o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        o = torch.empty(q.shape, dtype=q.dtype, device=q.device) if out is None else out
+        assert o.shape == q.shape and o.dtype == q.dtype
         g = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
         args.o, args.g = view_bhnd(o), view_bhn(g)
     if state_in is not None:
@@ -216,8 +221,9 @@ def forward_static_scratch(q, k, v, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, or
 
 
 def backward(q, k, v, o, g, d_out, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, order=2, state_in=None, dstate_in=None,
-             want_dstate=False, want_grads=True, flags=0):
-    """Calls fastmax_backward on (b,h,n,d) CUDA tensors.  Returns (dq, dk, dv, dstate_out)."""
+             want_dstate=False, want_grads=True, flags=0, grads_out=None):
+    """Calls fastmax_backward on (b,h,n,d) CUDA tensors.  Returns (dq, dk, dv, dstate_out).  `grads_out`: optional
+    (dq, dk, dv) tensors of any strides (unit stride on d) that receive the gradients."""
     import torch
 
     lib = load()
@@ -227,7 +233,8 @@ def backward(q, k, v, o, g, d_out, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, ord
     args.d_out = view_bhnd(d_out)
     dq = dk = dv = dsout = None
     if want_grads:
-        dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (q, k, v))
+        dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (q, k, v)) if grads_out is None \
+            else grads_out
         args.dq, args.dk, args.dv = view_bhnd(dq), view_bhnd(dk), view_bhnd(dv)
     if state_in is not None:
         args.state_in = state_in.data_ptr()

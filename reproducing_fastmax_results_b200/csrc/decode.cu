@@ -149,7 +149,9 @@ decode_step_kernel(const DecodeParams P) {
   }
 
   red[rg][c4] = acc;
-  __syncthreads();
+  // Every block of the cluster must be known to have started before another block writes into its shared memory;
+  // this barrier also orders the `red` rows for the reduction below (it is a superset of __syncthreads).
+  cluster.sync();
   if (tid < C4) {
     float4 t = red[0][tid];
 #pragma unroll

@@ -349,6 +349,11 @@ int32_t fastmax_debug_wait_histogram(int32_t* out, int32_t n) {
   return tc_wait_histogram(out, n);
 }
 
+int32_t fastmax_debug_wait_selftest(void* stream) {
+  // about a millisecond of SM clocks; wait-site code 99 is used by no production kernel
+  return tc_wait_selftest(2000000ll, 99, (cudaStream_t)stream);
+}
+
 int32_t fastmax_profile_enable(int32_t on) {
   g_prof_on.store(on ? 1 : 0);
   return FASTMAX_OK;
@@ -416,21 +421,21 @@ int32_t fastmax_forward(const fastmax_problem* pb, const fastmax_forward_args* a
   int rc = make_plan(pb, pl);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  const bool want_o = a->o.ptr != nullptr;
+  // no queries: there is no output to write, but a requested state_out is still produced
+  const bool want_o = a->o.ptr != nullptr && pb->nq > 0;
   if (pb->nq == 0 && !a->state_out) return FASTMAX_OK;  // no queries, no state requested: nothing to do
-  if (!want_o && !a->state_out) return FASTMAX_ERR_INVALID_ARGUMENT;
+  if (!a->o.ptr && !a->state_out) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (!pb->causal && a->state_in) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (pb->nk > 0) {
     if ((rc = check_view(a->k, pb->dtype, true))) return rc;
     if ((rc = check_view(a->v, pb->dtype, true))) return rc;
   }
-  if (want_o && pb->nq > 0) {
+  if (want_o) {
     if ((rc = check_view(a->q, pb->dtype, true))) return rc;
     if ((rc = check_view(a->o, pb->dtype, false))) return rc;
   }
   if (ws_bytes < fastmax_forward_workspace(pb, a) || (ws_bytes && (!ws || ((uintptr_t)ws % 256))))
     return FASTMAX_ERR_WORKSPACE;
-  if (want_o && pb->nq == 0) return FASTMAX_OK;
 
   int tcrc = tc_forward(pb, a, ws, ws_bytes, st);
   if (tcrc != FASTMAX_TC_NOT_HANDLED) return tcrc;
@@ -530,16 +535,34 @@ int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args*
   if (!L.want_grads && !a->dstate_out) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (L.want_grads && !(a->dq.ptr && a->dk.ptr && a->dv.ptr)) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (!pb->causal && (a->state_in || a->dstate_in)) return FASTMAX_ERR_INVALID_ARGUMENT;
-  if ((rc = check_view(a->q, pb->dtype, true))) return rc;
-  if ((rc = check_view(a->o, pb->dtype, false))) return rc;
-  if ((rc = check_view(a->g, FASTMAX_F32, false))) return rc;
-  if ((rc = check_view(a->d_out, pb->dtype, false))) return rc;
+  if (pb->nq > 0) {
+    if ((rc = check_view(a->q, pb->dtype, true))) return rc;
+    if ((rc = check_view(a->o, pb->dtype, false))) return rc;
+    if ((rc = check_view(a->g, FASTMAX_F32, false))) return rc;
+    if ((rc = check_view(a->d_out, pb->dtype, false))) return rc;
+  }
   if (L.want_grads) {
     if ((rc = check_view(a->k, pb->dtype, true))) return rc;
     if ((rc = check_view(a->v, pb->dtype, true))) return rc;
   }
   if (ws_bytes < fastmax_backward_workspace(pb, a) || !ws || ((uintptr_t)ws % 256)) return FASTMAX_ERR_WORKSPACE;
   if (pb->nq == 0 && pb->nk == 0) return FASTMAX_OK;
+  if (pb->nq == 0) {
+    // no query looks at these keys: dk = dv = 0, and the gradient moments pass through unchanged
+    if (a->dstate_out) {
+      const size_t nbytes = (size_t)pl.bh * pl.n_state * sizeof(float);
+      if (a->dstate_in) FM_CUDA(cudaMemcpyAsync(a->dstate_out, a->dstate_in, nbytes, cudaMemcpyDeviceToDevice, st));
+      else FM_CUDA(cudaMemsetAsync(a->dstate_out, 0, nbytes, st));
+    }
+    if (L.want_grads) {
+      float* zk = (float*)((char*)ws + L.dk);
+      float* zv = (float*)((char*)ws + L.dv);
+      FM_CUDA(cudaMemsetAsync(zk, 0, L.segS - L.dk, st));
+      if ((rc = launch_cast_out(pb, zk, pb->nk, &a->dk, st))) return rc;
+      if ((rc = launch_cast_out(pb, zv, pb->nk, &a->dv, st))) return rc;
+    }
+    return FASTMAX_OK;
+  }
 
   int tcrc = tc_backward(pb, a, ws, ws_bytes, st);
   if (tcrc != FASTMAX_TC_NOT_HANDLED) return tcrc;

@@ -142,7 +142,7 @@ fastmax_problem make_problem(const torch::Tensor& q, const torch::Tensor& k, boo
 // returns (o, g, state_out or empty)
 std::vector<torch::Tensor> forward(torch::Tensor q, torch::Tensor k, torch::Tensor v, bool causal, double inv_temp,
                                    double a0, double a1, double a2, int64_t p, c10::optional<torch::Tensor> state_in,
-                                   bool want_state, bool want_output, int64_t flags) {
+                                   bool want_state, bool want_output, int64_t flags, c10::optional<torch::Tensor> out) {
   CHECK_CUDA(q); CHECK_CUDA(k); CHECK_CUDA(v);
   TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "q, k, v must be (b, h, n, d)");
   TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(), "q, k, v dtypes differ");
@@ -153,7 +153,16 @@ std::vector<torch::Tensor> forward(torch::Tensor q, torch::Tensor k, torch::Tens
   a.q = view_bhnd(q); a.k = view_bhnd(k); a.v = view_bhnd(v);
   torch::Tensor o, g, sout;
   if (want_output) {
-    o = torch::empty({q.size(0), q.size(1), q.size(2), q.size(3)}, q.options());
+    // The output takes q's memory layout (a head-split view (b,n,h,d)->(b,h,n,d) stays a view of a (b,n,h*d) buffer,
+    // so the caller's merge `transpose(1,2).contiguous().view(b,n,h*d)` (model.py:335) copies nothing), or goes
+    // straight into the caller's `out` tensor, whatever its strides.
+    if (out.has_value() && out->defined()) {
+      o = *out;
+      CHECK_CUDA(o);
+      TORCH_CHECK(o.sizes() == q.sizes() && o.scalar_type() == q.scalar_type(), "out must have q's shape and dtype");
+    } else {
+      o = torch::empty_like(q);
+    }
     g = torch::empty({q.size(0), q.size(1), q.size(2)}, q.options().dtype(torch::kFloat32));
     a.o = view_bhnd(o);
     a.g = view_bhn(g);
@@ -180,7 +189,7 @@ std::vector<torch::Tensor> backward(torch::Tensor q, torch::Tensor k, torch::Ten
                                     torch::Tensor d_out, bool causal, double inv_temp, double a0, double a1, double a2,
                                     int64_t p, c10::optional<torch::Tensor> state_in,
                                     c10::optional<torch::Tensor> dstate_in, bool want_dstate, bool want_grads,
-                                    int64_t flags) {
+                                    int64_t flags, c10::optional<std::vector<torch::Tensor>> grads_out) {
   CHECK_CUDA(q); CHECK_CUDA(k); CHECK_CUDA(v); CHECK_CUDA(o); CHECK_CUDA(g); CHECK_CUDA(d_out);
   TORCH_CHECK(g.scalar_type() == torch::kFloat32, "g must be float32");
   const c10::cuda::CUDAGuard guard(q.device());
@@ -191,9 +200,19 @@ std::vector<torch::Tensor> backward(torch::Tensor q, torch::Tensor k, torch::Ten
   a.d_out = view_bhnd(d_out);
   torch::Tensor dq, dk, dv, dsout;
   if (want_grads) {
-    dq = torch::empty(q.sizes(), q.options());
-    dk = torch::empty(k.sizes(), k.options());
-    dv = torch::empty(v.sizes(), v.options());
+    // gradients take the layouts of q, k, v (see forward), or go into the caller's tensors
+    if (grads_out.has_value()) {
+      TORCH_CHECK(grads_out->size() == 3, "grads_out must be [dq, dk, dv]");
+      dq = (*grads_out)[0]; dk = (*grads_out)[1]; dv = (*grads_out)[2];
+      TORCH_CHECK(dq.sizes() == q.sizes() && dk.sizes() == k.sizes() && dv.sizes() == v.sizes() &&
+                      dq.scalar_type() == q.scalar_type() && dk.scalar_type() == q.scalar_type() &&
+                      dv.scalar_type() == q.scalar_type(),
+                  "grads_out must have the shapes and dtype of q, k, v");
+    } else {
+      dq = torch::empty_like(q);
+      dk = torch::empty_like(k);
+      dv = torch::empty_like(v);
+    }
     a.dq = view_bhnd(dq); a.dk = view_bhnd(dk); a.dv = view_bhnd(dv);
   }
   if (state_in.has_value() && state_in->defined()) a.state_in = (const float*)state_in->data_ptr();
@@ -214,7 +233,7 @@ std::vector<torch::Tensor> normalize_forward(torch::Tensor x, double lim) {
   CHECK_CUDA(x);
   const c10::cuda::CUDAGuard guard(x.device());
   auto stream = at::cuda::getCurrentCUDAStream().stream();
-  auto y = torch::empty(x.sizes(), x.options());
+  auto y = torch::empty_like(x);   // keeps x's layout (see forward)
   auto stats = torch::empty({x.size(0), x.size(1)}, x.options().dtype(torch::kInt64));
   fastmax_tensor xv = view_bhnd(x), yv = view_bhnd(y);
   check_status(fastmax_normalize_forward(x.size(0), x.size(1), x.size(2), x.size(3), dtype_of(x), (float)lim, &xv, &yv,
@@ -227,7 +246,7 @@ torch::Tensor normalize_backward(torch::Tensor y, torch::Tensor dy, torch::Tenso
   CHECK_CUDA(y); CHECK_CUDA(dy);
   const c10::cuda::CUDAGuard guard(y.device());
   auto stream = at::cuda::getCurrentCUDAStream().stream();
-  auto dx = torch::empty(y.sizes(), y.options());
+  auto dx = torch::empty_like(y);
   auto scratch = torch::empty({y.size(0) * y.size(1)}, y.options().dtype(torch::kFloat32));
   fastmax_tensor yv = view_bhnd(y), gv = view_bhnd(dy), dv = view_bhnd(dx);
   check_status(fastmax_normalize_backward(y.size(0), y.size(1), y.size(2), y.size(3), dtype_of(y), (float)lim, &yv, &gv,
@@ -241,12 +260,22 @@ int64_t launch_count() { return (int64_t)fastmax_launch_count(); }
 }  // namespace
 
 PYBIND11_MODULE(fastmax_cuda, m) {
-  m.def("forwardpass", &forwardpass, "forwardpass");
-  m.def("backwardpass", &backwardpass, "backwardpass");
-  m.def("forward", &forward, "strided (b,h,n,d) forward: returns [o, g, state_out]");
-  m.def("backward", &backward, "strided (b,h,n,d) backward: returns [dq, dk, dv, dstate_out]");
-  m.def("normalize_forward", &normalize_forward, "q/k normalisation: returns [y, stats]");
-  m.def("normalize_backward", &normalize_backward, "gradient of the q/k normalisation");
+  // The GIL is released for the duration of every call: the work is argument checks, allocation from torch's caching
+  // allocator and asynchronous launches, none of which touches Python objects.
+  using release = py::call_guard<py::gil_scoped_release>;
+  m.def("forwardpass", &forwardpass, "forwardpass", release());
+  m.def("backwardpass", &backwardpass, "backwardpass", release());
+  m.def("forward", &forward, "strided (b,h,n,d) forward: returns [o, g, state_out]", py::arg("q"), py::arg("k"), py::arg("v"),
+        py::arg("causal"), py::arg("inv_temp"), py::arg("a0"), py::arg("a1"), py::arg("a2"), py::arg("p"),
+        py::arg("state_in") = py::none(), py::arg("want_state") = false, py::arg("want_output") = true,
+        py::arg("flags") = 0, py::arg("out") = py::none(), release());
+  m.def("backward", &backward, "strided (b,h,n,d) backward: returns [dq, dk, dv, dstate_out]", py::arg("q"), py::arg("k"),
+        py::arg("v"), py::arg("o"), py::arg("g"), py::arg("d_out"), py::arg("causal"), py::arg("inv_temp"), py::arg("a0"),
+        py::arg("a1"), py::arg("a2"), py::arg("p"), py::arg("state_in") = py::none(), py::arg("dstate_in") = py::none(),
+        py::arg("want_dstate") = false, py::arg("want_grads") = true, py::arg("flags") = 0,
+        py::arg("grads_out") = py::none(), release());
+  m.def("normalize_forward", &normalize_forward, "q/k normalisation: returns [y, stats]", release());
+  m.def("normalize_backward", &normalize_backward, "gradient of the q/k normalisation", release());
   m.def("launch_count", &launch_count, "kernel launches issued by the library so far");
   m.def("version", []() { return std::string(fastmax_version()); });
 }

@@ -26,13 +26,6 @@ __device__ int g_tc_status = 0;
 // how often each wait site of the tensor-core kernels gave up first in its CTA (index = code & 255); diagnostics only
 __device__ int g_tc_wait_hist[256];
 
-// Development aid, compiled in with -DFM_TC_TIMELINE only: per-role clock stamps of CTA (0, 0) of the scan kernels
-// (1024 entries per role, tag << 32 | clock), read back with fastmax_debug_timeline_roles().
-#ifdef FM_TC_TIMELINE
-__device__ long long g_tc_timeline[8192];
-__device__ int g_tc_timeline_cnt[8];
-#endif
-
 namespace tc {
 
 constexpr int CH = 128;                 // tokens per chunk
@@ -238,6 +231,21 @@ intra_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant_
 #include "tc_scan3.cuh"
 #include "tc_p1.cuh"
 
+// Test-only kernel for the bounded-wait failure path: one thread waits, with a limit of `cycles` SM clocks, on an
+// mbarrier that nobody ever arrives on, then records wait site `code` exactly as a production role would
+// (s2::fail_record: histogram, abort flag, status word) and returns normally.  No TMA, MMA or TMEM is involved.
+__global__ void wait_selftest_kernel(long long cycles, int code) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && !mbar_wait_abortable(&bar, 0u, cycles, &abort_flag)) s2::fail_record(code, &abort_flag);
+}
+
 }  // namespace tc
 
 // ------------------------------------------------------------------------------------------------------
@@ -248,16 +256,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // function-local static with an initialiser: thread-safe, so two host threads making their first call together
+  // both see the resolved entry point
+  static const EncodeTiledFn fn = [] {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
+      return reinterpret_cast<EncodeTiledFn>(p);
+    return (EncodeTiledFn) nullptr;
+  }();
   return fn;
 }
 
@@ -366,6 +374,18 @@ static cudaError_t join_streams(SideStreams* p, cudaStream_t st, int n) {
   return cudaSuccess;
 }
 
+// Joins the side streams back into the caller's stream when a call leaves between its fork and its join (an error
+// return): the side streams must never be left holding work the caller's stream does not wait for.
+struct JoinOnExit {
+  SideStreams* p;
+  cudaStream_t st;
+  int n;
+  bool joined = false;
+  ~JoinOnExit() {
+    if (!joined) join_streams(p, st, n);
+  }
+};
+
 static bool tc_forward_supported(const fastmax_problem* pb, const fastmax_forward_args* a) {
   if (pb->flags & FASTMAX_FLAG_NO_TENSOR_CORES) return false;
   if (pb->dtype != FASTMAX_BF16 || pb->d != 64 || pb->order != 2 || !pb->causal) return false;
@@ -446,6 +466,7 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   cudaStream_t ss[2];
   std::unique_lock<std::mutex> side_lock;
   SideStreams* side = fork_streams(pb, st, 2, ss, side_lock);
+  JoinOnExit guard{side, st, 2};
   {
     LaunchScope ls(KK_TC_FWD, ss[0]);
     tc::s2::ApplyParams A{oacc, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, 0, P.nchunks, P.c0, P.c1, P.c2, a->state_out};
@@ -458,7 +479,10 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
     tc::intra_fwd_kernel<<<dim3(P.nchunks, 1, bh), tc::I_THREADS, tc::I_SMEM_BYTES, ss[1]>>>(tmq, tmk, tmv, P);
   }
   e = cudaGetLastError();
-  if (e == cudaSuccess) e = join_streams(side, st, 2);
+  if (e == cudaSuccess) {
+    guard.joined = true;
+    e = join_streams(side, st, 2);
+  }
   if (e != cudaSuccess) return report_cuda_error(e);
   return launch_finalize_fwd(pb, a, oacc, st);
 }
@@ -585,6 +609,7 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   cudaStream_t ss[3];
   std::unique_lock<std::mutex> side_lock;
   SideStreams* side = fork_streams(pb, st, 3, ss, side_lock);
+  JoinOnExit guard{side, st, 3};
   if (side) {
     e = launch_transpose(a->k, pb->batch, pb->heads, pb->nk, 0, kt, ss[1]);
     if (e == cudaSuccess) e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, pb->nk - pb->nq, qt, ss[2]);
@@ -637,17 +662,16 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   if (rc == FASTMAX_OK) rc = launch_cast_out(pb, dka, pb->nk, &a->dk, ss[2], tc::ACC_LD);
   if (rc == FASTMAX_OK) rc = launch_cast_out(pb, dva, pb->nk, &a->dv, ss[0], tc::ACC_LD);
   if (rc != FASTMAX_OK) return rc;
+  guard.joined = true;
   e = join_streams(side, st, 3);
   return e == cudaSuccess ? FASTMAX_OK : report_cuda_error(e);
 }
 
-#ifdef FM_TC_TIMELINE
-extern "C" int fastmax_debug_timeline_roles(long long* out, int* counts) {
-  cudaMemcpyFromSymbol(out, g_tc_timeline, sizeof(long long) * 8192);
-  cudaMemcpyFromSymbol(counts, g_tc_timeline_cnt, sizeof(int) * 8);
-  return 0;
+int tc_wait_selftest(long long cycles, int code, cudaStream_t st) {
+  tc::wait_selftest_kernel<<<1, 32, 0, st>>>(cycles, code);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FASTMAX_OK : report_cuda_error(e);
 }
-#endif
 
 int tc_wait_histogram(int* out, int n) {
   int h[256];

@@ -16,6 +16,8 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
 int tc_device_status(int* out);
 // Copies (and clears) the per-wait-site give-up counters (index = error code & 255).
 int tc_wait_histogram(int* out, int n);
+// Launches the test-only kernel that lets a bounded wait of `cycles` SM clocks run out and records wait site `code`.
+int tc_wait_selftest(long long cycles, int code, cudaStream_t st);
 
 // shared with the C-ABI translation unit
 int report_cuda_error(cudaError_t e);  // remembers e for fastmax_last_cuda_error(), returns FASTMAX_ERR_CUDA

@@ -51,12 +51,7 @@ constexpr int OFF_KT = OFF_RAWQ + 2 * REGION;          // 147456, 2 x KT_BUF (tw
 constexpr int OFF_BAR = OFF_KT + 2 * KT_BUF;           // 184320
 constexpr int OFF_OST = OFF_BAR + 512;                 // output staging for the bulk reduce: 128 rows x <= 68 floats
 constexpr int OST_BYTES = CH * 68 * 4;                 // 34816
-constexpr int OFF_TL = OFF_OST + OST_BYTES;            // development build only: 4 roles x 256 time stamps
-#ifdef FM_TC_TIMELINE
-constexpr int SMEM_BYTES = OFF_TL + 4 * 2048 + 1024;
-#else
-constexpr int SMEM_BYTES = OFF_TL + 1024;
-#endif
+constexpr int SMEM_BYTES = OFF_OST + OST_BYTES + 1024;
 static_assert(OFF_RAWQ % 1024 == 0 && OFF_KT % 128 == 0 && OFF_OST % 128 == 0, "tile alignment");
 constexpr uint32_t COL_O = 320u, COL_A = 400u;
 // barriers
@@ -208,18 +203,6 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
   const int nch = P.nchunks;
   const bool lin_slice = (tile0 + ntl == NTILES);   // this slice holds the linear/constant tile: weights go into Sb
   auto chunk_of = [&](int i) -> int { return DV ? (nch - 1 - i) : i; };  // i-th chunk of the scan
-#ifdef FM_TC_TIMELINE
-  // development aid: cheap (shared-memory) time stamps of one thread per role of CTA (0, 0), chunks 8..11
-  uint2* tl_ptr = nullptr;
-  int tl_n = 0, tl_c = 0;
-  if (blockIdx.x == 0 && lane == 0 && (w == W_MMA || w == 0 || w == W_MMA2 || w == W_CONS))
-    tl_ptr = reinterpret_cast<uint2*>(sm + OFF_TL) + 256 * (w == W_MMA ? 0 : (w == 0 ? 1 : (w == W_MMA2 ? 2 : 3)));
-#define S2_STAMP(tag) do { if (tl_ptr && tl_c >= 8 && tl_c < 12 && tl_n < 256) tl_ptr[tl_n++] = make_uint2((uint32_t)(tag), (uint32_t)clock()); } while (0)
-#define S2_CHUNK(c) tl_c = (c)
-#else
-#define S2_STAMP(tag) do { } while (0)
-#define S2_CHUNK(c) do { } while (0)
-#endif
 
   if (tid == 0) {
     // arrivals are one per WARP (an elected lane after __syncwarp), not one per thread
@@ -286,7 +269,6 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
     uint32_t k = 0;    // slabs this set has produced = phase count of its slot
     bool ok = true;
     for (int ci = 0; ci < nch && ok; ++ci) {
-      S2_CHUNK(ci);
       const int buf = ci & 1;
       if (!WAIT(B_KT_READY + buf, (uint32_t)(ci >> 1)) || !WAIT(B_Q_READY + buf, (uint32_t)(ci >> 1))) { FAIL(200); break; }
       const uint8_t* raw = rawq + buf * REGION;
@@ -300,20 +282,16 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
         const bool is_q = (d4 & 4u) != 0;
         const bool lin = lin_slice && t == ntl - 1;
         const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
-        S2_STAMP(40);
         uint32_t r[32];
         make_slab(r, is_q, half, lin, !lin_slice, row, raw, xt, pr);
-        S2_STAMP(41);
         if (k > 0 && !WAIT(B_EMPTY + set, k - 1)) { FAIL(201); ok = false; break; }
         __syncwarp();
-        S2_STAMP(42);
         tc_fence_after_sync();
         tmem_st32(slot_addr, r);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[(is_q ? B_FULL_Q : B_FULL_K) + set]);
-        S2_STAMP(43);
       }
       base = (base + (uint32_t)((ci == 0 ? 2 : 4) * ntl)) % NSETS;
       if (ok) {
@@ -332,14 +310,11 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
     const float out_scale = lin_slice ? 1.f : P.c2;   // pair-tile slices: the common weight c2, applied once, exactly
     bool ok = true;
     for (int ci = 0; ci < nch && ok; ++ci) {
-      S2_CHUNK(ci);
       const int c = chunk_of(ci);
       for (int t = 0; t < ntl && ok; ++t) {
         if (t == ntl - 1 && ci > 0) {  // the output of this chunk is complete once the last apply has finished
-          S2_STAMP(60);
           if (!WAIT(B_O_DONE, (uint32_t)(ci - 1))) { FAIL(220); ok = false; break; }
           __syncwarp();
-          S2_STAMP(61);
           tc_fence_after_sync();
           uint32_t ra[32], rb[32], rc[8];
           tmem_ld32(lane_addr + COL_O, ra);
@@ -380,14 +355,11 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
               bulk_commit_group();
             }
           }
-          S2_STAMP(62);
         }
         if (ci < nch - 1) {  // the bf16 copy of S_t feeds the next chunk's apply
-          S2_STAMP(70);
           // S_t is final (update issuer) and Sb_t is no longer read (apply issuer; the first chunk has no apply)
           if (!WAIT(B_S_DONE + t, (uint32_t)ci) || (ci > 0 && !WAIT(B_A_DONE + t, (uint32_t)(ci - 1)))) { FAIL(221); ok = false; break; }
           __syncwarp();
-          S2_STAMP(71);
           tc_fence_after_sync();
           uint8_t* dst = sb + t * SB_TILE + l * 16;
           if (lin_slice) {  // weights inside the copy: c2 / 2 c2 per unit, c1 and c0 in the linear/constant tile
@@ -422,7 +394,6 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars[B_SB_READY + t]);
-          S2_STAMP(72);
         }
       }
     }
@@ -482,10 +453,8 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
     bool ok = true;
     // one slab: wait for it, four MMAs (K = 64), release the ring slot (+ the tile / chunk level commits)
     auto issue = [&](uint32_t slot, uint32_t d, uint64_t b0, uint32_t first, uint64_t* done1, uint64_t* done2) -> bool {
-      S2_STAMP(10);
       if (!wait_fast(&full[slot], (phases >> slot) & 1u, abort_flag)) return false;
       __syncwarp();
-      S2_STAMP(11);
       phases ^= (1u << slot);
       tc_fence_after_sync();
       const uint32_t a0 = tmem_base + COL_A + 32u * slot;
@@ -499,12 +468,10 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
         if (done2) mma_commit(done2);
       }
       __syncwarp();
-      S2_STAMP(12);
       return true;
     };
     auto wrap = [](uint32_t x) -> uint32_t { return x >= NRING ? x - NRING : x; };  // x < 2 * NRING
     for (int ci = 0; ci < nch && ok; ++ci) {
-      S2_CHUNK(ci);
       const uint64_t dB_Vc = dB_V + (uint64_t)(((ci & 1) * VPBUF) >> 4);
       if (!mine_q && !WAIT(B_VP_READY + (ci & 1), (uint32_t)(ci >> 1))) { FAIL(233); break; }
       if (mine_q && ci >= 2 && !WAIT(B_O_FREE, (uint32_t)(ci - 2))) { FAIL(231); break; }
@@ -585,13 +552,6 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
   tc_fence_before_sync();
   __syncthreads();
   if (w == 0) tmem_dealloc(tmem_base, 512);
-#ifdef FM_TC_TIMELINE
-  if (tl_ptr && !DV) {
-    const int role = (int)((tl_ptr - reinterpret_cast<uint2*>(sm + OFF_TL)) / 256);
-    for (int i = 0; i < tl_n; ++i) g_tc_timeline[role * 1024 + i] = ((long long)tl_ptr[i].x << 32) | tl_ptr[i].y;
-    g_tc_timeline_cnt[role] = tl_n;
-  }
-#endif
 }
 
 // x (batch, head, token, 64) bf16, any strides -> xt [batch*head][64][ntp]: column p of xt holds token p - shift of x

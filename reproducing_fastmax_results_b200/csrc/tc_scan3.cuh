@@ -47,12 +47,7 @@ constexpr int OFF_XT = OFF_ZERO + BLK;                 // 149504: transposed X t
 constexpr int OFF_STG = OFF_XT + 2 * KT_BUF;           // 186368: dz staging, 128 rows x ACC_LD floats
 constexpr int STG_BYTES = CH * ACC_LD * 4;             // 34816
 constexpr int OFF_BAR = OFF_STG + STG_BYTES;           // 221184
-#ifdef FM_TC_TIMELINE
-constexpr int OFF_TL = OFF_BAR + 512;                  // development build only: 5 roles x 200 time stamps
-constexpr int SMEM_BYTES = OFF_TL + 5 * 1600 + 1024;
-#else
 constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
-#endif
 static_assert(OFF_XT % 128 == 0 && OFF_STG % 128 == 0 && OFF_BAR % 8 == 0, "tile alignment");
 static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 constexpr uint32_t COL_DPHI = 320u, COL_A = 448u;
@@ -116,20 +111,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
   const int nch = P.nchunks;
   auto chunk_of = [&](int i) -> int { return DK ? (nch - 1 - i) : i; };  // i-th chunk of the scan
   auto units_of = [&](int t) -> int { return (tile0 + t < NTILES - 1) ? 2 : 1; };  // the constant feature has no gradient
-#ifdef FM_TC_TIMELINE
-  // development aid: cheap (shared-memory) time stamps of one thread per role of CTA (0, 0), chunks 8..11
-  uint2* tl_ptr = nullptr;
-  int tl_n = 0, tl_c = 0;
-  {
-    const int role = w == 0 ? 0 : w == W_PROD ? 1 : w == W_CONS ? 2 : w == W_DPHI ? 3 : w == W_UPD ? 4 : -1;
-    if (blockIdx.x == 0 && lane == 0 && role >= 0) tl_ptr = reinterpret_cast<uint2*>(sm + OFF_TL) + 200 * role;
-  }
-#define S3_STAMP(tag) do { if (tl_ptr && tl_c >= 8 && tl_c < 12 && tl_n < 200) tl_ptr[tl_n++] = make_uint2((uint32_t)(tag), (uint32_t)clock()); } while (0)
-#define S3_CHUNK(c) tl_c = (c)
-#else
-#define S3_STAMP(tag) do { } while (0)
-#define S3_CHUNK(c) do { } while (0)
-#endif
 
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -222,7 +203,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     uint32_t cnt = 0;     // units this group has taken = phase count of its dphi buffer
     bool ok = true;
     for (int ci = 1; ci < nch && ok; ++ci) {
-      S3_CHUNK(ci);
       const int c = chunk_of(ci);
       const long long row = (long long)c * CH + l - P.z_shift;
       const bool valid = row >= 0 && row < P.nz;
@@ -239,11 +219,9 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
           // the z blocks of this unit, before the wait so the loads fly meanwhile
           uint4 za4 = make_uint4(0u, 0u, 0u, 0u), zb4 = make_uint4(0u, 0u, 0u, 0u);
           if (valid) { za4 = zrow[a]; zb4 = zrow[b]; }
-          S3_STAMP(10);
           if (!WAIT(B_DPHI_DONE + grp, cnt)) { FAIL(320); ok = false; break; }
           ++cnt;
           __syncwarp();
-          S3_STAMP(11);
           tc_fence_after_sync();
           const float wgt = (a == b) ? P.c2 : 2.f * P.c2;
           // packed float32 FMAs (two per instruction): pairs run over ri
@@ -260,7 +238,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
             uint32_t r[32];
             tmem_ld32(dphi_addr + 32u * hf, r);
             tmem_ld_wait();
-            S3_STAMP(14 + 2 * hf);
             if (hf == 1) {  // the whole unit has been read: the buffer can take the next one
               tc_fence_before_sync();
               __syncwarp();
@@ -278,7 +255,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
               }
               dza[4 * hf + mi] += s2v.x + s2v.y;
             }
-            S3_STAMP(15 + 2 * hf);
           }
           float dzb[8];
 #pragma unroll
@@ -298,7 +274,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
         }
       }
       if (!ok) break;
-      S3_STAMP(12);
       // ---- the chunk's dz: both groups add their blocks into the (zeroed) staging rows, group 0 first; the drain
       //      warp then adds the rows to global memory with one bulk reduce and zeroes them again ----
       float* rowf = stg + l * ACC_LD;
@@ -346,7 +321,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
       fence_proxy_async_smem();   // the copy engine reads these rows
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[grp == 0 ? B_STG_HALF : B_STG_FULL]);
-      S3_STAMP(13);
     }
   } else if (w < W_CONS) {
     // ================= producers: update slabs (Phi(X)^T, thread = feature) into the two TMEM slots =================
@@ -364,31 +338,26 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     uint32_t k = 0;   // slabs this set has produced = phase count of its slot
     bool ok = true;
     for (int ci = 0; ci < nch && ok; ++ci) {
-      S3_CHUNK(ci);
       const int buf = ci & 1;
       if (!WAIT(B_XT_READY + buf, (uint32_t)(ci >> 1))) { FAIL(300); break; }
       const uint8_t* box = xtile + buf * KT_BUF + set * KT_BOX;
       for (int t = 0; t < ntl && ok; ++t, ++k) {
         const bool lin = (tile0 + t == NTILES - 1);
         const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
-        S3_STAMP(40);
         uint32_t r[32];
         if (!lin) {
           const uint32_t q = (f >> 6) ? (pr >> 8) : pr;
           s2::update_pair_slab(r, box, 8 * (int)(q & 15) + ((f >> 3) & 7), 8 * (int)((q >> 4) & 15) + (f & 7));
         } else if (f < 64) s2::copy_trow_slab(r, box, f);
         else s2::fill_slab(r, f == 64 ? 0x3F803F80u : 0u);
-        S3_STAMP(41);
         if (k > 0 && !WAIT(B_EMPTY + set, k - 1)) { FAIL(301); ok = false; break; }
         __syncwarp();
-        S3_STAMP(42);
         tc_fence_after_sync();
         tmem_st32(slot_addr, r);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[B_FULL + set]);
-        S3_STAMP(43);
       }
       if (ok) {
         __syncwarp();
@@ -402,13 +371,10 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     const uint32_t lane_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16);
     bool ok = true;
     for (int ci = 0; ci + 1 < nch && ok; ++ci) {
-      S3_CHUNK(ci);
       for (int t = 0; t < ntl && ok; ++t) {
-        S3_STAMP(70);
         // S_t is final (update issuer) and Sb_t is no longer read (dphi issuer; the first chunk has no dphi)
         if (!WAIT(B_S_DONE + t, (uint32_t)ci) || (ci > 0 && !WAIT(B_A_DONE + t, (uint32_t)(ci - 1)))) { FAIL(310); ok = false; break; }
         __syncwarp();
-        S3_STAMP(71);
         tc_fence_after_sync();
         uint8_t* dst = sb + t * SB_TILE + l * 16;
 #pragma unroll
@@ -427,7 +393,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[B_SB_READY + t]);
-        S3_STAMP(72);
       }
     }
   } else {
@@ -441,7 +406,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
       uint32_t cnt = 0;   // units issued into this buffer
       bool ok = true;
       for (int ci = 0; ci < nch && ok; ++ci) {
-        S3_CHUNK(ci);
         const int buf = ci & 1;
         int mu = 0;       // index of the unit within the chunk
         if (!WAIT(B_G_READY + buf, (uint32_t)(ci >> 1))) { FAIL(330); break; }
@@ -453,11 +417,9 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
           const int nu = units_of(t);
           for (int u = 0; u < nu && ok; ++u, ++mu) {
             if ((uint32_t)(mu & 1) != db) continue;
-            S3_STAMP(20);
             if (cnt > 0 && !WAIT(B_DPHI_FREE + db, cnt - 1u)) { FAIL(332); ok = false; break; }
             ++cnt;
             __syncwarp();
-            S3_STAMP(21);
             tc_fence_after_sync();
             if (elect_one()) {
               const uint32_t d = tmem_base + COL_DPHI + 64u * db;
@@ -468,7 +430,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
               mma_commit(&bars[B_DPHI_DONE + db]);
             }
             __syncwarp();
-            S3_STAMP(22);
           }
           // this issuer's MMAs on Sb_t are all issued (possibly none): its half of the tile's "no longer read" signal
           if (ok && elect_one()) mma_commit(&bars[B_A_DONE + t]);
@@ -485,7 +446,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
       uint32_t k = 0;   // tiles issued = phase count of both slots
       bool ok = true;
       for (int ci = 0; ci < nch && ok; ++ci) {
-        S3_CHUNK(ci);
         const int buf = ci & 1;
         if (!WAIT(B_Y_READY + buf, (uint32_t)(ci >> 1))) { FAIL(340); break; }
         const uint64_t dB = make_smem_desc(smem_u32(ytile + buf * TILE9), 128, 2048, 0);
@@ -495,10 +455,8 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
           const uint32_t d = tmem_base + 80u * t;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
-            S3_STAMP(30);
             if (!WAIT(B_FULL + hf, k)) { FAIL(342); ok = false; break; }
             __syncwarp();
-            S3_STAMP(31);
             tc_fence_after_sync();
             if (elect_one()) {
               const uint32_t a0 = tmem_base + COL_A + 32u * hf;
@@ -514,7 +472,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
               }
             }
             __syncwarp();
-            S3_STAMP(32);
           }
         }
       }
@@ -586,13 +543,6 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   if (w == 0) tmem_dealloc(tmem_base, 512);
-#ifdef FM_TC_TIMELINE
-  if (tl_ptr && !DK) {
-    const int role = (int)((tl_ptr - reinterpret_cast<uint2*>(sm + OFF_TL)) / 200);
-    for (int i = 0; i < tl_n; ++i) g_tc_timeline[role * 1024 + i] = ((long long)tl_ptr[i].x << 32) | tl_ptr[i].y;
-    g_tc_timeline_cnt[role] = tl_n;
-  }
-#endif
 }
 
 }  // namespace s3

@@ -160,3 +160,53 @@ def test_forward_backward_replay_from_a_cuda_graph():
         for a, b in zip(outs, want):
             assert float((a.float() - b.float()).abs().max()) <= 5e-3 * float(b.float().abs().max()) + 1e-6
     assert float((ref[0].float() - outs[0].float()).abs().max()) > 0.0   # the replays really used the new q
+
+
+def test_fastmax_keeps_the_head_split_layout_so_the_merge_is_free():
+    """q, k, v as the (b,n,h,d)->(b,h,n,d) views of a projection (transformer/model.py:283-285): the output and the
+    gradients come back in the same memory layout, so `transpose(1, 2).contiguous()` (model.py:335) copies nothing."""
+    import reproducing_fastmax_results_b200 as pkg
+
+    B, N, H, D = 2, 80, 4, 32
+    torch.manual_seed(4)
+    base = [torch.randn(B, N, H * D, device="cuda", requires_grad=True) for _ in range(3)]
+    q, k, v = (t.view(B, N, H, D).transpose(1, 2) for t in base)
+    o = pkg.fastmax_custom(q, k, v, None, None, True, 0.0, False, 4.0, 1.0, 1.0, 0.5, 1.0, 2)
+    assert o.stride() == q.stride()
+    merged = o.transpose(1, 2)
+    assert merged.is_contiguous() and merged.contiguous().data_ptr() == o.data_ptr()
+    merged.reshape(B, N, H * D).sum().backward()
+    poly = orc.Poly(1.0, 1.0, 0.5, 0.25, 2)
+    qh, kh, vh = (host(t) for t in (q, k, v))
+    o_ref, _ = orc.fastmax_naive(qh, kh, vh, True, poly)
+    assert orc.max_norm_err(host(o), o_ref) < 1e-4
+    dq_ref, _, _ = orc.fastmax_naive_grads(qh, kh, vh, np.ones_like(qh), True, poly)
+    assert orc.max_norm_err(host(base[0].grad).reshape(B, N, H, D).transpose(0, 2, 1, 3), dq_ref) < 1e-4
+
+
+def test_extension_calls_release_the_gil():
+    """A Python thread keeps running while another one is inside the extension (SURVEY of the boundary: the
+    reference holds the GIL and synchronises the device; this extension does neither)."""
+    import threading
+    import time
+
+    import reproducing_fastmax_results_b200 as pkg
+
+    ext = pkg.load_extension()
+    x = torch.randn(4, 16, 2048, 64, device="cuda").bfloat16()
+    ticks = []
+    stop = threading.Event()
+
+    def ticker():
+        while not stop.is_set():
+            ticks.append(time.perf_counter())
+            time.sleep(0)
+
+    th = threading.Thread(target=ticker)
+    th.start()
+    for _ in range(20):
+        ext.forward(x, x, x, True, 0.1, 1.0, 1.0, 0.5, 2)
+    torch.cuda.synchronize()
+    stop.set()
+    th.join()
+    assert len(ticks) > 20

@@ -122,6 +122,31 @@ def test_general_coefficients_and_strided_views():
         assert orc.max_norm_err(host(got), ref) < 1e-4
 
 
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 32), (torch.bfloat16, 64)])
+def test_outputs_written_straight_into_merged_head_buffers(dtype, D):
+    """o, dq, dk, dv go through strides into (b, n, h*d) buffers (the layout after the head merge of
+    transformer/model.py:335), so no transpose copy is needed on either side of the operator."""
+    B, H, N = 2, 16, 200
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    rng = np.random.default_rng(9)
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / (2.0 * np.sqrt(D)), 2)
+    q, k, v, do = (rng.standard_normal((B, N, H * D)).astype(np.float32) for _ in range(4))
+    L = lib()
+    split = lambda t: t.view(B, N, H, D).transpose(1, 2)
+    qd, kd, vd, dod = (split(dev(x).to(dtype)) for x in (q, k, v, do))
+    bufs = [torch.full((B, N, H * D), float("nan"), device="cuda", dtype=dtype) for _ in range(4)]
+    o, g, _ = L.forward(qd, kd, vd, True, poly.inv_temp, order=2, out=split(bufs[0]))
+    L.backward(qd, kd, vd, o, g, dod, True, poly.inv_temp, order=2, grads_out=tuple(split(b) for b in bufs[1:]))
+    torch.cuda.synchronize()
+    ref_in = [host(t) for t in (qd, kd, vd, dod)]
+    o_ref, _ = orc.fastmax_naive(ref_in[0], ref_in[1], ref_in[2], True, poly)
+    refs = (o_ref,) + tuple(orc.fastmax_naive_grads(*ref_in, True, poly))
+    for buf, ref in zip(bufs, refs):
+        got = host(buf).reshape(B, N, H, D).transpose(0, 2, 1, 3)
+        assert np.isfinite(got).all()
+        assert orc.max_norm_err(got, ref) < tol
+
+
 @pytest.mark.parametrize("D", [32, 64])
 def test_state_carry_between_calls(D):
     """A causal sequence cut in two: the second call starts from the first call's state (what a
@@ -206,3 +231,21 @@ def test_empty_and_error_paths():
     x = torch.randn(1, 1, 8, 32, device="cuda")
     o, g, _ = L.forward(x, x, x, True, 0.1)
     assert torch.isfinite(o).all()
+
+
+def test_no_queries_still_produce_the_key_state_and_zero_key_gradients():
+    """nq = 0 with nk > 0: the forward writes state_out (= moments of the keys), the backward returns zero dk, dv."""
+    B, H, N, D = 1, 2, 70, 32
+    rng = np.random.default_rng(12)
+    k, v = (dev(rng.standard_normal((B, H, N, D)).astype(np.float32)) for _ in range(2))
+    q = torch.empty(B, H, 0, D, device="cuda")
+    L = lib()
+    poly = orc.Poly(1.0, 1.0, 0.5, 0.3, 2)
+    o, g, s = L.forward(q, k, v, True, poly.inv_temp, order=2, want_state=True)
+    _, _, s_ref = L.forward(k, k, v, True, poly.inv_temp, order=2, want_state=True, want_output=False)
+    torch.cuda.synchronize()
+    assert o.shape[2] == 0 and torch.equal(s, s_ref) and float(s.abs().max()) > 0
+    do = torch.empty(B, H, 0, D, device="cuda")
+    dq, dk, dv, _ = L.backward(q, k, v, o, g, do, True, poly.inv_temp, order=2)
+    torch.cuda.synchronize()
+    assert dq.shape[2] == 0 and float(dk.abs().max()) == 0.0 and float(dv.abs().max()) == 0.0

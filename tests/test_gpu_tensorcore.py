@@ -107,6 +107,32 @@ def test_wait_histogram_is_empty_after_clean_runs():
     assert lib.fastmax_debug_wait_histogram(None, 256) == 1  # FASTMAX_ERR_INVALID_ARGUMENT
 
 
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_context_stays_usable():
+    """The failure path of the device-side waits (bounded wait -> wait-site record -> status word -> host): the
+    test-only kernel waits ~1 ms on a barrier nobody signals and gives up; no production kernel is disturbed."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    lib = L.load()
+    torch.cuda.synchronize()
+    assert lib.fastmax_check_status() == 0 and L.wait_histogram() == {}
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.fastmax_debug_wait_selftest(stream) == 0
+    torch.cuda.synchronize()
+    assert lib.fastmax_check_status() == 5        # FASTMAX_ERR_DEVICE_TIMEOUT, reported once ...
+    assert lib.fastmax_check_status() == 0        # ... and cleared by the read
+    assert L.wait_histogram() == {99: 1}          # the wait site that gave up, one thread block
+    assert L.wait_histogram() == {}
+    # the next ordinary call works and is clean
+    x = torch.randn(1, 16, 300, 64, device="cuda").bfloat16()
+    o, g, _ = L.forward(x, x, x, True, 0.1, order=2)
+    torch.cuda.synchronize()
+    assert lib.fastmax_check_status() == 0 and torch.isfinite(o.float()).all()
+    with pytest.raises(L.FastmaxError):           # the Python helper turns the status into an exception
+        lib.fastmax_debug_wait_selftest(stream)
+        L.check_status()
+    assert L.wait_histogram() == {99: 1}
+
+
 @pytest.mark.parametrize("shape", [(1, 13, 129, 129), (1, 16, 257, 385), (3, 5, 1024, 1024)])
 def test_tensorcore_more_shapes_forward_backward(shape):
     """Chunk-boundary sizes, a key prefix that is not a multiple of the chunk, and head counts that are not a

@@ -132,3 +132,99 @@ def test_cuda_engine_pieces_match_whole_sequence(D, dtype, pieces):
         for j, ref in enumerate((dq_ref, dk_ref, dv_ref)):
             got = np.concatenate([host(gr[j])[0, h] for gr in grads], 0)
             assert orc.max_norm_err(got, ref) < tol, ("dq", "dk", "dv")[j]
+
+
+def _failing_peer_worker(rank, world, port, out_dir):
+    """Rank 1 raises before the exchange; rank 0 must come back from the collective with an error, not hang."""
+    import datetime
+    import time
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    x = torch.ones(4, 3, dtype=torch.float64)
+    assert torch.equal(sp.exclusive_prefix(x), torch.full((4, 3), float(rank), dtype=torch.float64))  # healthy exchange first
+    if rank == 1:
+        raise RuntimeError("injected failure before the exchange")
+    t0 = time.monotonic()
+    try:
+        sp.exclusive_prefix(x)
+        verdict = "no error"
+    except Exception as e:  # the process group reports the lost peer (closed connection or its timeout)
+        verdict = "error: " + type(e).__name__
+    with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+        f.write("%s\n%.3f\n" % (verdict, time.monotonic() - t0))
+    os._exit(0)   # skip the group's teardown handshake with a peer that is gone
+
+
+def test_a_rank_that_fails_before_the_exchange_gives_its_peer_an_error(tmp_path):
+    """Failure made on the host: no GPU is involved, nothing hangs.  The surviving rank gets an exception from the
+    collective within the process group's timeout and can report it."""
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_peer_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+    assert all(not p.is_alive() for p in procs), "a rank hung"
+    assert procs[1].exitcode != 0
+    text = open(os.path.join(str(tmp_path), "rank0.txt")).read().splitlines()
+    assert text[0].startswith("error"), text
+    assert float(text[1]) < 30.0, text
+
+
+def _nccl_worker(rank, world, port, out_dir, D, dtype_name):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from reproducing_fastmax_results_b200 import _lib
+
+        dtype = torch.float32 if dtype_name == "f32" else torch.bfloat16
+        B, H, N = 1, 16, 2 * 300
+        cuts = [0, 260, N]   # uneven pieces, neither a multiple of the chunk length
+        q, k, v, do = (torch.from_numpy(a[:, :, cuts[rank]:cuts[rank + 1]].copy()).to(dev, dtype)
+                       for a in _inputs(B, H, N, D, seed=21))
+        q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+        _lib.profile_collect()
+        _lib.profile(True)
+        o = sp.SequenceParallelFastMax.apply(q, k, v, 2.0 * math.sqrt(D), 1.0, 1.0, 0.5, 2, None)
+        o.backward(do)
+        torch.cuda.synchronize()
+        _lib.profile(False)
+        kinds = sorted(_lib.profile_collect())
+        _lib.check_status()
+        host = lambda t: t.detach().float().cpu().numpy()
+        np.savez(os.path.join(out_dir, f"rank{rank}.npz"), o=host(o), dq=host(q.grad), dk=host(k.grad), dv=host(v.grad),
+                 kinds=np.array(kinds))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,dtype_name", [(32, "f32"), (64, "bf16")])
+def test_nccl_ranks_reproduce_the_unsplit_sequence(tmp_path, D, dtype_name):
+    """The real composition: two processes, one GPU each, CudaEngine + all_gather over NCCL
+    (SequenceParallelFastMax forward and backward), against the unsplit float64 result."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    mp.spawn(_nccl_worker, args=(world, _free_port(), str(tmp_path), D, dtype_name), nprocs=world, join=True)
+    B, H, N = 1, 16, 600
+    tol = 1e-4 if dtype_name == "f32" else 2e-2
+    q, k, v, do = _inputs(B, H, N, D, seed=21)
+    if dtype_name == "bf16":
+        q, k, v, do = (torch.from_numpy(a).bfloat16().double().numpy() for a in (q, k, v, do))
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / (2.0 * math.sqrt(D)), 2)
+    parts = [np.load(os.path.join(str(tmp_path), f"rank{r}.npz")) for r in range(world)]
+    for h in range(H):
+        o_ref, _ = orc.fastmax_naive(q[0, h], k[0, h], v[0, h], True, poly)
+        refs = dict(zip(("dq", "dk", "dv"), orc.fastmax_naive_grads(q[0, h], k[0, h], v[0, h], do[0, h], True, poly)))
+        refs["o"] = o_ref
+        for name, ref in refs.items():
+            got = np.concatenate([p[name][0, h] for p in parts], 0)
+            assert orc.max_norm_err(got, ref) < tol, (name, h)
