@@ -764,12 +764,12 @@ def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq
                 t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
                 if dist is not None:
                     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                return float(t.item()) / n, float(loss)
+                return float(t.item()) / n, float(loss.detach())
 
             import io
 
             with contextlib.redirect_stdout(io.StringIO()):   # the reference prints a dtype notice per call under bf16
-                loss0 = float(step())
+                loss0 = float(step().detach())
                 for _ in range(warmup - 1):
                     step()
                 l0 = lib.fastmax_launch_count()

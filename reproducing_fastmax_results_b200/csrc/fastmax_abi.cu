@@ -533,7 +533,8 @@ int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args*
   BwdLayout L;
   bwd_layout(pb, a, pl, L);
   if (!L.want_grads && !a->dstate_out) return FASTMAX_ERR_INVALID_ARGUMENT;
-  if (L.want_grads && !(a->dq.ptr && a->dk.ptr && a->dv.ptr)) return FASTMAX_ERR_INVALID_ARGUMENT;
+  // all three gradients or none (an empty tensor's pointer may be null: dq when nq == 0, dk and dv when nk == 0)
+  if (L.want_grads && !((a->dq.ptr || pb->nq == 0) && ((a->dk.ptr && a->dv.ptr) || pb->nk == 0))) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (!pb->causal && (a->state_in || a->dstate_in)) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (pb->nq > 0) {
     if ((rc = check_view(a->q, pb->dtype, true))) return rc;

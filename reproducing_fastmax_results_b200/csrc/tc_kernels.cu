@@ -36,6 +36,33 @@ constexpr int SB_TILE = 9 * BLK;        // 72 columns stored; the MMA's columns 
 constexpr int NTILES = 19;
 constexpr long long WAIT_CYCLES = 4000000000ll;       // ~2 s at 2 GHz
 
+// Which chunks of a scan (by scan index ci = 0 .. nchunks-1, in the order the scan visits them) read the state and
+// which ones add to it.  A chunk "applies" when some of its positions hold rows of the tile that multiplies the state
+// (queries in the forward and dq scans, keys in the dk and dv scans) and the state is not trivially zero; it
+// "updates" when some of its positions hold rows that build the state and a later chunk (or the caller, through
+// state_out) still needs the result.  Both sets are contiguous ranges; a range with first > last is empty.  The
+// bf16 copy of the state is refreshed after the updates c_first .. c_last, i.e. only where an apply follows before the
+// next update (and once before chunk 0 when the state starts from a caller-provided array, h = 1).  Every role of a scan kernel derives its barrier phase counts from
+// these ranges, so causal calls with nk > nq, calls with a carried state and the non-causal layout (all keys first,
+// then all queries) run through the same code.
+struct Sched {
+  int a_first, a_last;
+  int u_first, u_last;
+  int c_first, c_last;
+  int h;
+  __host__ __device__ static int clampi(int x, int lo, int hi) { return x < lo ? lo : (x > hi ? hi : x); }
+  __host__ __device__ bool A(int ci) const { return ci >= a_first && ci <= a_last; }
+  __host__ __device__ bool U(int ci) const { return ci >= u_first && ci <= u_last; }
+  __host__ __device__ bool C(int ci) const { return ci >= c_first && ci <= c_last; }
+  __host__ __device__ int na_total() const { return a_last >= a_first ? a_last - a_first + 1 : 0; }
+  __host__ __device__ int nu_total() const { return u_last >= u_first ? u_last - u_first + 1 : 0; }
+  __host__ __device__ int na_before(int ci) const { return clampi(ci - a_first, 0, na_total()); }   // applies in chunks < ci
+  __host__ __device__ int nu_before(int ci) const { return clampi(ci - u_first, 0, nu_total()); }   // updates in chunks < ci
+  __host__ __device__ int nc_before(int ci) const {                                                 // copies made before chunk ci
+    return h + clampi(ci - c_first, 0, c_last >= c_first ? c_last - c_first + 1 : 0);
+  }
+};
+
 struct FwdParams {
   float* oacc;   // [BH][nq][68]
   int heads, nq, nk, off, nchunks;
@@ -386,18 +413,68 @@ struct JoinOnExit {
   }
 };
 
-static bool tc_forward_supported(const fastmax_problem* pb, const fastmax_forward_args* a) {
+// Positions of a call: keys sit at positions 0 .. nk-1.  Causal: query l sits at position nk - nq + l (it sees the keys
+// up to its own position).  Non-causal: the queries follow the keys, from the next chunk boundary on, so every query
+// sees every key and no chunk holds both; the intra-chunk (masked) kernels are then not needed at all.
+struct ScanGeom {
+  int k0;            // position of query 0
+  int nch;           // chunks of 128 positions
+  int qc0, qc1;      // chunks that hold queries
+  int kc0, kc1;      // chunks that hold keys
+  int nslices, tile_first, state_rows;
+};
+static ScanGeom scan_geom(const fastmax_problem* pb) {
+  ScanGeom g{};
+  g.k0 = pb->causal ? pb->nk - pb->nq : (pb->nk + tc::CH - 1) / tc::CH * tc::CH;
+  const int npos = pb->causal ? pb->nk : g.k0 + pb->nq;
+  g.nch = (npos + tc::CH - 1) / tc::CH;
+  g.qc0 = g.k0 / tc::CH;
+  g.qc1 = pb->nq > 0 ? (g.k0 + pb->nq - 1) / tc::CH : g.qc0 - 1;
+  g.kc0 = 0;
+  g.kc1 = (pb->nk - 1) / tc::CH;
+  g.nslices = pb->order == 2 ? 5 : 1;
+  g.tile_first = pb->order == 2 ? 0 : tc::NTILES - 1;
+  g.state_rows = pb->order == 2 ? 64 * 36 + 65 : 65;
+  return g;
+}
+// Schedule of one scan.  Forward direction (forward pass, dq): query chunks apply, key chunks update.  Reverse
+// direction (dk, dv): key chunks apply, query chunks update, and scan index ci visits chunk nch - 1 - ci.
+static tc::Sched make_sched(const ScanGeom& g, bool reverse, bool has_init, bool want_apply, bool want_state) {
+  tc::Sched sc{};
+  int a0, a1, u0, u1;
+  if (!reverse) { a0 = g.qc0; a1 = g.qc1; u0 = g.kc0; u1 = g.kc1; }
+  else { a0 = g.nch - 1 - g.kc1; a1 = g.nch - 1 - g.kc0; u0 = g.nch - 1 - g.qc1; u1 = g.nch - 1 - g.qc0; }
+  if (!want_apply) { a0 = 0; a1 = -1; }
+  else if (!has_init && a0 == 0) a0 = 1;           // the state is still zero in the first chunk
+  if (!want_state && u1 > a1 - 1) u1 = a1 - 1;     // updates that nothing reads any more
+  sc.a_first = a0; sc.a_last = a1; sc.u_first = u0; sc.u_last = u1;
+  sc.c_first = u0 > a0 - 1 ? u0 : a0 - 1;
+  sc.c_last = u1 < a1 - 1 ? u1 : a1 - 1;
+  sc.h = has_init ? 1 : 0;
+  return sc;
+}
+
+static bool tc_common_supported(const fastmax_problem* pb) {
   if (pb->flags & FASTMAX_FLAG_NO_TENSOR_CORES) return false;
-  if (pb->dtype != FASTMAX_BF16 || pb->d != 64 || pb->order != 2 || !pb->causal) return false;
-  if (!a->o.ptr || a->state_in) return false;   // state_out alone is fine: the scan writes its final state out
-  if (pb->nq <= 0 || pb->nk <= 0) return false;
-  if ((long long)pb->batch * pb->heads * 5 < 64) return false;  // too few CTAs: the segmented engine does better
+  if (pb->dtype != FASTMAX_BF16 || pb->d != 64 || (pb->order != 1 && pb->order != 2)) return false;
+  if (pb->nk <= 0) return false;
+  if ((long long)pb->batch * pb->heads * (pb->order == 2 ? 5 : 1) < 64) return false;  // too few thread blocks: the segmented CUDA-core engine does better
+  if ((long long)pb->nk + pb->nq + 2 * tc::CH >= (1ll << 30)) return false;
+  return true;
+}
+
+static bool tc_forward_supported(const fastmax_problem* pb, const fastmax_forward_args* a) {
+  if (!tc_common_supported(pb)) return false;
+  const bool want_o = a->o.ptr && pb->nq > 0;
+  if (!want_o && !a->state_out) return false;
+  if (!pb->causal && a->state_in) return false;
   return true;
 }
 
 size_t tc_forward_workspace(const fastmax_problem* pb, const fastmax_forward_args* a) {
   if (!tc_forward_supported(pb, a)) return 0;
-  return ((size_t)pb->batch * pb->heads * pb->nq * 68 * sizeof(float) + 255) / 256 * 256 +
+  const bool want_o = a->o.ptr && pb->nq > 0;
+  return (want_o ? ((size_t)pb->batch * pb->heads * pb->nq * 68 * sizeof(float) + 255) / 256 * 256 : 0) +
          transposed_bytes(pb->batch * pb->heads, pb->nk);
 }
 
@@ -434,18 +511,25 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   if (tc_p1_supported(pb, a)) return tc_p1_forward(pb, a, st);
   if (!tc_forward_supported(pb, a)) return FASTMAX_TC_NOT_HANDLED;
   if (ws_bytes < tc_forward_workspace(pb, a)) return FASTMAX_ERR_WORKSPACE;
+  const bool want_o = a->o.ptr && pb->nq > 0;
   CUtensorMap tmq, tmk, tmv;
-  if (!make_map(&tmq, a->q, pb->batch, pb->heads, pb->nq, 64, tc::CH, true) ||
-      !make_map(&tmk, a->k, pb->batch, pb->heads, pb->nk, 64, tc::CH, true) ||
+  if (!make_map(&tmk, a->k, pb->batch, pb->heads, pb->nk, 64, tc::CH, true) ||
       !make_map(&tmv, a->v, pb->batch, pb->heads, pb->nk, 8, tc::CH, false))
     return FASTMAX_TC_NOT_HANDLED;  // layout the copy engine cannot describe: the CUDA-core engine takes it
+  if (want_o) {
+    if (!make_map(&tmq, a->q, pb->batch, pb->heads, pb->nq, 64, tc::CH, true)) return FASTMAX_TC_NOT_HANDLED;
+  } else {
+    tmq = tmk;   // a state-only call applies nothing: the tile is loaded and never read
+  }
   const int bh = pb->batch * pb->heads;
+  const ScanGeom G = scan_geom(pb);
   float* oacc = (float*)ws;
-  const size_t oacc_bytes = ((size_t)bh * pb->nq * 68 * sizeof(float) + 255) / 256 * 256;
+  const size_t oacc_bytes = want_o ? ((size_t)bh * pb->nq * 68 * sizeof(float) + 255) / 256 * 256 : 0;
   __nv_bfloat16* kt = (__nv_bfloat16*)((char*)ws + oacc_bytes);
   CUtensorMap tmkt;
   if (!make_map_t(&tmkt, kt, bh, pb->nk, tokens_padded(pb->nk))) return FASTMAX_TC_NOT_HANDLED;
-  cudaError_t e = cudaMemsetAsync(oacc, 0, (size_t)bh * pb->nq * 68 * sizeof(float), st);
+  cudaError_t e = cudaSuccess;
+  if (want_o) e = cudaMemsetAsync(oacc, 0, (size_t)bh * pb->nq * 68 * sizeof(float), st);
   if (e == cudaSuccess) e = launch_transpose(a->k, pb->batch, pb->heads, pb->nk, 0, kt, st);
   if (e != cudaSuccess) return report_cuda_error(e);
   tc::FwdParams P{};
@@ -453,38 +537,46 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   P.heads = pb->heads;
   P.nq = pb->nq;
   P.nk = pb->nk;
-  P.off = pb->nk - pb->nq;
-  P.nchunks = (pb->nk + tc::CH - 1) / tc::CH;
+  P.off = G.k0;
+  P.nchunks = G.nch;
   P.c0 = pb->a0;
   P.c1 = pb->a1 * pb->inv_temperature;
-  P.c2 = pb->a2 * pb->inv_temperature * pb->inv_temperature;
+  P.c2 = pb->order == 2 ? pb->a2 * pb->inv_temperature * pb->inv_temperature : 0.f;
   e = cudaFuncSetAttribute(tc::s2::scan_apply_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s2::SMEM_BYTES);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(tc::intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::I_SMEM_BYTES);
   if (e != cudaSuccess) return report_cuda_error(e);
   // the scan and the intra-chunk kernel both ADD into the O' accumulator: independent, side by side
+  const bool intra = want_o && pb->causal;
   cudaStream_t ss[2];
   std::unique_lock<std::mutex> side_lock;
-  SideStreams* side = fork_streams(pb, st, 2, ss, side_lock);
+  SideStreams* side = intra ? fork_streams(pb, st, 2, ss, side_lock) : nullptr;
+  if (!intra) ss[0] = ss[1] = st;
   JoinOnExit guard{side, st, 2};
   {
     LaunchScope ls(KK_TC_FWD, ss[0]);
-    tc::s2::ApplyParams A{oacc, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, 0, P.nchunks, P.c0, P.c1, P.c2, a->state_out};
-    tc::s2::scan_apply_kernel<false><<<dim3(5 * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmq, tmkt, tmv, A);
+    tc::s2::ApplyParams A{};
+    A.out = oacc; A.heads = pb->heads; A.nz = pb->nq; A.ny = pb->nk; A.z_shift = G.k0; A.y_shift = 0; A.nchunks = G.nch;
+    A.c0 = P.c0; A.c1 = P.c1; A.c2 = P.c2;
+    A.state_out = a->state_out; A.state_in = a->state_in;
+    A.sc = make_sched(G, false, a->state_in != nullptr, want_o, a->state_out != nullptr);
+    A.nslices = G.nslices; A.tile_first = G.tile_first; A.state_rows = G.state_rows;
+    tc::s2::scan_apply_kernel<false><<<dim3(G.nslices * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmq, tmkt, tmv, A);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
-  {
+  if (intra) {
     LaunchScope ls(KK_TC_INTRA_FWD, ss[1]);
-    tc::intra_fwd_kernel<<<dim3(P.nchunks, 1, bh), tc::I_THREADS, tc::I_SMEM_BYTES, ss[1]>>>(tmq, tmk, tmv, P);
+    const int nch_k = (pb->nk + tc::CH - 1) / tc::CH;
+    tc::intra_fwd_kernel<<<dim3(nch_k, 1, bh), tc::I_THREADS, tc::I_SMEM_BYTES, ss[1]>>>(tmq, tmk, tmv, P);
+    e = cudaGetLastError();
   }
-  e = cudaGetLastError();
   if (e == cudaSuccess) {
     guard.joined = true;
     e = join_streams(side, st, 2);
   }
   if (e != cudaSuccess) return report_cuda_error(e);
-  return launch_finalize_fwd(pb, a, oacc, st);
+  return want_o ? launch_finalize_fwd(pb, a, oacc, st) : FASTMAX_OK;
 }
 
 static int device_sms() {
@@ -500,12 +592,11 @@ static int device_sms() {
 }
 
 static bool tc_backward_supported(const fastmax_problem* pb, const fastmax_backward_args* a) {
-  if (pb->flags & FASTMAX_FLAG_NO_TENSOR_CORES) return false;
-  if (pb->dtype != FASTMAX_BF16 || pb->d != 64 || pb->order != 2 || !pb->causal) return false;
-  if (!a->dq.ptr || !a->dk.ptr || !a->dv.ptr) return false;
-  if (a->state_in || a->dstate_in || a->dstate_out) return false;
-  if (pb->nq <= 0 || pb->nk <= 0) return false;
-  if ((long long)pb->batch * pb->heads * 5 < 64) return false;
+  if (!tc_common_supported(pb) || pb->nq <= 0) return false;
+  const bool want_grads = a->dq.ptr || a->dk.ptr || a->dv.ptr;
+  if (want_grads && !(a->dq.ptr && a->dk.ptr && a->dv.ptr)) return false;
+  if (!want_grads && !a->dstate_out) return false;
+  if (!pb->causal && (a->state_in || a->dstate_in)) return false;
   // the dO' prologue reads o and dO two bf16 at a time
   for (const fastmax_tensor* t : {&a->o, &a->d_out})
     if (((uintptr_t)t->ptr & 3) || (t->stride_b & 1) || (t->stride_h & 1) || (t->stride_n & 1)) return false;
@@ -515,32 +606,35 @@ static bool tc_backward_supported(const fastmax_problem* pb, const fastmax_backw
 struct TcBwdLayout {
   size_t dop, qt, kt, dq, dk, dv, total;
 };
-static void tc_bwd_layout(const fastmax_problem* pb, TcBwdLayout& L) {
+static void tc_bwd_layout(const fastmax_problem* pb, bool want_grads, TcBwdLayout& L) {
   const size_t bh = (size_t)pb->batch * pb->heads;
+  const ScanGeom G = scan_geom(pb);
   auto up = [](size_t x) { return (x + 255) / 256 * 256; };
   size_t off = 0;
   L.dop = off; off += up(bh * pb->nq * 80 * sizeof(__nv_bfloat16));
-  L.qt = off; off += transposed_bytes((int)bh, pb->nk);  // q transposed, aligned with the key positions
-  L.kt = off; off += transposed_bytes((int)bh, pb->nk);  // k transposed
-  L.dq = off; off += up(bh * pb->nq * tc::ACC_LD * sizeof(float));
-  L.dk = off; off += up(bh * pb->nk * tc::ACC_LD * sizeof(float));
-  L.dv = off; off += up(bh * pb->nk * tc::ACC_LD * sizeof(float));
+  L.qt = off; off += transposed_bytes((int)bh, G.k0 + pb->nq);  // q transposed, column = position of the query
+  L.kt = off; if (want_grads) off += transposed_bytes((int)bh, pb->nk);  // k transposed
+  L.dq = off; if (want_grads) off += up(bh * pb->nq * tc::ACC_LD * sizeof(float));
+  L.dk = off; if (want_grads) off += up(bh * pb->nk * tc::ACC_LD * sizeof(float));
+  L.dv = off; if (want_grads) off += up(bh * pb->nk * tc::ACC_LD * sizeof(float));
   L.total = off;
 }
 
 size_t tc_backward_workspace(const fastmax_problem* pb, const fastmax_backward_args* a) {
   if (!tc_backward_supported(pb, a)) return 0;
   TcBwdLayout L;
-  tc_bwd_layout(pb, L);
+  tc_bwd_layout(pb, a->dq.ptr != nullptr, L);
   return L.total;
 }
 
 int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (!tc_backward_supported(pb, a)) return FASTMAX_TC_NOT_HANDLED;
+  const bool want_grads = a->dq.ptr != nullptr;
   TcBwdLayout L;
-  tc_bwd_layout(pb, L);
+  tc_bwd_layout(pb, want_grads, L);
   if (ws_bytes < L.total) return FASTMAX_ERR_WORKSPACE;
   const int bh = pb->batch * pb->heads;
+  const ScanGeom G = scan_geom(pb);
   char* base = (char*)ws;
   __nv_bfloat16* dop = (__nv_bfloat16*)(base + L.dop);
   float* dqa = (float*)(base + L.dq);
@@ -548,16 +642,17 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   float* dva = (float*)(base + L.dv);
   __nv_bfloat16* qt = (__nv_bfloat16*)(base + L.qt);
   __nv_bfloat16* kt = (__nv_bfloat16*)(base + L.kt);
+  const int nqpos = G.k0 + pb->nq;    // positions up to the last query
   CUtensorMap tmq, tmk, tmv, tmdo, tmqt, tmkt;
   fastmax_tensor dopt{dop, (int64_t)pb->heads * pb->nq * 80, (int64_t)pb->nq * 80, 80};
   if (!make_map(&tmq, a->q, pb->batch, pb->heads, pb->nq, 64, tc::CH, true) ||
       !make_map(&tmk, a->k, pb->batch, pb->heads, pb->nk, 64, tc::CH, true) ||
       !make_map(&tmv, a->v, pb->batch, pb->heads, pb->nk, 8, tc::CH, false) ||
       !make_map(&tmdo, dopt, pb->batch, pb->heads, pb->nq, 8, tc::CH, false, 80) ||
-      !make_map_t(&tmqt, qt, bh, pb->nk, tokens_padded(pb->nk)) ||
-      !make_map_t(&tmkt, kt, bh, pb->nk, tokens_padded(pb->nk)))
+      !make_map_t(&tmqt, qt, bh, nqpos, tokens_padded(nqpos)) ||
+      (want_grads && !make_map_t(&tmkt, kt, bh, pb->nk, tokens_padded(pb->nk))))
     return FASTMAX_TC_NOT_HANDLED;
-  cudaError_t e = cudaSuccess;   // (no memset of the accumulators: the intra-chunk kernel writes every row first)
+  cudaError_t e = cudaSuccess;
   {
     const long long nrows = (long long)bh * pb->nq;
     const int threads = 256;
@@ -579,6 +674,30 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
+  const float c0 = pb->a0, c1 = pb->a1 * pb->inv_temperature;
+  const float c2 = pb->order == 2 ? pb->a2 * pb->inv_temperature * pb->inv_temperature : 0.f;
+  e = cudaFuncSetAttribute(tc::s2::scan_apply_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s2::SMEM_BYTES);
+  if (e != cudaSuccess) return report_cuda_error(e);
+  auto dv_params = [&](bool want_apply) {
+    tc::s2::ApplyParams A{};
+    A.out = want_apply ? dva : nullptr; A.heads = pb->heads; A.nz = pb->nk; A.ny = pb->nk; A.z_shift = 0; A.y_shift = G.k0;
+    A.nchunks = G.nch; A.c0 = c0; A.c1 = c1; A.c2 = c2;
+    A.state_out = a->dstate_out; A.state_in = a->dstate_in;
+    A.sc = make_sched(G, true, a->dstate_in != nullptr, want_apply, a->dstate_out != nullptr);
+    A.nslices = G.nslices; A.tile_first = G.tile_first; A.state_rows = G.state_rows;
+    return A;
+  };
+  if (!want_grads) {
+    // only the gradient moments are wanted (what a sequence-parallel rank publishes): the dv scan, updates only
+    e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, G.k0, qt, st);
+    if (e != cudaSuccess) return report_cuda_error(e);
+    {
+      LaunchScope ls(KK_TC_BWD_DV, st);
+      tc::s2::scan_apply_kernel<true><<<dim3(G.nslices * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, st>>>(tmk, tmqt, tmdo, dv_params(false));
+    }
+    e = cudaGetLastError();
+    return e == cudaSuccess ? FASTMAX_OK : report_cuda_error(e);
+  }
   // The chain-rule scans rebalance registers between their warp groups with setmaxnreg; that only terminates if
   // the CTA was launched with the register count the budget in tc_scan3.cuh assumes.  Otherwise the CUDA-core
   // engine takes the call.
@@ -589,41 +708,40 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
            f0.numRegs >= tc::s3::REG_LAUNCH && f1.numRegs >= tc::s3::REG_LAUNCH;
   }();
   if (!chain_ok) return FASTMAX_TC_NOT_HANDLED;
-  const float c0 = pb->a0, c1 = pb->a1 * pb->inv_temperature, c2 = pb->a2 * pb->inv_temperature * pb->inv_temperature;
-  const int nch = (pb->nk + tc::CH - 1) / tc::CH;
-  e = cudaFuncSetAttribute(tc::s2::scan_apply_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s2::SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(tc::s3::scan_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s3::SMEM_BYTES);
+  e = cudaFuncSetAttribute(tc::s3::scan_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s3::SMEM_BYTES);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(tc::s3::scan_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s3::SMEM_BYTES);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(tc::intra_bwd_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::IP_SMEM_BYTES);
   if (e != cudaSuccess) return report_cuda_error(e);
-  // The intra-chunk kernel goes first: it STORES its part into every row of the three accumulators (no memset).  It
-  // fills all SMs by itself (one CTA per SM), so nothing is lost by letting the scans wait for it.  The three scans
-  // then ADD on top with reduce operations, side by side: dv on the caller's stream, dq and dk on side streams.  An
-  // accumulator is cast to its output as soon as its scan is done, on that scan's stream, so the casts overlap the
-  // tails of the scans that are still running.
-  // The transposed copies are only read by the scans: they are made on the side streams while the intra-chunk
-  // kernel (which leaves the memory system idle) runs.
+  // Causal: the intra-chunk kernel goes first: it STORES its part into every row of the three accumulators (no
+  // memset).  It fills all SMs by itself (one CTA per SM), so nothing is lost by letting the scans wait for it.  The
+  // three scans then ADD on top with reduce operations, side by side: dv on the caller's stream, dq and dk on side
+  // streams.  An accumulator is cast to its output as soon as its scan is done, on that scan's stream, so the casts
+  // overlap the tails of the scans that are still running.  The transposed copies are only read by the scans: they
+  // are made on the side streams while the intra-chunk kernel (which leaves the memory system idle) runs.
+  // Non-causal: no chunk holds both queries and keys, so there is no intra-chunk term; the accumulators are zeroed.
   cudaStream_t ss[3];
   std::unique_lock<std::mutex> side_lock;
   SideStreams* side = fork_streams(pb, st, 3, ss, side_lock);
   JoinOnExit guard{side, st, 3};
   if (side) {
     e = launch_transpose(a->k, pb->batch, pb->heads, pb->nk, 0, kt, ss[1]);
-    if (e == cudaSuccess) e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, pb->nk - pb->nq, qt, ss[2]);
+    if (e == cudaSuccess) e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, G.k0, qt, ss[2]);
     if (e == cudaSuccess) e = cudaEventRecord(side->aux, ss[2]);   // the dv scan on the caller's stream reads q^T too
     if (e != cudaSuccess) return report_cuda_error(e);
   }
-  {
-    tc::IntraBwdParams I{dqa, dka, dva, pb->heads, pb->nq, pb->nk, pb->nk - pb->nq, c0, c1, c2};
+  if (pb->causal) {
+    const int nch_k = (pb->nk + tc::CH - 1) / tc::CH;
+    tc::IntraBwdParams I{dqa, dka, dva, pb->heads, pb->nq, pb->nk, G.k0, c0, c1, c2};
     LaunchScope ls(KK_TC_INTRA_BWD, ss[0]);
-    const int nitems = nch * bh;
+    const int nitems = nch_k * bh;
     const int ctas = nitems < device_sms() ? nitems : device_sms();   // persistent: one CTA per SM walks the items
-    tc::intra_bwd_pipe_kernel<<<dim3(ctas), tc::IP_THREADS, tc::IP_SMEM_BYTES, ss[0]>>>(tmq, tmk, tmv, tmdo, I, nch, nitems);
+    tc::intra_bwd_pipe_kernel<<<dim3(ctas), tc::IP_THREADS, tc::IP_SMEM_BYTES, ss[0]>>>(tmq, tmk, tmv, tmdo, I, nch_k, nitems);
+    e = cudaGetLastError();
+  } else {
+    e = cudaMemsetAsync(dqa, 0, L.total - L.dq, ss[0]);   // the three accumulators are contiguous
   }
-  e = cudaGetLastError();
   if (e == cudaSuccess && side) {
     e = cudaEventRecord(side->mid, ss[0]);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(ss[1], side->mid, 0);
@@ -631,30 +749,37 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
     if (e == cudaSuccess) e = cudaStreamWaitEvent(ss[0], side->aux, 0);
   } else if (e == cudaSuccess) {   // one stream: the copies simply follow
     e = launch_transpose(a->k, pb->batch, pb->heads, pb->nk, 0, kt, st);
-    if (e == cudaSuccess) e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, pb->nk - pb->nq, qt, st);
+    if (e == cudaSuccess) e = launch_transpose(a->q, pb->batch, pb->heads, pb->nq, G.k0, qt, st);
   }
   if (e != cudaSuccess) return report_cuda_error(e);
+  auto chain_params = [&](bool dk) {
+    tc::s3::ChainParams C{};
+    C.out = dk ? dka : dqa;
+    const fastmax_tensor& z = dk ? a->k : a->q;
+    C.z = View{z.ptr, z.stride_b, z.stride_h, z.stride_n};
+    C.heads = pb->heads; C.nz = dk ? pb->nk : pb->nq; C.nk = pb->nk; C.z_shift = dk ? 0 : G.k0; C.do_shift = G.k0;
+    C.nchunks = G.nch; C.c1 = c1; C.c2 = c2;
+    C.state_in = dk ? a->dstate_in : a->state_in;
+    C.sc = make_sched(G, dk, C.state_in != nullptr, true, false);
+    C.nslices = G.nslices; C.tile_first = G.tile_first; C.state_rows = G.state_rows;
+    return C;
+  };
   {
     LaunchScope ls(KK_TC_BWD_Q, ss[1]);
-    tc::s3::ChainParams C{dqa, View{a->q.ptr, a->q.stride_b, a->q.stride_h, a->q.stride_n}, pb->heads, pb->nq, pb->nk,
-                          pb->nk - pb->nq, pb->nk - pb->nq, nch, c1, c2};
-    tc::s3::scan_chain_kernel<false><<<dim3(5 * bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, ss[1]>>>(tmkt, tmv, tmdo, C);
+    tc::s3::scan_chain_kernel<false><<<dim3(G.nslices * bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, ss[1]>>>(tmkt, tmv, tmdo, chain_params(false));
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
   {
     // dk: the reverse chain-rule scan; dv: the reverse apply + update scan
     LaunchScope ls(KK_TC_BWD_KV, ss[2]);
-    tc::s3::ChainParams C{dka, View{a->k.ptr, a->k.stride_b, a->k.stride_h, a->k.stride_n}, pb->heads, pb->nk, pb->nk, 0,
-                          pb->nk - pb->nq, nch, c1, c2};
-    tc::s3::scan_chain_kernel<true><<<dim3(5 * bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, ss[2]>>>(tmqt, tmv, tmdo, C);
+    tc::s3::scan_chain_kernel<true><<<dim3(G.nslices * bh), tc::s3::THREADS, tc::s3::SMEM_BYTES, ss[2]>>>(tmqt, tmv, tmdo, chain_params(true));
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);
   {
-    tc::s2::ApplyParams A{dva, pb->heads, pb->nk, pb->nk, 0, pb->nk - pb->nq, nch, c0, c1, c2};
     LaunchScope ls(KK_TC_BWD_DV, ss[0]);
-    tc::s2::scan_apply_kernel<true><<<dim3(5 * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmk, tmqt, tmdo, A);
+    tc::s2::scan_apply_kernel<true><<<dim3(G.nslices * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmk, tmqt, tmdo, dv_params(true));
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return report_cuda_error(e);

@@ -49,6 +49,7 @@ constexpr int OFF_VP = OFF_SB + 4 * SB_TILE;           // 73728, 2 buffers
 constexpr int OFF_RAWQ = OFF_VP + 2 * VPBUF;           // 114688, 2 x REGION, 128-byte swizzle
 constexpr int OFF_KT = OFF_RAWQ + 2 * REGION;          // 147456, 2 x KT_BUF (two 64-token boxes each, not swizzled)
 constexpr int OFF_BAR = OFF_KT + 2 * KT_BUF;           // 184320
+constexpr int OFF_TAB = OFF_BAR + 352;                 // slab tables of the producer sets: [3 sets][3 kinds][3 bases] words
 constexpr int OFF_OST = OFF_BAR + 512;                 // output staging for the bulk reduce: 128 rows x <= 68 floats
 constexpr int OST_BYTES = CH * 68 * 4;                 // 34816
 constexpr int SMEM_BYTES = OFF_OST + OST_BYTES + 1024;
@@ -58,6 +59,7 @@ constexpr uint32_t COL_O = 320u, COL_A = 400u;
 constexpr int B_FULL_Q = 0, B_FULL_K = 3, B_EMPTY = 6, B_Q_READY = 9, B_Q_FREE = 11, B_KT_READY = 13, B_KT_FREE = 15,
               B_VP_READY = 17, B_VP_FREE = 19, B_SB_READY = 21, B_S_DONE = 25, B_A_DONE = 29, B_O_DONE = 33, B_O_FREE = 34,
               B_COUNT = 35;
+static_assert(B_COUNT * 8 <= 320 && OFF_TAB + 27 * 4 <= OFF_OST, "barrier block layout");
 
 struct ApplyParams {
   float* out;          // forward: O' accumulator [BH][nz][68]; dv scan: dV accumulator [BH][nz][ACC_LD = 68]
@@ -68,7 +70,13 @@ struct ApplyParams {
   int y_shift;         // Y row of chunk position p is p - y_shift (forward: 0; dv scan: nk - nq)
   int nchunks;
   float c0, c1, c2;
-  float* state_out;    // forward only, optional: moment state of all keys, float32 [BH][64 * 36 + 65][68] (exchange layout)
+  float* state_out;        // optional: the final state (forward: moments of all keys; dv scan: gradient moments), float32
+                           // [BH][state_rows][68] (exchange layout)
+  const float* state_in;   // optional: the state the scan starts from (same layout); sc.h = 1
+  Sched sc;                // which chunks apply / update
+  int nslices;             // thread blocks per head (order 2: 5; order 1: 1)
+  int tile_first;          // first feature tile of the problem (order 2: 0; order 1: the linear/constant tile)
+  int state_rows;          // rows of the exchange layout (order 2: 64 * 36 + 65; order 1: 65)
 };
 
 // A bounded wait gave up: count the wait site (first failure of the CTA only), raise the CTA's abort flag, set the
@@ -196,13 +204,15 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
   // The five slices of a head are neighbours in the grid, so they run at about the same time and share the head's
   // q / k / v tiles through L2.  gridDim.x = 5 * batch * heads.
-  const int head = (int)blockIdx.x / 5, slice = (int)blockIdx.x - 5 * head;
+  const int head = (int)blockIdx.x / P.nslices, slice = (int)blockIdx.x - P.nslices * head;
   const int b_idx = head / P.heads, h_idx = head - b_idx * P.heads;
-  const int tile0 = slice * 4;
+  const int tile0 = P.tile_first + slice * 4;
   const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
   const int nch = P.nchunks;
+  const Sched sc = P.sc;
   const bool lin_slice = (tile0 + ntl == NTILES);   // this slice holds the linear/constant tile: weights go into Sb
   auto chunk_of = [&](int i) -> int { return DV ? (nch - 1 - i) : i; };  // i-th chunk of the scan
+  uint32_t* slab_tabs = reinterpret_cast<uint32_t*>(sm + OFF_TAB);
 
   if (tid == 0) {
     // arrivals are one per WARP (an elected lane after __syncwarp), not one per thread
@@ -217,6 +227,26 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
     mbar_init(&bars[B_O_FREE], 4);
     *abort_flag = 0;
     fence_mbar_init();
+    // Slab tables.  A chunk's slab sequence depends on its kind: 0 = apply + update (per tile A0 U0 A1 U1, in the last
+    // tile A0 A1 U0 U1 so the output drain overlaps the updates), 1 = update only (U0 U1), 2 = apply only (A0 A1).
+    // Entry [set][kind][base]: the slabs of such a chunk that fall into ring slot `set` when the chunk's first slab has
+    // sequence index `base` (mod 3); 4 bits per slab (tile | apply << 2 | half << 3), their count in bits 28..31.
+    for (int set = 0; set < NSETS; ++set)
+      for (int kind = 0; kind < 3; ++kind)
+        for (int base = 0; base < NSETS; ++base) {
+          uint32_t tab = 0, n = 0;
+          const int nsl = (kind == 0 ? 4 : 2) * ntl;
+          for (int i = 0; i < nsl; ++i) {
+            if ((base + i) % NSETS != set) continue;
+            int t, half;
+            bool is_q;
+            if (kind == 0) { t = i >> 2; slab_kind(false, t == ntl - 1, i & 3, is_q, half); }
+            else { t = i >> 1; is_q = (kind == 2); half = i & 1; }
+            tab |= (uint32_t)(t | ((is_q ? 1 : 0) << 2) | (half << 3)) << (4 * n);
+            ++n;
+          }
+          slab_tabs[(set * 3 + kind) * 3 + base] = tab | (n << 28);
+        }
   }
   if (w == 0) tmem_alloc(tmem_slot, 512);
   // the MMAs read one column block past the nine stored ones of each B operand: keep those bytes finite
@@ -245,55 +275,39 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
       if (tile0 + t < NTILES - 1) { pair_decode(2 * (tile0 + t), 8, a0, b0); pair_decode(2 * (tile0 + t) + 1, 8, a1, b1); }
       pairs |= (uint64_t)(a0 | (b0 << 4) | (a1 << 8) | (b1 << 12)) << (16 * t);
     }
-    // This set's slabs of a chunk, as tables (4 bits per slab: tile | apply << 2 | half << 3; count in bits 28..31):
-    // one for the first chunk (two update slabs per tile) and one per value of (index of the chunk's first slab) mod 3.
-    uint32_t tab_first = 0, tabs[3] = {0u, 0u, 0u};
-    {
-      uint32_t n = 0;
-      for (int i = 0; i < 2 * ntl; ++i)
-        if (i % NSETS == set) { tab_first |= (uint32_t)((i >> 1) | ((i & 1) << 3)) << (4 * n); ++n; }
-      tab_first |= n << 28;
-      for (int base = 0; base < NSETS; ++base) {
-        n = 0;
-        for (int i = 0; i < 4 * ntl; ++i) {
-          if ((base + i) % NSETS != set) continue;
-          bool is_q; int half;
-          slab_kind(false, (i >> 2) == ntl - 1, i & 3, is_q, half);
-          tabs[base] |= (uint32_t)((i >> 2) | ((is_q ? 1 : 0) << 2) | (half << 3)) << (4 * n);
-          ++n;
-        }
-        tabs[base] |= n << 28;
-      }
-    }
     uint32_t base = 0; // (index of the current chunk's first slab) mod 3
     uint32_t k = 0;    // slabs this set has produced = phase count of its slot
     bool ok = true;
     for (int ci = 0; ci < nch && ok; ++ci) {
       const int buf = ci & 1;
       if (!WAIT(B_KT_READY + buf, (uint32_t)(ci >> 1)) || !WAIT(B_Q_READY + buf, (uint32_t)(ci >> 1))) { FAIL(200); break; }
-      const uint8_t* raw = rawq + buf * REGION;
-      const uint8_t* xt = kt + buf * KT_BUF;
-      const uint32_t tab = ci == 0 ? tab_first : (base == 0 ? tabs[0] : (base == 1 ? tabs[1] : tabs[2]));
-      const int cnt = (int)(tab >> 28);
+      const bool has_a = sc.A(ci), has_u = sc.U(ci);
+      if (has_a || has_u) {
+        const int kind = (has_a && has_u) ? 0 : (has_u ? 1 : 2);
+        const uint8_t* raw = rawq + buf * REGION;
+        const uint8_t* xt = kt + buf * KT_BUF;
+        const uint32_t tab = slab_tabs[(set * 3 + kind) * 3 + (int)base];
+        const int cnt = (int)(tab >> 28);
 #pragma unroll 1
-      for (int e = 0; e < cnt; ++e, ++k) {
-        const uint32_t d4 = (tab >> (4 * e)) & 15u;
-        const int t = (int)(d4 & 3u), half = (int)(d4 >> 3);
-        const bool is_q = (d4 & 4u) != 0;
-        const bool lin = lin_slice && t == ntl - 1;
-        const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
-        uint32_t r[32];
-        make_slab(r, is_q, half, lin, !lin_slice, row, raw, xt, pr);
-        if (k > 0 && !WAIT(B_EMPTY + set, k - 1)) { FAIL(201); ok = false; break; }
-        __syncwarp();
-        tc_fence_after_sync();
-        tmem_st32(slot_addr, r);
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[(is_q ? B_FULL_Q : B_FULL_K) + set]);
+        for (int e = 0; e < cnt; ++e, ++k) {
+          const uint32_t d4 = (tab >> (4 * e)) & 15u;
+          const int t = (int)(d4 & 3u), half = (int)(d4 >> 3);
+          const bool is_q = (d4 & 4u) != 0;
+          const bool lin = lin_slice && t == ntl - 1;
+          const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
+          uint32_t r[32];
+          make_slab(r, is_q, half, lin, !lin_slice, row, raw, xt, pr);
+          if (k > 0 && !WAIT(B_EMPTY + set, k - 1)) { FAIL(201); ok = false; break; }
+          __syncwarp();
+          tc_fence_after_sync();
+          tmem_st32(slot_addr, r);
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[(is_q ? B_FULL_Q : B_FULL_K) + set]);
+        }
+        base = (base + (uint32_t)((kind == 0 ? 4 : 2) * ntl)) % NSETS;
       }
-      base = (base + (uint32_t)((ci == 0 ? 2 : 4) * ntl)) % NSETS;
       if (ok) {
         __syncwarp();
         if (lane == 0) {
@@ -308,12 +322,81 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
     const uint32_t lane_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16);
     float* obase = P.out + (long long)head * P.nz * OUT_LD;
     const float out_scale = lin_slice ? 1.f : P.c2;   // pair-tile slices: the common weight c2, applied once, exactly
+    constexpr int ST_LD = 68;
     bool ok = true;
+    // S_t (float32, TMEM) -> Sb_t (bf16, shared memory), the B operand of the apply MMAs
+    auto convert_tile = [&](int t) {
+      uint8_t* dst = sb + t * SB_TILE + l * 16;
+      if (lin_slice) {  // weights inside the copy: c2 / 2 c2 per unit, c1 and c0 in the linear/constant tile
+        const float wgt = tile_weight(tile0 + t, l, P.c0, P.c1, P.c2);
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + 80u * t + 32u * part, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jb = 0; jb < 4; ++jb) store_block8(dst + (4 * part + jb) * BLK, &r[8 * jb], wgt);
+        }
+        uint32_t r8[8];
+        tmem_ld8(lane_addr + 80u * t + 64u, r8);
+        tmem_ld_wait();
+        store_block8(dst + 8 * BLK, r8, wgt);
+      } else {          // plain rounding: the weights are in the apply slabs (factor 2) and in the drain (c2)
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + 80u * t + 32u * part, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jb = 0; jb < 4; ++jb) store_block8_plain(dst + (4 * part + jb) * BLK, &r[8 * jb]);
+        }
+        uint32_t r8[8];
+        tmem_ld8(lane_addr + 80u * t + 64u, r8);
+        tmem_ld_wait();
+        store_block8_plain(dst + 8 * BLK, r8);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[B_SB_READY + t]);
+    };
+    if (sc.h) {
+      // The scan starts from the caller's state: its rows go into the TMEM accumulators (80 columns: 64 values, the
+      // denominator moment, zeros) and the first bf16 copy is made from them.  The arrival on SB_READY releases both
+      // issuers, so it also orders these tensor-memory stores before the first update MMA.
+      const float* sbase = P.state_in + (long long)head * P.state_rows * ST_LD;
+      for (int t = 0; t < ntl; ++t) {
+        const int srow = 128 * (tile0 + t - P.tile_first) + l;
+        uint32_t ra[32], rb[32], rc[16];
+        if (srow < P.state_rows) {
+          const float4* src = reinterpret_cast<const float4*>(sbase + (long long)srow * ST_LD);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 x = src[j], y = src[8 + j];
+            ra[4 * j] = __float_as_uint(x.x); ra[4 * j + 1] = __float_as_uint(x.y); ra[4 * j + 2] = __float_as_uint(x.z); ra[4 * j + 3] = __float_as_uint(x.w);
+            rb[4 * j] = __float_as_uint(y.x); rb[4 * j + 1] = __float_as_uint(y.y); rb[4 * j + 2] = __float_as_uint(y.z); rb[4 * j + 3] = __float_as_uint(y.w);
+          }
+          rc[0] = __float_as_uint(src[16].x);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ra[j] = rb[j] = 0u;
+          rc[0] = 0u;
+        }
+#pragma unroll
+        for (int j = 1; j < 16; ++j) rc[j] = 0u;
+        tmem_st32(lane_addr + 80u * t, ra);
+        tmem_st32(lane_addr + 80u * t + 32u, rb);
+        tmem_st16(lane_addr + 80u * t + 64u, rc);
+        tmem_st_wait();
+        convert_tile(t);
+      }
+    }
     for (int ci = 0; ci < nch && ok; ++ci) {
       const int c = chunk_of(ci);
+      const bool has_a = sc.A(ci), has_c = sc.C(ci);
       for (int t = 0; t < ntl && ok; ++t) {
-        if (t == ntl - 1 && ci > 0) {  // the output of this chunk is complete once the last apply has finished
-          if (!WAIT(B_O_DONE, (uint32_t)(ci - 1))) { FAIL(220); ok = false; break; }
+        if (t == ntl - 1 && has_a) {  // the output of this chunk is complete once the last apply has finished
+          if (!WAIT(B_O_DONE, (uint32_t)sc.na_before(ci))) { FAIL(220); ok = false; break; }
           __syncwarp();
           tc_fence_after_sync();
           uint32_t ra[32], rb[32], rc[8];
@@ -356,60 +439,29 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
             }
           }
         }
-        if (ci < nch - 1) {  // the bf16 copy of S_t feeds the next chunk's apply
-          // S_t is final (update issuer) and Sb_t is no longer read (apply issuer; the first chunk has no apply)
-          if (!WAIT(B_S_DONE + t, (uint32_t)ci) || (ci > 0 && !WAIT(B_A_DONE + t, (uint32_t)(ci - 1)))) { FAIL(221); ok = false; break; }
+        if (has_c) {  // the bf16 copy of S_t feeds the next apply
+          // S_t is final (this chunk's update) and Sb_t is no longer read (the applies up to and including this chunk's)
+          const int na_thr = sc.na_before(ci) + (has_a ? 1 : 0);
+          if (!WAIT(B_S_DONE + t, (uint32_t)sc.nu_before(ci)) || (na_thr > 0 && !WAIT(B_A_DONE + t, (uint32_t)(na_thr - 1)))) { FAIL(221); ok = false; break; }
           __syncwarp();
           tc_fence_after_sync();
-          uint8_t* dst = sb + t * SB_TILE + l * 16;
-          if (lin_slice) {  // weights inside the copy: c2 / 2 c2 per unit, c1 and c0 in the linear/constant tile
-            const float wgt = tile_weight(tile0 + t, l, P.c0, P.c1, P.c2);
-#pragma unroll
-            for (int part = 0; part < 2; ++part) {
-              uint32_t r[32];
-              tmem_ld32(lane_addr + 80u * t + 32u * part, r);
-              tmem_ld_wait();
-#pragma unroll
-              for (int jb = 0; jb < 4; ++jb) store_block8(dst + (4 * part + jb) * BLK, &r[8 * jb], wgt);
-            }
-            uint32_t r8[8];
-            tmem_ld8(lane_addr + 80u * t + 64u, r8);
-            tmem_ld_wait();
-            store_block8(dst + 8 * BLK, r8, wgt);
-          } else {          // plain rounding: the weights are in the apply slabs (factor 2) and in the drain (c2)
-#pragma unroll
-            for (int part = 0; part < 2; ++part) {
-              uint32_t r[32];
-              tmem_ld32(lane_addr + 80u * t + 32u * part, r);
-              tmem_ld_wait();
-#pragma unroll
-              for (int jb = 0; jb < 4; ++jb) store_block8_plain(dst + (4 * part + jb) * BLK, &r[8 * jb]);
-            }
-            uint32_t r8[8];
-            tmem_ld8(lane_addr + 80u * t + 64u, r8);
-            tmem_ld_wait();
-            store_block8_plain(dst + 8 * BLK, r8);
-          }
-          fence_proxy_async_smem();
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars[B_SB_READY + t]);
+          convert_tile(t);
         }
       }
     }
-    if (!DV && P.state_out != nullptr && ok) {
-      // The caller wants the moment state of all keys: S_t is complete once the last chunk's update has finished.
-      // Tile rows are the state's rows (two 64-feature pair units per tile, then the linear rows and the constant);
-      // the values are un-weighted sums, which is the exchange format.  Features were rounded to bf16 before the
-      // products were summed in float32.
-      constexpr int ST_ROWS = 64 * 36 + 65, ST_LD = 68;
-      float* sbase = P.state_out + (long long)head * ST_ROWS * ST_LD;
+    if (P.state_out != nullptr && ok) {
+      // The caller wants the final state: S_t is complete once the last update has finished.  Tile rows are the
+      // state's rows (two 64-feature pair units per tile, then the linear rows and the constant); the values are
+      // un-weighted sums, which is the exchange format.  Features were rounded to bf16 before the products were
+      // summed in float32.
+      float* sbase = P.state_out + (long long)head * P.state_rows * ST_LD;
+      const int nu = sc.nu_total();
       for (int t = 0; t < ntl; ++t) {
-        if (nch > 0 && !WAIT(B_S_DONE + t, (uint32_t)(nch - 1))) { FAIL(224); break; }
+        if (nu > 0 && !WAIT(B_S_DONE + t, (uint32_t)(nu - 1))) { FAIL(224); break; }
         __syncwarp();
         tc_fence_after_sync();
         uint32_t ra[32], rb[32], rc[8];
-        if (nch > 0) {
+        if (nu > 0 || sc.h) {
           tmem_ld32(lane_addr + 80u * t, ra);
           tmem_ld32(lane_addr + 80u * t + 32u, rb);
           tmem_ld8(lane_addr + 80u * t + 64u, rc);
@@ -419,8 +471,8 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
           for (int j = 0; j < 32; ++j) ra[j] = rb[j] = 0u;
           rc[0] = 0u;
         }
-        const int srow = 128 * (tile0 + t) + l;
-        if (srow < ST_ROWS) {
+        const int srow = 128 * (tile0 + t - P.tile_first) + l;
+        if (srow < P.state_rows) {
           float4* dst = reinterpret_cast<float4*>(sbase + (long long)srow * ST_LD);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -473,44 +525,49 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
     auto wrap = [](uint32_t x) -> uint32_t { return x >= NRING ? x - NRING : x; };  // x < 2 * NRING
     for (int ci = 0; ci < nch && ok; ++ci) {
       const uint64_t dB_Vc = dB_V + (uint64_t)(((ci & 1) * VPBUF) >> 4);
+      const bool has_a = sc.A(ci), has_u = sc.U(ci);
+      const int nc = sc.nc_before(ci);     // copies of the state made so far: this chunk works with copy number nc - 1
+      // the Y tile is loaded for every chunk; a chunk without an update still hands its buffer back (below)
       if (!mine_q && !WAIT(B_VP_READY + (ci & 1), (uint32_t)(ci >> 1))) { FAIL(233); break; }
-      if (mine_q && ci >= 2 && !WAIT(B_O_FREE, (uint32_t)(ci - 2))) { FAIL(231); break; }
-      for (int t = 0; t < ntl && ok; ++t) {
+      if (mine_q && has_a) {               // the output accumulator is free once the previous apply has been drained
+        const int na = sc.na_before(ci);
+        if (na > 0 && !WAIT(B_O_FREE, (uint32_t)(na - 1))) { FAIL(231); break; }
+      }
+      // positions of a tile's slabs in the chunk's slab sequence (see the slab tables)
+      const bool both = has_a && has_u;
+      for (int t = 0; t < ntl && ok && (has_a || has_u); ++t) {
         const bool last = (t == ntl - 1);
-        if (ci == 0) {  // slabs of the tile: U0 U1
-          if (!mine_q) {
+        const uint32_t a1pos = both ? (last ? 1u : 2u) : 1u, u0pos = both ? (last ? 2u : 1u) : 0u, u1pos = both ? 3u : 1u;
+        if (mine_q ? has_a : has_u) {
+          // Sb_t holds the copy this chunk's apply reads; the update may overwrite S_t once that copy exists
+          if (nc > 0 && !WAIT(B_SB_READY + t, (uint32_t)(nc - 1))) { FAIL(230); ok = false; break; }
+          if (mine_q) {
+            const uint32_t d = tmem_base + COL_O;
+            const uint64_t b = dB_S + (uint64_t)((t * SB_TILE) >> 4);
+            ok = issue(s0, d, b, t > 0 ? 1u : 0u, nullptr, nullptr) &&
+                 issue(wrap(s0 + a1pos), d, b + 64u, 1u, &bars[B_A_DONE + t], last ? &bars[B_O_DONE] : nullptr);
+            if (!ok) FAIL(232);
+          } else {
             const uint32_t d = tmem_base + 80u * t;
-            ok = issue(s0, d, dB_Vc, 0u, nullptr, nullptr) &&
-                 issue(wrap(s0 + 1), d, dB_Vc + 64u, 1u, &bars[B_S_DONE + t], last ? &bars[B_VP_FREE + (ci & 1)] : nullptr);
+            const uint32_t acc0 = (sc.nu_before(ci) > 0 || sc.h) ? 1u : 0u;   // the first update starts the accumulator
+            ok = issue(wrap(s0 + u0pos), d, dB_Vc, acc0, nullptr, nullptr) &&
+                 issue(wrap(s0 + u1pos), d, dB_Vc + 64u, 1u, &bars[B_S_DONE + t], last ? &bars[B_VP_FREE + (ci & 1)] : nullptr);
             if (!ok) FAIL(234);
           }
-          s0 = wrap(s0 + 2);
-          continue;
         }
-        // Sb_t holds S_t of the previous chunk (apply reads it; update may overwrite S_t once it has been copied)
-        if (!WAIT(B_SB_READY + t, (uint32_t)(ci - 1))) { FAIL(230); ok = false; break; }
-        // slabs of the tile: A0 U0 A1 U1, in the last tile A0 A1 U0 U1
-        if (mine_q) {
-          const uint32_t d = tmem_base + COL_O;
-          const uint64_t b = dB_S + (uint64_t)((t * SB_TILE) >> 4);
-          ok = issue(s0, d, b, t > 0 ? 1u : 0u, nullptr, nullptr) &&
-               issue(wrap(s0 + (last ? 1u : 2u)), d, b + 64u, 1u, &bars[B_A_DONE + t], last ? &bars[B_O_DONE] : nullptr);
-          if (!ok) FAIL(232);
-        } else {
-          const uint32_t d = tmem_base + 80u * t;
-          ok = issue(wrap(s0 + (last ? 2u : 1u)), d, dB_Vc, 1u, nullptr, nullptr) &&
-               issue(s0 /* s0 + 3 */, d, dB_Vc + 64u, 1u, &bars[B_S_DONE + t], last ? &bars[B_VP_FREE + (ci & 1)] : nullptr);
-          if (!ok) FAIL(234);
-        }
-        s0 = wrap(s0 + 1);  // four slabs per tile: (s0 + 4) mod 3
+        s0 = wrap(s0 + (both ? 1u : 2u));  // four (or two) slabs per tile, modulo the three ring slots
+      }
+      if (ok && !mine_q && !has_u) {       // nothing of this chunk reads the Y buffer
+        if (elect_one()) mma_commit(&bars[B_VP_FREE + (ci & 1)]);
+        __syncwarp();
       }
     }
     // every MMA of this issuer has completed once its last commit has arrived
     if (ok && nch > 0) {
       if (!mine_q) {
         if (!wait_fast(&bars[B_VP_FREE + ((nch - 1) & 1)], (uint32_t)((nch - 1) >> 1) & 1u, abort_flag)) FAIL(235);
-      } else if (nch > 1) {
-        if (!wait_fast(&bars[B_A_DONE + ntl - 1], (uint32_t)(nch - 2) & 1u, abort_flag)) FAIL(236);
+      } else if (sc.na_total() > 0) {
+        if (!wait_fast(&bars[B_A_DONE + ntl - 1], (uint32_t)(sc.na_total() - 1) & 1u, abort_flag)) FAIL(236);
       }
     }
     tc_fence_after_sync();

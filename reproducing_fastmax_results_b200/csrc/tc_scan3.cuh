@@ -66,6 +66,10 @@ struct ChainParams {
   int do_shift;        // dO' row of chunk position p is p - do_shift (nk - nq)
   int nchunks;
   float c1, c2;
+  const float* state_in;   // optional: the state the scan starts from (dq: moments of earlier keys; dk: gradient moments of
+                           // later queries), float32 [BH][state_rows][68]; sc.h = 1
+  Sched sc;                // which chunks run the chain rule ("apply") / update the state
+  int nslices, tile_first, state_rows;   // as in s2::ApplyParams
 };
 
 template <int R> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R)); }
@@ -104,11 +108,12 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
   // The five slices of a head are neighbours in the grid, so they run at about the same time and share the head's
   // q / k / v tiles through L2.  gridDim.x = 5 * batch * heads.
-  const int head = (int)blockIdx.x / 5, slice = (int)blockIdx.x - 5 * head;
+  const int head = (int)blockIdx.x / P.nslices, slice = (int)blockIdx.x - P.nslices * head;
   const int b_idx = head / P.heads, h_idx = head - b_idx * P.heads;
-  const int tile0 = slice * 4;
+  const int tile0 = P.tile_first + slice * 4;
   const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
   const int nch = P.nchunks;
+  const Sched sc = P.sc;
   auto chunk_of = [&](int i) -> int { return DK ? (nch - 1 - i) : i; };  // i-th chunk of the scan
   auto units_of = [&](int t) -> int { return (tile0 + t < NTILES - 1) ? 2 : 1; };  // the constant feature has no gradient
 
@@ -202,7 +207,8 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     float acc[5][8];
     uint32_t cnt = 0;     // units this group has taken = phase count of its dphi buffer
     bool ok = true;
-    for (int ci = 1; ci < nch && ok; ++ci) {
+    for (int ci = 0; ci < nch && ok; ++ci) {
+      if (!sc.A(ci)) continue;
       const int c = chunk_of(ci);
       const long long row = (long long)c * CH + l - P.z_shift;
       const bool valid = row >= 0 && row < P.nz;
@@ -277,7 +283,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
       // ---- the chunk's dz: both groups add their blocks into the (zeroed) staging rows, group 0 first; the drain
       //      warp then adds the rows to global memory with one bulk reduce and zeroes them again ----
       float* rowf = stg + l * ACC_LD;
-      const uint32_t j = (uint32_t)(ci - 1);  // drains so far
+      const uint32_t j = (uint32_t)sc.na_before(ci);  // drains so far
       if (grp == 0) {
         if (j > 0 && !WAIT(B_STG_FREE, j - 1)) { FAIL(321); break; }   // reduced, read and zeroed
       } else {
@@ -341,7 +347,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
       const int buf = ci & 1;
       if (!WAIT(B_XT_READY + buf, (uint32_t)(ci >> 1))) { FAIL(300); break; }
       const uint8_t* box = xtile + buf * KT_BUF + set * KT_BOX;
-      for (int t = 0; t < ntl && ok; ++t, ++k) {
+      for (int t = 0; t < ntl && ok && sc.U(ci); ++t, ++k) {
         const bool lin = (tile0 + t == NTILES - 1);
         const uint32_t pr = (uint32_t)(pairs >> (16 * t)) & 0xffffu;
         uint32_t r[32];
@@ -370,29 +376,62 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
     const int l = (w & 3) * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((w & 3) * 32) << 16);
     bool ok = true;
-    for (int ci = 0; ci + 1 < nch && ok; ++ci) {
-      for (int t = 0; t < ntl && ok; ++t) {
-        // S_t is final (update issuer) and Sb_t is no longer read (dphi issuer; the first chunk has no dphi)
-        if (!WAIT(B_S_DONE + t, (uint32_t)ci) || (ci > 0 && !WAIT(B_A_DONE + t, (uint32_t)(ci - 1)))) { FAIL(310); ok = false; break; }
-        __syncwarp();
-        tc_fence_after_sync();
-        uint8_t* dst = sb + t * SB_TILE + l * 16;
+    auto convert_tile = [&](int t) {
+      uint8_t* dst = sb + t * SB_TILE + l * 16;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + 80u * t + 32u * part, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jb = 0; jb < 4; ++jb) store_block8_plain(dst + (4 * part + jb) * BLK, &r[8 * jb]);
+      }
+      uint32_t r8[8];
+      tmem_ld8(lane_addr + 80u * t + 64u, r8);
+      tmem_ld_wait();
+      store_block8_plain(dst + 8 * BLK, r8);
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[B_SB_READY + t]);
+    };
+    if (sc.h) {
+      // the scan starts from the caller's state: rows -> TMEM accumulators (80 columns: 64 values, the denominator
+      // moment, zeros), then the first bf16 copy; the SB_READY arrival orders the stores before the first update MMA
+      constexpr int ST_LD = 68;
+      const float* sbase = P.state_in + (long long)head * P.state_rows * ST_LD;
+      for (int t = 0; t < ntl; ++t) {
+        const int srow = 128 * (tile0 + t - P.tile_first) + l;
+        const bool have = srow < P.state_rows;
+        const float4* src = reinterpret_cast<const float4*>(sbase + (long long)(have ? srow : 0) * ST_LD);
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
           uint32_t r[32];
-          tmem_ld32(lane_addr + 80u * t + 32u * part, r);
-          tmem_ld_wait();
 #pragma unroll
-          for (int jb = 0; jb < 4; ++jb) store_block8_plain(dst + (4 * part + jb) * BLK, &r[8 * jb]);
+          for (int j = 0; j < 8; ++j) {
+            const float4 x = have ? src[8 * part + j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            r[4 * j] = __float_as_uint(x.x); r[4 * j + 1] = __float_as_uint(x.y); r[4 * j + 2] = __float_as_uint(x.z); r[4 * j + 3] = __float_as_uint(x.w);
+          }
+          tmem_st32(lane_addr + 80u * t + 32u * part, r);
         }
-        uint32_t r8[8];
-        tmem_ld8(lane_addr + 80u * t + 64u, r8);
-        tmem_ld_wait();
-        store_block8_plain(dst + 8 * BLK, r8);
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
+        uint32_t rc[16];
+        rc[0] = have ? __float_as_uint(src[16].x) : 0u;
+#pragma unroll
+        for (int j = 1; j < 16; ++j) rc[j] = 0u;
+        tmem_st16(lane_addr + 80u * t + 64u, rc);
+        tmem_st_wait();
+        convert_tile(t);
+      }
+    }
+    for (int ci = 0; ci < nch && ok; ++ci) {
+      if (!sc.C(ci)) continue;
+      const int na_thr = sc.na_before(ci) + (sc.A(ci) ? 1 : 0);
+      for (int t = 0; t < ntl && ok; ++t) {
+        // S_t is final (this chunk's update) and Sb_t is no longer read (the dphi MMAs up to and including this chunk's)
+        if (!WAIT(B_S_DONE + t, (uint32_t)sc.nu_before(ci)) || (na_thr > 0 && !WAIT(B_A_DONE + t, (uint32_t)(na_thr - 1)))) { FAIL(310); ok = false; break; }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[B_SB_READY + t]);
+        tc_fence_after_sync();
+        convert_tile(t);
       }
     }
   } else {
@@ -412,8 +451,9 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
         const uint32_t g_addr = smem_u32(gtile + buf * TILE9);
         const uint64_t dA = make_smem_desc(g_addr, 2048, 128, 0);                       // column blocks 2 ks, 2 ks + 1
         const uint64_t dA_last = make_smem_desc(g_addr + 8 * BLK, smem_u32(sm + OFF_ZERO) - (g_addr + 8 * BLK), 128, 0);  // 8, zero
-        for (int t = 0; t < ntl && ok && ci > 0; ++t) {
-          if (!WAIT(B_SB_READY + t, (uint32_t)(ci - 1))) { FAIL(331); ok = false; break; }
+        const int nc = sc.nc_before(ci);
+        for (int t = 0; t < ntl && ok && sc.A(ci); ++t) {
+          if (nc > 0 && !WAIT(B_SB_READY + t, (uint32_t)(nc - 1))) { FAIL(331); ok = false; break; }
           const int nu = units_of(t);
           for (int u = 0; u < nu && ok; ++u, ++mu) {
             if ((uint32_t)(mu & 1) != db) continue;
@@ -449,9 +489,16 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
         const int buf = ci & 1;
         if (!WAIT(B_Y_READY + buf, (uint32_t)(ci >> 1))) { FAIL(340); break; }
         const uint64_t dB = make_smem_desc(smem_u32(ytile + buf * TILE9), 128, 2048, 0);
+        const int nc = sc.nc_before(ci);
+        const uint32_t acc0 = (sc.nu_before(ci) > 0 || sc.h) ? 1u : 0u;   // the first update starts the accumulators
+        if (!sc.U(ci)) {   // nothing of this chunk reads the Y buffer: hand it back
+          if (elect_one()) mma_commit(&bars[B_Y_FREE + buf]);
+          __syncwarp();
+          continue;
+        }
         for (int t = 0; t < ntl && ok; ++t, ++k) {
-          // S_t may be overwritten once the previous chunk's copy of it exists
-          if (ci > 0 && !WAIT(B_SB_READY + t, (uint32_t)(ci - 1))) { FAIL(341); ok = false; break; }
+          // S_t may be overwritten once the latest copy of it exists
+          if (nc > 0 && !WAIT(B_SB_READY + t, (uint32_t)(nc - 1))) { FAIL(341); ok = false; break; }
           const uint32_t d = tmem_base + 80u * t;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
@@ -461,7 +508,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
             if (elect_one()) {
               const uint32_t a0 = tmem_base + COL_A + 32u * hf;
               const uint64_t b0 = dB + (uint64_t)(64 * hf);
-              mma_ts(d, a0, b0, IDESC, (ci > 0 || hf > 0) ? 1u : 0u);
+              mma_ts(d, a0, b0, IDESC, hf > 0 ? 1u : acc0);
               mma_ts(d, a0 + 8u, b0 + 16u, IDESC, 1u);
               mma_ts(d, a0 + 16u, b0 + 32u, IDESC, 1u);
               mma_ts(d, a0 + 24u, b0 + 48u, IDESC, 1u);
@@ -483,9 +530,10 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
       // finished chunk to the accumulator in global memory: one bulk reduce-add, then the rows are zeroed again.
       float* obase = P.out + (long long)head * P.nz * ACC_LD;
       bool ok = true;
-      uint32_t drained = 0;   // chain chunks ci = 1 .. drained have been drained
+      uint32_t drained = 0;   // chain-rule chunks sc.a_first .. sc.a_first + drained - 1 have been drained
+      const uint32_t na_total = (uint32_t)sc.na_total();
       auto drain_one = [&]() -> bool {
-        const int ci = (int)drained + 1;
+        const int ci = sc.a_first + (int)drained;
         if (!WAIT(B_STG_FULL, drained)) { FAIL(360); return false; }
         __syncwarp();
         if (lane == 0) {
@@ -533,9 +581,9 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
         }
         __syncwarp();
         // the chunk two behind the one just loaded has left the chain-rule groups (or soon will): drain it
-        if (ci >= 3) ok = drain_one();
+        if (drained < na_total && sc.a_first + (int)drained <= ci - 2) ok = drain_one();
       }
-      while (ok && (int)drained < nch - 1) ok = drain_one();
+      while (ok && drained < na_total) ok = drain_one();
       if (lane == 0) bulk_wait_all();  // the last reduce has landed before the CTA retires
     }
   }

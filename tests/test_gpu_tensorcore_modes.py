@@ -1,0 +1,172 @@
+"""The tensor-memory scans beyond the plain causal order-2 case: non-causal (all keys first, then all queries),
+order 1 (causal forward, and every order-1 backward), calls that carry a moment state in or out, and state-only calls.
+Each test asserts which kernels ran (the `tc_*` kinds), then compares with the CPU oracle (bf16 tolerance 2e-2,
+max-normalised per tensor)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import fastmax_oracle as orc
+
+pytestmark = pytest.mark.gpu
+D = 64
+TC_SCANS = {"tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_scan_bwd_dv"}
+FFMA = {"scan_fwd", "scan_bwd_q", "scan_bwd_kv", "moments_kv", "moments_qg"}
+
+
+def host(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def inputs(B, H, nq, nk, seed, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q, do = ((torch.randn(B, H, nq, D, device="cuda", generator=g) * scale).bfloat16() for _ in range(2))
+    k, v = ((torch.randn(B, H, nk, D, device="cuda", generator=g) * scale).bfloat16() for _ in range(2))
+    return q, k, v, do
+
+
+def run(L, q, k, v, do, causal, poly, **kw):
+    L.profile_collect()
+    L.profile(True)
+    o, g, _ = L.forward(q, k, v, causal, poly.inv_temp, poly.a0, poly.a1, poly.a2, order=poly.p, **kw)
+    dq, dk, dv, _ = L.backward(q, k, v, o, g, do, causal, poly.inv_temp, poly.a0, poly.a1, poly.a2, order=poly.p, **kw)
+    L.check_status()
+    L.profile(False)
+    return (o, g, dq, dk, dv), set(L.profile_collect())
+
+
+def check(outs, q, k, v, do, causal, poly, heads):
+    o, g, dq, dk, dv = outs
+    for b, h in heads:
+        a = [host(t[b, h]) for t in (q, k, v, do)]
+        o_ref, g_ref = orc.fastmax_naive(a[0], a[1], a[2], causal, poly)
+        dq_ref, dk_ref, dv_ref = orc.fastmax_naive_grads(a[0], a[1], a[2], a[3], causal, poly)
+        errs = {n: orc.max_norm_err(host(x[b, h]), r) for n, x, r in
+                (("o", o, o_ref), ("g", g, g_ref), ("dq", dq, dq_ref), ("dk", dk, dk_ref), ("dv", dv, dv_ref))}
+        assert max(errs.values()) < 2e-2, (b, h, errs)
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 256, 256), (1, 16, 300, 200), (2, 8, 77, 1000), (1, 13, 640, 129), (1, 16, 50, 60)])
+def test_noncausal_order2_on_tensor_memory(shape):
+    """No mask: the moment build S = Phi(K)^T [V|1] over all keys, then the apply over all queries, as the two phases of
+    one scan (update-only chunks, then apply-only chunks), forward and backward."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, nq, nk = shape
+    q, k, v, do = inputs(B, H, nq, nk, nq * 5 + nk)
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / (2.0 * math.sqrt(D)), 2)
+    outs, kinds = run(L, q, k, v, do, False, poly)
+    assert TC_SCANS <= kinds and not (FFMA & kinds) and "tc_intra_fwd" not in kinds and "tc_intra_bwd" not in kinds, kinds
+    check(outs, q, k, v, do, False, poly, [(0, 0), (B - 1, H - 1)])
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("shape", [(4, 16, 256, 256), (1, 64, 300, 300), (2, 40, 100, 333)])
+def test_order1_on_tensor_memory(shape, causal):
+    """Order 1 (what transformer/model.py:292-300 asks for as shipped): the scans run over the linear/constant feature
+    tile alone, one thread block per head."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, nq, nk = shape
+    q, k, v, do = inputs(B, H, nq, nk, nq + 3 * nk, 0.5)
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / math.sqrt(D), 1)
+    outs, kinds = run(L, q, k, v, do, causal, poly)
+    want = {"tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_scan_bwd_dv"} | ({"tc_scan_fwd"} if causal else {"p1_fwd"})
+    assert want <= kinds and not (FFMA & kinds), kinds
+    check(outs, q, k, v, do, causal, poly, [(0, 0), (B - 1, H - 1), (B // 2, H // 2)])
+
+
+@pytest.mark.parametrize("order", [1, 2])
+def test_carried_states_stay_on_tensor_memory(order):
+    """A causal sequence cut in three: every piece starts from the moment state of the pieces before it (forward) and
+    from the gradient moments of the pieces after it (backward).  All calls, including the state-only ones a
+    sequence-parallel rank publishes, run on the tensor-memory kernels."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, N = 1, 64 if order == 1 else 16, 700
+    q, k, v, do = inputs(B, H, N, N, 31 + order)
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / (2.0 * math.sqrt(D)), order)
+    cuts = [0, 260, 389, N]
+    sl = [slice(cuts[i], cuts[i + 1]) for i in range(3)]
+    cut = lambda t, s: t[:, :, s].contiguous()
+    kw = dict(order=order)
+    L.profile_collect()
+    L.profile(True)
+    totals = [L.forward(cut(k, s), cut(k, s), cut(v, s), True, poly.inv_temp, want_state=True, want_output=False, **kw)[2] for s in sl]
+    prefixes = [sum(totals[:i], torch.zeros_like(totals[0])) for i in range(3)]
+    outs = [L.forward(cut(q, s), cut(k, s), cut(v, s), True, poly.inv_temp, state_in=prefixes[i], **kw)[:2] for i, s in enumerate(sl)]
+    gtot = [L.backward(cut(q, s), cut(k, s), cut(v, s), outs[i][0], outs[i][1], cut(do, s), True, poly.inv_temp,
+                       state_in=prefixes[i], want_dstate=True, want_grads=False, **kw)[3] for i, s in enumerate(sl)]
+    suffixes = [sum(gtot[i + 1:], torch.zeros_like(gtot[0])) for i in range(3)]
+    grads = [L.backward(cut(q, s), cut(k, s), cut(v, s), outs[i][0], outs[i][1], cut(do, s), True, poly.inv_temp,
+                        state_in=prefixes[i], dstate_in=suffixes[i], **kw)[:3] for i, s in enumerate(sl)]
+    L.check_status()
+    L.profile(False)
+    kinds = set(L.profile_collect())
+    assert TC_SCANS <= kinds and not (FFMA & kinds), kinds
+    # chained state: the state after piece 2 given the state after piece 1 equals the sum of the totals
+    _, _, chained = L.forward(cut(q, sl[1]), cut(k, sl[1]), cut(v, sl[1]), True, poly.inv_temp, state_in=prefixes[1], want_state=True, **kw)
+    assert orc.max_norm_err(host(chained), host(prefixes[2])) < 1e-5
+    for h in (0, H - 1):
+        a = [host(t[0, h]) for t in (q, k, v, do)]
+        o_ref, _ = orc.fastmax_naive(a[0], a[1], a[2], True, poly)
+        refs = (o_ref,) + tuple(orc.fastmax_naive_grads(a[0], a[1], a[2], a[3], True, poly))
+        got_o = np.concatenate([host(o_[0][0, h]) for o_ in outs], 0)
+        assert orc.max_norm_err(got_o, refs[0]) < 2e-2
+        for j in range(3):
+            got = np.concatenate([host(gr[j][0, h]) for gr in grads], 0)
+            assert orc.max_norm_err(got, refs[j + 1]) < 2e-2, ("dq", "dk", "dv")[j]
+
+
+def test_state_only_calls_match_the_float32_engine():
+    """The key moments and the gradient moments written by the tensor-memory scans against the CUDA-core engine's
+    (exact float32 features): only the bf16 rounding of the products separates them."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, N = 1, 16, 300
+    q, k, v, do = inputs(B, H, N, N, 5)
+    it = 1.0 / (2.0 * math.sqrt(D))
+    o, g, _ = L.forward(q, k, v, True, it, order=2)
+    for flags in (0,):
+        L.profile_collect()
+        L.profile(True)
+        _, _, s_tc = L.forward(k, k, v, True, it, order=2, want_state=True, want_output=False)
+        _, _, _, ds_tc = L.backward(q, k, v, o, g, do, True, it, order=2, want_dstate=True, want_grads=False)
+        L.check_status()
+        L.profile(False)
+        kinds = set(L.profile_collect())
+        assert "tc_scan_fwd" in kinds and "tc_scan_bwd_dv" in kinds and not (FFMA & kinds), kinds
+    _, _, s_ref = L.forward(k, k, v, True, it, order=2, want_state=True, want_output=False, flags=L.FLAG_NO_TENSOR_CORES)
+    _, _, _, ds_ref = L.backward(q, k, v, o, g, do, True, it, order=2, want_dstate=True, want_grads=False, flags=L.FLAG_NO_TENSOR_CORES)
+    torch.cuda.synchronize()
+    assert orc.max_norm_err(host(s_tc), host(s_ref)) < 5e-3
+    assert orc.max_norm_err(host(ds_tc), host(ds_ref)) < 2e-2   # dO' itself is rounded to bf16 on this path
+
+
+def test_decoder_prefill_continuation_on_tensor_memory():
+    """FastmaxDecoder: a prompt processed in two prefill calls (the second starts from the first one's state), then
+    single-token steps: the same outputs as one causal pass over everything."""
+    from reproducing_fastmax_results_b200 import _lib as L
+    from reproducing_fastmax_results_b200.decoding import FastmaxDecoder
+
+    B, H, N = 2, 16, 300
+    q, k, v, _ = inputs(B, H, N + 3, N + 3, 77)
+    temperature = 2.0 * math.sqrt(D)
+    dec = FastmaxDecoder(B, H, D, p=2, temperature=temperature)
+    L.profile_collect()
+    L.profile(True)
+    o1 = dec.prefill(q[:, :, :170], k[:, :, :170], v[:, :, :170])
+    o2 = dec.prefill(q[:, :, 170:N], k[:, :, 170:N], v[:, :, 170:N])
+    L.check_status()
+    L.profile(False)
+    kinds = set(L.profile_collect())
+    assert "tc_scan_fwd" in kinds and not (FFMA & kinds), kinds
+    steps = [dec.step(q[:, :, N + i], k[:, :, N + i], v[:, :, N + i]) for i in range(3)]
+    torch.cuda.synchronize()
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / temperature, 2)
+    for b, h in [(0, 0), (1, 15)]:
+        o_ref, _ = orc.fastmax_naive(host(q[b, h]), host(k[b, h]), host(v[b, h]), True, poly)
+        got = np.concatenate([host(o1[b, h]), host(o2[b, h])] + [host(s[b, h]).reshape(1, D) for s in steps], 0)
+        assert orc.max_norm_err(got, o_ref) < 2e-2

@@ -104,8 +104,12 @@ def test_gloo_ranks_reproduce_the_unsplit_sequence(tmp_path, cuts):
 def test_cuda_engine_pieces_match_whole_sequence(D, dtype, pieces):
     """The schedule of sequence_parallel.forward/backward with the CUDA engine; the exchange between ranks is
     done by hand (sum of the other pieces' states) because all pieces live on one device here."""
-    B, H, N = 1, 3, 128 * pieces + 40
+    from reproducing_fastmax_results_b200 import _lib
+
+    B, H, N = 1, (16 if dtype == torch.bfloat16 else 3), 128 * pieces + 40
     tol = 1e-4 if dtype == torch.float32 else 2e-2
+    _lib.profile_collect()
+    _lib.profile(True)
     q, k, v, do = (torch.from_numpy(a).to("cuda", dtype) for a in _inputs(B, H, N, D, seed=11))
     temperature = 2.0 * math.sqrt(D)
     eng = sp.CudaEngine(1.0 / temperature)
@@ -121,6 +125,11 @@ def test_cuda_engine_pieces_match_whole_sequence(D, dtype, pieces):
     grads = [eng.backward(cut(q, s), cut(k, s), cut(v, s), outs[i][0], outs[i][1], cut(do, s), prefixes[i], suffixes[i])
              for i, s in enumerate(sl)]
     torch.cuda.synchronize()
+    _lib.profile(False)
+    kinds = set(_lib.profile_collect())
+    if dtype == torch.bfloat16:   # every piece, with or without a carried state, runs on the tensor-memory kernels
+        assert {"tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_scan_bwd_dv"} <= kinds, kinds
+        assert not ({"scan_fwd", "scan_bwd_q", "scan_bwd_kv", "moments_kv", "moments_qg"} & kinds), kinds
     poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / temperature, 2)
     host = lambda t: t.float().cpu().numpy().astype(np.float64)
     qh, kh, vh, doh = (host(t) for t in (q, k, v, do))
