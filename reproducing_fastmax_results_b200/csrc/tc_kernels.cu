@@ -45,11 +45,17 @@ constexpr long long WAIT_CYCLES = 4000000000ll;       // ~2 s at 2 GHz
 // next update (and once before chunk 0 when the state starts from a caller-provided array, h = 1).  Every role of a scan kernel derives its barrier phase counts from
 // these ranges, so causal calls with nk > nq, calls with a carried state and the non-causal layout (all keys first,
 // then all queries) run through the same code.
+// Phase discipline: an mbarrier wait names a phase by its parity only, so a waiter must see every completion of a
+// barrier it uses, in order, and may never fall two completions behind.  That is why the update issuer signals
+// "S_t is final" (S_DONE) only for the chunks somebody waits on (the copies, and the last update when the caller
+// wants the final state, s_final = 1) instead of for every update, and why the host declines layouts in which a
+// carried state meets update-only chunks before the first apply.
 struct Sched {
   int a_first, a_last;
   int u_first, u_last;
   int c_first, c_last;
   int h;
+  int s_final;
   __host__ __device__ static int clampi(int x, int lo, int hi) { return x < lo ? lo : (x > hi ? hi : x); }
   __host__ __device__ bool A(int ci) const { return ci >= a_first && ci <= a_last; }
   __host__ __device__ bool U(int ci) const { return ci >= u_first && ci <= u_last; }
@@ -58,6 +64,8 @@ struct Sched {
   __host__ __device__ int nu_total() const { return u_last >= u_first ? u_last - u_first + 1 : 0; }
   __host__ __device__ int na_before(int ci) const { return clampi(ci - a_first, 0, na_total()); }   // applies in chunks < ci
   __host__ __device__ int nu_before(int ci) const { return clampi(ci - u_first, 0, nu_total()); }   // updates in chunks < ci
+  __host__ __device__ int ncv_total() const { return c_last >= c_first ? c_last - c_first + 1 : 0; }
+  __host__ __device__ bool SD(int ci) const { return C(ci) || (s_final && ci == u_last); }        // update ci signals S_DONE
   __host__ __device__ int nc_before(int ci) const {                                                 // copies made before chunk ci
     return h + clampi(ci - c_first, 0, c_last >= c_first ? c_last - c_first + 1 : 0);
   }
@@ -451,6 +459,7 @@ static tc::Sched make_sched(const ScanGeom& g, bool reverse, bool has_init, bool
   sc.c_first = u0 > a0 - 1 ? u0 : a0 - 1;
   sc.c_last = u1 < a1 - 1 ? u1 : a1 - 1;
   sc.h = has_init ? 1 : 0;
+  sc.s_final = (want_state && sc.nu_total() > 0 && !sc.C(u1)) ? 1 : 0;
   return sc;
 }
 
@@ -468,6 +477,7 @@ static bool tc_forward_supported(const fastmax_problem* pb, const fastmax_forwar
   const bool want_o = a->o.ptr && pb->nq > 0;
   if (!want_o && !a->state_out) return false;
   if (!pb->causal && a->state_in) return false;
+  if (a->state_in && pb->nk != pb->nq) return false;   // see the phase discipline note at Sched
   return true;
 }
 
@@ -597,6 +607,7 @@ static bool tc_backward_supported(const fastmax_problem* pb, const fastmax_backw
   if (want_grads && !(a->dq.ptr && a->dk.ptr && a->dv.ptr)) return false;
   if (!want_grads && !a->dstate_out) return false;
   if (!pb->causal && (a->state_in || a->dstate_in)) return false;
+  if (a->state_in && pb->nk != pb->nq) return false;   // see the phase discipline note at Sched
   // the dO' prologue reads o and dO two bf16 at a time
   for (const fastmax_tensor* t : {&a->o, &a->d_out})
     if (((uintptr_t)t->ptr & 3) || (t->stride_b & 1) || (t->stride_h & 1) || (t->stride_n & 1)) return false;

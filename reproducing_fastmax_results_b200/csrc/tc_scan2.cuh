@@ -442,7 +442,7 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
         if (has_c) {  // the bf16 copy of S_t feeds the next apply
           // S_t is final (this chunk's update) and Sb_t is no longer read (the applies up to and including this chunk's)
           const int na_thr = sc.na_before(ci) + (has_a ? 1 : 0);
-          if (!WAIT(B_S_DONE + t, (uint32_t)sc.nu_before(ci)) || (na_thr > 0 && !WAIT(B_A_DONE + t, (uint32_t)(na_thr - 1)))) { FAIL(221); ok = false; break; }
+          if (!WAIT(B_S_DONE + t, (uint32_t)(sc.nc_before(ci) - sc.h)) || (na_thr > 0 && !WAIT(B_A_DONE + t, (uint32_t)(na_thr - 1)))) { FAIL(221); ok = false; break; }
           __syncwarp();
           tc_fence_after_sync();
           convert_tile(t);
@@ -456,8 +456,10 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
       // summed in float32.
       float* sbase = P.state_out + (long long)head * P.state_rows * ST_LD;
       const int nu = sc.nu_total();
+      // S_DONE completions: one per copy, then one for the last update unless that update was followed by a copy
+      const int last_sd = sc.ncv_total() + sc.s_final - 1;
       for (int t = 0; t < ntl; ++t) {
-        if (nu > 0 && !WAIT(B_S_DONE + t, (uint32_t)(nu - 1))) { FAIL(224); break; }
+        if (nu > 0 && last_sd >= 0 && !WAIT(B_S_DONE + t, (uint32_t)last_sd)) { FAIL(224); break; }
         __syncwarp();
         tc_fence_after_sync();
         uint32_t ra[32], rb[32], rc[8];
@@ -551,7 +553,8 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
             const uint32_t d = tmem_base + 80u * t;
             const uint32_t acc0 = (sc.nu_before(ci) > 0 || sc.h) ? 1u : 0u;   // the first update starts the accumulator
             ok = issue(wrap(s0 + u0pos), d, dB_Vc, acc0, nullptr, nullptr) &&
-                 issue(wrap(s0 + u1pos), d, dB_Vc + 64u, 1u, &bars[B_S_DONE + t], last ? &bars[B_VP_FREE + (ci & 1)] : nullptr);
+                 issue(wrap(s0 + u1pos), d, dB_Vc + 64u, 1u, sc.SD(ci) ? &bars[B_S_DONE + t] : nullptr,
+                       last ? &bars[B_VP_FREE + (ci & 1)] : nullptr);
             if (!ok) FAIL(234);
           }
         }

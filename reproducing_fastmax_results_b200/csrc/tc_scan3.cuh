@@ -428,7 +428,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
       const int na_thr = sc.na_before(ci) + (sc.A(ci) ? 1 : 0);
       for (int t = 0; t < ntl && ok; ++t) {
         // S_t is final (this chunk's update) and Sb_t is no longer read (the dphi MMAs up to and including this chunk's)
-        if (!WAIT(B_S_DONE + t, (uint32_t)sc.nu_before(ci)) || (na_thr > 0 && !WAIT(B_A_DONE + t, (uint32_t)(na_thr - 1)))) { FAIL(310); ok = false; break; }
+        if (!WAIT(B_S_DONE + t, (uint32_t)(sc.nc_before(ci) - sc.h)) || (na_thr > 0 && !WAIT(B_A_DONE + t, (uint32_t)(na_thr - 1)))) { FAIL(310); ok = false; break; }
         __syncwarp();
         tc_fence_after_sync();
         convert_tile(t);
@@ -514,7 +514,7 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
               mma_ts(d, a0 + 24u, b0 + 48u, IDESC, 1u);
               mma_commit(&bars[B_EMPTY + hf]);
               if (hf == 1) {
-                mma_commit(&bars[B_S_DONE + t]);
+                if (sc.SD(ci)) mma_commit(&bars[B_S_DONE + t]);
                 if (t == ntl - 1) mma_commit(&bars[B_Y_FREE + buf]);
               }
             }
