@@ -160,6 +160,23 @@ typedef struct {
 
 int32_t fastmax_decode_step(const fastmax_problem* pb, const fastmax_decode_args* args, void* cuda_stream);
 
+/* ---- optional key prologue and output epilogue -------------------------------------------------------
+ * Two steps the reference's forward_cuda carries but never performs; offered so a caller can switch them on.
+ *
+ * fastmax_key_prologue replaces apply_rpe_and_temp (fastmax_cuda_forward.cu:282-292), including the line the
+ * reference has commented out (:289):   k[l] <- k[l] * inv_temperature + rpe[(l + nk) mod (2 nk - 1)]   in place.
+ * rpe: float32 (2 nk - 1, d) contiguous, 16-byte aligned, or NULL (scale only, which is all the reference does).
+ * A caller that uses it passes inv_temperature = 1 to fastmax_forward afterwards.
+ *
+ * fastmax_output_noise replaces apply_dropout (fastmax_cuda_forward.cu:340-349):  out <- x * (1 + scale * noise),
+ * element-wise on (batch, head, token, dim) views of the operator's dtype; out may alias x.  The reference
+ * launches it with the literal scale 0.0 (:443), i.e. as a no-op. */
+int32_t fastmax_key_prologue(int32_t batch, int32_t heads, int32_t nk, int32_t d, int32_t dtype, float inv_temperature,
+                             const fastmax_tensor* k, const float* rpe, void* cuda_stream);
+int32_t fastmax_output_noise(int32_t batch, int32_t heads, int32_t n, int32_t d, int32_t dtype, float scale,
+                             const fastmax_tensor* x, const fastmax_tensor* noise, const fastmax_tensor* out,
+                             void* cuda_stream);
+
 /* ---- q/k normalisation ----------------------------------------------------------------------------
  * Replaces calc_norms / find_max / apply_norm (fastmax_cuda_forward.cu:294-338, 424-433) with the
  * normalisation the reference's oracle defines (attention_mechanisms/fastattention_einops.py:327-334):

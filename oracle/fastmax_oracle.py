@@ -389,6 +389,25 @@ def normalize_grad(x, dy, lim: float = 1.0):
 
 
 # --------------------------------------------------------------------------------------------
+# 5b. the two steps of forward_cuda that the reference carries but never performs
+#     (fastmax_cuda_forward.cu:282-292 with the commented-out line 289; :340-349 called with scale 0 at :443)
+# --------------------------------------------------------------------------------------------
+def key_prologue(k, inv_temp: float, rpe=None):
+    """k[l] * inv_temp + rpe[(l + nk) mod (2 nk - 1)]   (apply_rpe_and_temp with its RPE line switched on)."""
+    k = np.asarray(k, np.float64) * inv_temp
+    if rpe is not None:
+        nk = k.shape[-2]
+        idx = (np.arange(nk) + nk) % (2 * nk - 1)
+        k = k + np.asarray(rpe, np.float64)[idx]
+    return k
+
+
+def output_noise(o, noise, scale: float):
+    """o * (1 + scale * noise)   (apply_dropout, fastmax_cuda_forward.cu:340-349)."""
+    return np.asarray(o, np.float64) * (1.0 + scale * np.asarray(noise, np.float64))
+
+
+# --------------------------------------------------------------------------------------------
 # 6. error metric used by every parity test (outputs cross zero, so errors are normalised by the
 #    tensor's largest magnitude, never element by element).
 # --------------------------------------------------------------------------------------------

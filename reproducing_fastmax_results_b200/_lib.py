@@ -23,6 +23,7 @@ EXPORTED_SYMBOLS = [
     "fastmax_backward_workspace", "fastmax_backward",
     "fastmax_decode_step",
     "fastmax_normalize_forward", "fastmax_normalize_backward",
+    "fastmax_key_prologue", "fastmax_output_noise",
     "fastmax_status_string", "fastmax_last_cuda_error", "fastmax_last_cuda_error_string",
     "fastmax_version", "fastmax_launch_count", "fastmax_check_status", "fastmax_debug_wait_histogram",
     "fastmax_debug_wait_selftest",
@@ -104,6 +105,12 @@ def load():
     lib.fastmax_normalize_backward.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                                C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p,
                                                C.c_void_p, C.c_void_p]
+    lib.fastmax_key_prologue.restype = C.c_int32
+    lib.fastmax_key_prologue.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.POINTER(Tensor),
+                                         C.c_void_p, C.c_void_p]
+    lib.fastmax_output_noise.restype = C.c_int32
+    lib.fastmax_output_noise.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.POINTER(Tensor),
+                                         C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]
     lib.fastmax_status_string.restype = C.c_char_p
     lib.fastmax_status_string.argtypes = [C.c_int32]
     lib.fastmax_last_cuda_error.restype = C.c_int32
@@ -308,6 +315,28 @@ def normalize_backward(y, dy, stats, lim=1.0):
                                          C.byref(yv), C.byref(gv), C.byref(dv), stats.data_ptr(), scratch.data_ptr(),
                                          _stream()), "fastmax_normalize_backward")
     return dx
+
+
+def key_prologue(k, inv_temp, rpe=None):
+    """Calls fastmax_key_prologue: k (b,h,n,d) is scaled by inv_temp in place and, with rpe (float32 (2n-1, d)), gets
+    rpe[(l + n) mod (2n - 1)] added to key l."""
+    lib = load()
+    kv = view_bhnd(k)
+    check(lib.fastmax_key_prologue(k.shape[0], k.shape[1], k.shape[2], k.shape[3], dtype_code(k), inv_temp, C.byref(kv),
+                                   None if rpe is None else rpe.data_ptr(), _stream()), "fastmax_key_prologue")
+    return k
+
+
+def output_noise(x, noise, scale, out=None):
+    """Calls fastmax_output_noise: returns x * (1 + scale * noise) (written into `out`, which may be x)."""
+    import torch
+
+    lib = load()
+    out = torch.empty_like(x) if out is None else out
+    xv, nv, ov = view_bhnd(x), view_bhnd(noise), view_bhnd(out)
+    check(lib.fastmax_output_noise(x.shape[0], x.shape[1], x.shape[2], x.shape[3], dtype_code(x), scale, C.byref(xv),
+                                   C.byref(nv), C.byref(ov), _stream()), "fastmax_output_noise")
+    return out
 
 
 def check_status():

@@ -77,49 +77,72 @@ class FastMax(torch.autograd.Function):
 
     q, k, v may be float32 or bfloat16 and need not be contiguous (only the head dim must have stride 1), so
     the transposed views produced by a head split are consumed without a copy.  `drop_noise`, `rpe_matrix`
-    and `dropout` are accepted and ignored, which is what the reference's kernels do with them
-    (fastmax_cuda_forward.cu:289, 443).  With `normalize` the op computes
+    and `dropout` are accepted and, by default, ignored, which is what the reference's kernels do with them
+    (fastmax_cuda_forward.cu:289, 443).  Two trailing switches turn the dead code paths of the reference on:
+    `apply_rpe` adds rpe_matrix[(l + n) mod (2n - 1)] to key l after the temperature scaling (the line commented out
+    at fastmax_cuda_forward.cu:289) and `noise_dropout` multiplies the output by 1 + dropout * drop_noise (the
+    reference's apply_dropout, :340-349, which it launches with scale 0).  With `normalize` the op computes
     lim * (x - mean_d x) / max_token ||x - mean_d x|| for q and k (fastattention_einops.py:327-334) and its
     exact gradient.  Scores are (q . k) / temperature.
     """
 
     @staticmethod
     def forward(ctx, q, k, v, drop_noise=None, rpe_matrix=None, mask=False, dropout=0.0, normalize=False,
-                temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2):
+                temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2, apply_rpe=False, noise_dropout=False):
         ext = _ext()
         three_d = q.dim() == 3
         if three_d:
             q, k, v = q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
+            drop_noise = drop_noise.unsqueeze(0) if (noise_dropout and drop_noise is not None) else drop_noise
         elif q.dim() != 4:
             raise ValueError("q, k, v must be (b, h, n, d) or (b*h, n, d)")
         stats_q = stats_k = None
         if normalize:
             q, stats_q = ext.normalize_forward(q, float(lim))
             k, stats_k = ext.normalize_forward(k, float(lim))
-        o, g, _ = ext.forward(q, k, v, bool(mask), 1.0 / float(temperature), float(a0), float(a1), float(a2), int(p),
-                              None, False, True, 0)
-        ctx.save_for_backward(q, k, v, o, g, *([stats_q, stats_k] if normalize else []))
-        ctx.cfg = (bool(mask), 1.0 / float(temperature), float(a0), float(a1), float(a2), int(p), bool(normalize),
-                   float(lim), three_d)
-        return o.squeeze(0) if three_d else o
+        inv_t = 1.0 / float(temperature)
+        k_scale = 1.0     # dk of the operator is w.r.t. the k it saw: times k_scale gives the gradient of the input k
+        k_op = k
+        if apply_rpe:
+            if rpe_matrix is None:
+                raise ValueError("apply_rpe needs rpe_matrix, a (2n-1, d) tensor")
+            k_op = ext.key_prologue(k.clone(), inv_t, rpe_matrix)   # k / temperature + rpe rows, on a private copy
+            k_scale, inv_t = inv_t, 1.0
+        o, g, _ = ext.forward(q, k_op, v, bool(mask), inv_t, float(a0), float(a1), float(a2), int(p), None, False, True, 0)
+        noise = None
+        out = o
+        if noise_dropout and float(dropout) != 0.0:
+            if drop_noise is None:
+                raise ValueError("noise_dropout needs drop_noise, a tensor shaped like q")
+            noise = drop_noise.to(o.dtype)
+            out = ext.output_noise(o, noise, float(dropout))
+        extra = ([stats_q, stats_k] if normalize else []) + ([k] if (normalize and apply_rpe) else [])
+        ctx.save_for_backward(q, k_op, v, o, g, *extra, *([noise] if noise is not None else []))
+        ctx.cfg = (bool(mask), inv_t, float(a0), float(a1), float(a2), int(p), bool(normalize), float(lim), three_d,
+                   k_scale, float(dropout) if noise is not None else 0.0, bool(apply_rpe))
+        return out.squeeze(0) if three_d else out
 
     @staticmethod
     def backward(ctx, grad_output):
         ext = _ext()
-        mask, inv_t, a0, a1, a2, p, normalize, lim, three_d = ctx.cfg
+        mask, inv_t, a0, a1, a2, p, normalize, lim, three_d, k_scale, noise_scale, apply_rpe = ctx.cfg
         q, k, v, o, g = ctx.saved_tensors[:5]
         if three_d:
             grad_output = grad_output.unsqueeze(0)
         if grad_output.stride(-1) != 1:
             grad_output = grad_output.contiguous()
+        if noise_scale != 0.0:     # out = o * (1 + s * noise)  ->  d o = d out * (1 + s * noise)
+            grad_output = ext.output_noise(grad_output, ctx.saved_tensors[-1], noise_scale)
         dq, dk, dv, _ = ext.backward(q, k, v, o, g, grad_output, mask, inv_t, a0, a1, a2, p, None, None, False, True, 0)
+        if k_scale != 1.0:         # the operator saw k / temperature + rpe rows
+            dk = ext.key_prologue(dk, k_scale, None)
         if normalize:
             stats_q, stats_k = ctx.saved_tensors[5:7]
             dq = ext.normalize_backward(q, dq, stats_q, lim)
-            dk = ext.normalize_backward(k, dk, stats_k, lim)
+            dk = ext.normalize_backward(ctx.saved_tensors[7] if apply_rpe else k, dk, stats_k, lim)
         if three_d:
             dq, dk, dv = dq.squeeze(0), dk.squeeze(0), dv.squeeze(0)
-        return dq, dk, dv, None, None, None, None, None, None, None, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None, None, None, None, None, None, None, None, None
 
 
 def fastmax(q, k, v, mask=False, normalize=False, temperature=None, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2,
@@ -135,17 +158,22 @@ def fastmax(q, k, v, mask=False, normalize=False, temperature=None, a0=1.0, a1=1
 class FASTMultiHeadAttention(torch.nn.Module):
     """nn.Module shim of transformer/model.py:208-216."""
 
-    def __init__(self, use_custom_gradient=True, zero_copy=True):
+    def __init__(self, use_custom_gradient=True, zero_copy=True, apply_rpe=False, noise_dropout=False):
         super().__init__()
         self.use_custom_gradient = use_custom_gradient
         self.zero_copy = zero_copy
+        self.apply_rpe = apply_rpe            # FastMax only: see its docstring
+        self.noise_dropout = noise_dropout
 
     def forward(self, q, k, v, drop_noise=None, rpe_matrix=None, mask=False, dropout=0.0, normalize=False,
                 temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2):
         if not self.use_custom_gradient:
             return 0  # what the reference returns (model.py:216)
-        fn = FastMax if self.zero_copy else FASTMultiHeadAttention_Function
-        return fn.apply(q, k, v, drop_noise, rpe_matrix, mask, dropout, normalize, temperature, a0, a1, a2, lim, p)
+        if self.zero_copy:
+            return FastMax.apply(q, k, v, drop_noise, rpe_matrix, mask, dropout, normalize, temperature, a0, a1, a2, lim, p,
+                                 self.apply_rpe, self.noise_dropout)
+        return FASTMultiHeadAttention_Function.apply(q, k, v, drop_noise, rpe_matrix, mask, dropout, normalize, temperature,
+                                                     a0, a1, a2, lim, p)
 
 
 def rpe_matrix_creator(n, d, device, dtype, structured=False, is_zero=True):

@@ -471,4 +471,39 @@ __global__ void norm_bwd_apply_kernel(View y, View dy, View dx, int d, int n, in
   }
 }
 
+// ---- optional key prologue and output epilogue (dead code paths of the reference, offered as options) ----
+// k <- k * inv_temp + rpe[(l + nk) mod (2 nk - 1)]   (rpe may be null: scale only).  Thread = four consecutive dims
+// of one key row; grid.y = batch*head.  Needs 8-byte (bf16) / 16-byte (float) aligned rows.
+template <typename T>
+__global__ void key_prologue_kernel(View k, const float* __restrict__ rpe, float inv_temp, int d, int nk, int heads) {
+  const int vpr = d / 4;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)nk * vpr) return;
+  const int l = (int)(idx / vpr), c = (int)(idx - (long long)l * vpr) * 4;
+  const int head = blockIdx.y, b = head / heads, h = head - b * heads;
+  T* p = reinterpret_cast<T*>(const_cast<void*>(k.ptr)) + (long long)b * k.sb + (long long)h * k.sh + (long long)l * k.sn + c;
+  float4 x = load4<T>(p);
+  x.x *= inv_temp; x.y *= inv_temp; x.z *= inv_temp; x.w *= inv_temp;
+  if (rpe != nullptr) {
+    const float4 r = *reinterpret_cast<const float4*>(rpe + (long long)((l + nk) % (2 * nk - 1)) * d + c);
+    x.x += r.x; x.y += r.y; x.z += r.z; x.w += r.w;
+  }
+  store4<T>(p, x.x, x.y, x.z, x.w);
+}
+
+// out <- x * (1 + scale * noise)   (out may alias x).  Same thread mapping.
+template <typename T>
+__global__ void output_noise_kernel(View x, View noise, View out, float scale, int d, int n, int heads) {
+  const int vpr = d / 4;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * vpr) return;
+  const int l = (int)(idx / vpr), c = (int)(idx - (long long)l * vpr) * 4;
+  const int head = blockIdx.y, b = head / heads, h = head - b * heads;
+  auto at = [&](const View& t) {
+    return reinterpret_cast<T*>(const_cast<void*>(t.ptr)) + (long long)b * t.sb + (long long)h * t.sh + (long long)l * t.sn + c;
+  };
+  const float4 a = load4<T>(at(x)), z = load4<T>(at(noise));
+  store4<T>(at(out), a.x * (1.f + scale * z.x), a.y * (1.f + scale * z.y), a.z * (1.f + scale * z.z), a.w * (1.f + scale * z.w));
+}
+
 }  // namespace fm

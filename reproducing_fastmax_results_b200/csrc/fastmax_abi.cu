@@ -52,7 +52,7 @@ void launch_end(int kind, cudaStream_t st) {
 }
 static const char* kKindNames[KK_COUNT] = {
     "moments_kv", "moments_qg", "state_scan", "scan_fwd", "scan_bwd_q", "scan_bwd_kv", "finalize_fwd",
-    "bwd_prologue", "cast_out", "normalize", "tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_moments", "p1_fwd", "tc_intra_fwd", "tc_intra_bwd", "tc_transpose", "tc_scan_bwd_dv", "decode_step"};
+    "bwd_prologue", "cast_out", "normalize", "tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_moments", "p1_fwd", "tc_intra_fwd", "tc_intra_bwd", "tc_transpose", "tc_scan_bwd_dv", "decode_step", "key_prologue", "output_noise"};
 
 static int sm_count() {
   static int cached[64] = {0};
@@ -667,6 +667,54 @@ int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args*
   if ((rc = launch_cast_out(pb, dqa, pb->nq, &a->dq, st))) return rc;
   if ((rc = launch_cast_out(pb, dka, pb->nk, &a->dk, st))) return rc;
   if ((rc = launch_cast_out(pb, dva, pb->nk, &a->dv, st))) return rc;
+  return FASTMAX_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// optional key prologue / output epilogue
+// ---------------------------------------------------------------------------------------------------
+int32_t fastmax_key_prologue(int32_t batch, int32_t heads, int32_t nk, int32_t d, int32_t dtype, float inv_temperature,
+                             const fastmax_tensor* k, const float* rpe, void* stream) {
+  if (!k || batch < 0 || heads < 0 || nk < 0) return FASTMAX_ERR_INVALID_ARGUMENT;
+  if (d != 16 && d != 32 && d != 64) return FASTMAX_ERR_UNSUPPORTED;
+  if (dtype != FASTMAX_F32 && dtype != FASTMAX_BF16) return FASTMAX_ERR_INVALID_ARGUMENT;
+  if ((long long)batch * heads * nk == 0) return FASTMAX_OK;
+  int rc = check_view(*k, dtype, true);
+  if (rc) return rc;
+  if (rpe && ((uintptr_t)rpe & 15)) return FASTMAX_ERR_MISALIGNED;
+  if ((long long)batch * heads > 65535) return FASTMAX_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = 256;
+  dim3 grid((unsigned)(((long long)nk * (d / 4) + threads - 1) / threads), (unsigned)(batch * heads));
+  {
+    LaunchScope ls(KK_KEY_PROLOGUE, st);
+    if (dtype == FASTMAX_F32) key_prologue_kernel<float><<<grid, threads, 0, st>>>(to_view(*k), rpe, inv_temperature, d, nk, heads);
+    else key_prologue_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(to_view(*k), rpe, inv_temperature, d, nk, heads);
+  }
+  FM_CUDA(cudaGetLastError());
+  return FASTMAX_OK;
+}
+
+int32_t fastmax_output_noise(int32_t batch, int32_t heads, int32_t n, int32_t d, int32_t dtype, float scale,
+                             const fastmax_tensor* x, const fastmax_tensor* noise, const fastmax_tensor* out, void* stream) {
+  if (!x || !noise || !out || batch < 0 || heads < 0 || n < 0) return FASTMAX_ERR_INVALID_ARGUMENT;
+  if (d != 16 && d != 32 && d != 64) return FASTMAX_ERR_UNSUPPORTED;
+  if (dtype != FASTMAX_F32 && dtype != FASTMAX_BF16) return FASTMAX_ERR_INVALID_ARGUMENT;
+  if ((long long)batch * heads * n == 0) return FASTMAX_OK;
+  for (const fastmax_tensor* t : {x, noise, out}) {
+    int rc = check_view(*t, dtype, true);
+    if (rc) return rc;
+  }
+  if ((long long)batch * heads > 65535) return FASTMAX_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = 256;
+  dim3 grid((unsigned)(((long long)n * (d / 4) + threads - 1) / threads), (unsigned)(batch * heads));
+  {
+    LaunchScope ls(KK_OUTPUT_NOISE, st);
+    if (dtype == FASTMAX_F32) output_noise_kernel<float><<<grid, threads, 0, st>>>(to_view(*x), to_view(*noise), to_view(*out), scale, d, n, heads);
+    else output_noise_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(to_view(*x), to_view(*noise), to_view(*out), scale, d, n, heads);
+  }
+  FM_CUDA(cudaGetLastError());
   return FASTMAX_OK;
 }
 

@@ -86,7 +86,10 @@ torch::Tensor forwardpass(torch::Tensor q, torch::Tensor k, torch::Tensor v, tor
     check_status(fastmax_normalize_forward(1, bh, nk, d, FASTMAX_F32, lim, &kv, &kv, (uint64_t*)stats.data_ptr(), stream),
                  "fastmax normalize(k)");
   }
-  if (temperature != 1.0f) k.div_(temperature);
+  if (temperature != 1.0f) {   // k <- k / temperature in place, as apply_rpe_and_temp does (fwd.cu:282-292)
+    fastmax_tensor kv = view_nbd(k);
+    check_status(fastmax_key_prologue(1, bh, nk, d, FASTMAX_F32, 1.0f / temperature, &kv, nullptr, stream), "fastmax key_prologue");
+  }
   auto o = torch::empty({nq, bh, d + 1}, q.options());
   fastmax_problem pb{};
   pb.batch = 1; pb.heads = bh; pb.nq = nq; pb.nk = nk; pb.d = d; pb.order = p; pb.causal = mask ? 1 : 0;
@@ -255,6 +258,37 @@ torch::Tensor normalize_backward(torch::Tensor y, torch::Tensor dy, torch::Tenso
   return dx;
 }
 
+// k <- k * inv_temp (+ rpe rows) in place; returns k
+torch::Tensor key_prologue(torch::Tensor k, double inv_temp, c10::optional<torch::Tensor> rpe) {
+  CHECK_CUDA(k);
+  const c10::cuda::CUDAGuard guard(k.device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  const float* rp = nullptr;
+  torch::Tensor r;
+  if (rpe.has_value() && rpe->defined()) {
+    r = rpe->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(r.dim() == 2 && r.size(0) == 2 * k.size(2) - 1 && r.size(1) == k.size(3), "rpe_matrix must be (2n-1, d)");
+    rp = (const float*)r.data_ptr();
+  }
+  fastmax_tensor kv = view_bhnd(k);
+  check_status(fastmax_key_prologue(k.size(0), k.size(1), k.size(2), k.size(3), dtype_of(k), (float)inv_temp, &kv, rp, stream),
+               "fastmax key_prologue");
+  return k;
+}
+
+// x * (1 + scale * noise)
+torch::Tensor output_noise(torch::Tensor x, torch::Tensor noise, double scale) {
+  CHECK_CUDA(x); CHECK_CUDA(noise);
+  TORCH_CHECK(noise.sizes() == x.sizes() && noise.scalar_type() == x.scalar_type(), "drop_noise must look like the output");
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  auto out = torch::empty_like(x);
+  fastmax_tensor xv = view_bhnd(x), nv = view_bhnd(noise), ov = view_bhnd(out);
+  check_status(fastmax_output_noise(x.size(0), x.size(1), x.size(2), x.size(3), dtype_of(x), (float)scale, &xv, &nv, &ov, stream),
+               "fastmax output_noise");
+  return out;
+}
+
 int64_t launch_count() { return (int64_t)fastmax_launch_count(); }
 
 }  // namespace
@@ -276,6 +310,9 @@ PYBIND11_MODULE(fastmax_cuda, m) {
         py::arg("grads_out") = py::none(), release());
   m.def("normalize_forward", &normalize_forward, "q/k normalisation: returns [y, stats]", release());
   m.def("normalize_backward", &normalize_backward, "gradient of the q/k normalisation", release());
+  m.def("key_prologue", &key_prologue, "k <- k * inv_temp + rpe rows, in place", py::arg("k"), py::arg("inv_temp"),
+        py::arg("rpe") = py::none(), release());
+  m.def("output_noise", &output_noise, "x * (1 + scale * noise)", release());
   m.def("launch_count", &launch_count, "kernel launches issued by the library so far");
   m.def("version", []() { return std::string(fastmax_version()); });
 }

@@ -535,30 +535,37 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
         const int na = sc.na_before(ci);
         if (na > 0 && !WAIT(B_O_FREE, (uint32_t)(na - 1))) { FAIL(231); break; }
       }
-      // positions of a tile's slabs in the chunk's slab sequence (see the slab tables)
-      const bool both = has_a && has_u;
-      for (int t = 0; t < ntl && ok && (has_a || has_u); ++t) {
-        const bool last = (t == ntl - 1);
-        const uint32_t a1pos = both ? (last ? 1u : 2u) : 1u, u0pos = both ? (last ? 2u : 1u) : 0u, u1pos = both ? 3u : 1u;
-        if (mine_q ? has_a : has_u) {
+      // Positions of this issuer's two slabs of a tile in the chunk's slab sequence (see the slab tables), for a tile
+      // that is not the last one (p0, p1) and for the last one (q0, q1); everything the tile loop needs is fixed here
+      // so that the loop itself stays as short as the MMA issue rate wants it.
+      const bool both = has_a && has_u, mine = mine_q ? has_a : has_u;
+      const uint32_t p0 = (both && !mine_q) ? 1u : 0u, p1 = both ? (mine_q ? 2u : 3u) : 1u;
+      const uint32_t q0 = (both && !mine_q) ? 2u : 0u, q1 = both ? (mine_q ? 1u : 3u) : 1u;
+      const uint32_t adv = both ? 1u : 2u;   // four (or two) slabs per tile, modulo the three ring slots
+      const uint32_t acc0 = mine_q ? 0u : ((sc.nu_before(ci) > 0 || sc.h) ? 1u : 0u);   // the first update starts the accumulator
+      const bool sd = sc.SD(ci);
+      if (!mine) {
+        for (int t = 0; t < ntl && (has_a || has_u); ++t) s0 = wrap(s0 + adv);
+      } else {
+        for (int t = 0; t < ntl && ok; ++t) {
+          const bool last = (t == ntl - 1);
           // Sb_t holds the copy this chunk's apply reads; the update may overwrite S_t once that copy exists
           if (nc > 0 && !WAIT(B_SB_READY + t, (uint32_t)(nc - 1))) { FAIL(230); ok = false; break; }
           if (mine_q) {
             const uint32_t d = tmem_base + COL_O;
             const uint64_t b = dB_S + (uint64_t)((t * SB_TILE) >> 4);
             ok = issue(s0, d, b, t > 0 ? 1u : 0u, nullptr, nullptr) &&
-                 issue(wrap(s0 + a1pos), d, b + 64u, 1u, &bars[B_A_DONE + t], last ? &bars[B_O_DONE] : nullptr);
+                 issue(wrap(s0 + (last ? q1 : p1)), d, b + 64u, 1u, &bars[B_A_DONE + t], last ? &bars[B_O_DONE] : nullptr);
             if (!ok) FAIL(232);
           } else {
             const uint32_t d = tmem_base + 80u * t;
-            const uint32_t acc0 = (sc.nu_before(ci) > 0 || sc.h) ? 1u : 0u;   // the first update starts the accumulator
-            ok = issue(wrap(s0 + u0pos), d, dB_Vc, acc0, nullptr, nullptr) &&
-                 issue(wrap(s0 + u1pos), d, dB_Vc + 64u, 1u, sc.SD(ci) ? &bars[B_S_DONE + t] : nullptr,
+            ok = issue(wrap(s0 + (last ? q0 : p0)), d, dB_Vc, acc0, nullptr, nullptr) &&
+                 issue(wrap(s0 + (last ? q1 : p1)), d, dB_Vc + 64u, 1u, sd ? &bars[B_S_DONE + t] : nullptr,
                        last ? &bars[B_VP_FREE + (ci & 1)] : nullptr);
             if (!ok) FAIL(234);
           }
+          s0 = wrap(s0 + adv);
         }
-        s0 = wrap(s0 + (both ? 1u : 2u));  // four (or two) slabs per tile, modulo the three ring slots
       }
       if (ok && !mine_q && !has_u) {       // nothing of this chunk reads the Y buffer
         if (elect_one()) mma_commit(&bars[B_VP_FREE + (ci & 1)]);

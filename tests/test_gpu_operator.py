@@ -210,3 +210,52 @@ def test_extension_calls_release_the_gil():
     stop.set()
     th.join()
     assert len(ticks) > 20
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_key_prologue_and_output_noise_kernels(dtype):
+    """fastmax_key_prologue / fastmax_output_noise through the C ABI against the oracle's restatement of
+    apply_rpe_and_temp (with its commented-out RPE line) and apply_dropout, on strided views."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, N, D = 2, 3, 37, 32
+    rng = np.random.default_rng(21)
+    k, x, noise = (rng.standard_normal((B, N, H, D)).astype(np.float32) for _ in range(3))
+    rpe = rng.standard_normal((2 * N - 1, D)).astype(np.float32)
+    kd, xd, nd = (torch.from_numpy(a).cuda().to(dtype).transpose(1, 2) for a in (k, x, noise))
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    k_ref = orc.key_prologue(host(kd), 0.3, rpe)
+    L.key_prologue(kd, 0.3, torch.from_numpy(rpe).cuda())
+    assert orc.max_norm_err(host(kd), k_ref) < tol
+    k2 = torch.from_numpy(k).cuda().to(dtype).transpose(1, 2)
+    L.key_prologue(k2, 0.5)
+    assert orc.max_norm_err(host(k2), orc.key_prologue(host(torch.from_numpy(k).cuda().to(dtype).transpose(1, 2)), 0.5)) < tol
+    out = L.output_noise(xd, nd, 0.1)
+    assert orc.max_norm_err(host(out), orc.output_noise(host(xd), host(nd), 0.1)) < tol
+
+
+def test_fastmax_with_rpe_and_noise_dropout_switched_on():
+    """The two optional steps inside the operator, forward and gradients, against the oracle composed the same way."""
+    import reproducing_fastmax_results_b200 as pkg
+
+    B, H, N, D, t, rate = 2, 3, 40, 32, 3.0, 0.1
+    rng = np.random.default_rng(23)
+    q, k, v, do, noise = (rng.standard_normal((B, H, N, D)).astype(np.float32) for _ in range(5))
+    rpe = 0.3 * rng.standard_normal((2 * N - 1, D)).astype(np.float32)
+    qd, kd, vd = (torch.from_numpy(a).cuda().requires_grad_(True) for a in (q, k, v))
+    dod, nd, rd = (torch.from_numpy(a).cuda() for a in (do, noise, rpe))
+    op = pkg.FASTMultiHeadAttention(apply_rpe=True, noise_dropout=True)
+    out = op(qd, kd, vd, nd, rd, True, rate, False, t, 1.0, 1.0, 0.5, 1.0, 2)
+    out.backward(dod)
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0, 2)
+    k_op = orc.key_prologue(k, 1.0 / t, rpe)
+    o_ref, _ = orc.fastmax_naive(q, k_op, v, True, poly)
+    assert orc.max_norm_err(host(out), orc.output_noise(o_ref, noise, rate)) < 1e-4
+    dq_ref, dk_ref, dv_ref = orc.fastmax_naive_grads(q, k_op, v, orc.output_noise(do, noise, rate), True, poly)
+    assert orc.max_norm_err(host(qd.grad), dq_ref) < 1e-4
+    assert orc.max_norm_err(host(kd.grad), dk_ref / t) < 1e-4
+    assert orc.max_norm_err(host(vd.grad), dv_ref) < 1e-4
+    # default switches: the arguments are ignored, as in the reference
+    plain = pkg.fastmax_custom(qd, kd, vd, nd, rd, True, rate, False, t, 1.0, 1.0, 0.5, 1.0, 2)
+    o_plain, _ = orc.fastmax_naive(q, k, v, True, orc.Poly(1.0, 1.0, 0.5, 1.0 / t, 2))
+    assert orc.max_norm_err(host(plain), o_plain) < 1e-4

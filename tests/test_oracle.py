@@ -174,3 +174,19 @@ def test_reference_property_causality(tiny):
     v2[-1] -= 7.0
     o2, _ = orc.fastmax_streaming(q, k2, v2, True, poly, chunk=2)
     assert np.allclose(o1[:-1], o2[:-1]) and not np.allclose(o1[-1], o2[-1])
+
+
+def test_key_prologue_and_output_noise_follow_the_reference_kernels():
+    """apply_rpe_and_temp with its RPE line (fastmax_cuda_forward.cu:288-289) and apply_dropout (:346), as loops."""
+    rng = np.random.default_rng(0)
+    nk, d = 7, 4
+    k = rng.standard_normal((3, nk, d))
+    rpe = rng.standard_normal((2 * nk - 1, d))
+    ref = k.copy()
+    for l in range(nk):
+        ref[:, l] = ref[:, l] / 2.5 + rpe[(l + nk) % (2 * nk - 1)]
+    assert np.allclose(orc.key_prologue(k, 1 / 2.5, rpe), ref)
+    assert np.allclose(orc.key_prologue(k, 1 / 2.5), k / 2.5)
+    o, noise = rng.standard_normal((2, 5, d)), rng.standard_normal((2, 5, d))
+    assert np.allclose(orc.output_noise(o, noise, 0.1), o * (1 + 0.1 * noise))
+    assert np.allclose(orc.output_noise(o, noise, 0.0), o)   # what the reference actually runs (scale 0.0, :443)
