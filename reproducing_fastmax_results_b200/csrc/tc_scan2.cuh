@@ -227,26 +227,26 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
     mbar_init(&bars[B_O_FREE], 4);
     *abort_flag = 0;
     fence_mbar_init();
-    // Slab tables.  A chunk's slab sequence depends on its kind: 0 = apply + update (per tile A0 U0 A1 U1, in the last
-    // tile A0 A1 U0 U1 so the output drain overlaps the updates), 1 = update only (U0 U1), 2 = apply only (A0 A1).
-    // Entry [set][kind][base]: the slabs of such a chunk that fall into ring slot `set` when the chunk's first slab has
-    // sequence index `base` (mod 3); 4 bits per slab (tile | apply << 2 | half << 3), their count in bits 28..31.
-    for (int set = 0; set < NSETS; ++set)
-      for (int kind = 0; kind < 3; ++kind)
-        for (int base = 0; base < NSETS; ++base) {
-          uint32_t tab = 0, n = 0;
-          const int nsl = (kind == 0 ? 4 : 2) * ntl;
-          for (int i = 0; i < nsl; ++i) {
-            if ((base + i) % NSETS != set) continue;
-            int t, half;
-            bool is_q;
-            if (kind == 0) { t = i >> 2; slab_kind(false, t == ntl - 1, i & 3, is_q, half); }
-            else { t = i >> 1; is_q = (kind == 2); half = i & 1; }
-            tab |= (uint32_t)(t | ((is_q ? 1 : 0) << 2) | (half << 3)) << (4 * n);
-            ++n;
-          }
-          slab_tabs[(set * 3 + kind) * 3 + base] = tab | (n << 28);
-        }
+  }
+  if (tid >= 32 && tid < 32 + 27) {
+    // Slab tables, one entry per thread.  A chunk's slab sequence depends on its kind: 0 = apply + update (per tile
+    // A0 U0 A1 U1, in the last tile A0 A1 U0 U1 so the output drain overlaps the updates), 1 = update only (U0 U1),
+    // 2 = apply only (A0 A1).  Entry [set][kind][base]: the slabs of such a chunk that fall into ring slot `set` when
+    // the chunk's first slab has sequence index `base` (mod 3); 4 bits per slab (tile | apply << 2 | half << 3), their
+    // count in bits 28..31.
+    const int e = tid - 32, set = e / 9, kind = (e / 3) % 3, base = e % 3;
+    uint32_t tab = 0, n = 0;
+    const int nsl = (kind == 0 ? 4 : 2) * ntl;
+    for (int i = 0; i < nsl; ++i) {
+      if ((base + i) % NSETS != set) continue;
+      int t, half;
+      bool is_q;
+      if (kind == 0) { t = i >> 2; slab_kind(false, t == ntl - 1, i & 3, is_q, half); }
+      else { t = i >> 1; is_q = (kind == 2); half = i & 1; }
+      tab |= (uint32_t)(t | ((is_q ? 1 : 0) << 2) | (half << 3)) << (4 * n);
+      ++n;
+    }
+    slab_tabs[e] = tab | (n << 28);
   }
   if (w == 0) tmem_alloc(tmem_slot, 512);
   // the MMAs read one column block past the nine stored ones of each B operand: keep those bytes finite
