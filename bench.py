@@ -35,6 +35,10 @@ WORKLOADS = {
     "cfg2_bf16_causal_p2_B8_H16_N4096_D64": (8, 16, 4096, 64, 2, True, "bf16", 1.0),
     # profiling case: same per-CTA work as config 2, a few GB on the device, inputs (134 MB) larger than L2
     "prof_bf16_causal_p2_B4_H16_N4096_D64": (4, 16, 4096, 64, 2, True, "bf16", 1.0),
+    # the config-2 shape without a mask: the moment build over all keys, then the apply over all queries (and the
+    # matching backward), on the same tensor-memory scans
+    "nc_bf16_noncausal_p2_B8_H16_N4096_D64": (8, 16, 4096, 64, 2, False, "bf16", 1.0),
+    "ncprof_bf16_noncausal_p2_B4_H16_N4096_D64": (4, 16, 4096, 64, 2, False, "bf16", 1.0),
     # BASELINE config 3: one long causal sequence, cut into contiguous pieces across the ranks (strong scaling)
     "cfg3_f32_causal_p2_B1_H8_N131072_D32": (1, 8, 131072, 32, 2, True, "f32", 1.0),
     # BASELINE config 4: order 1, non-causal, wide batch, forward (run with --mode fwd): HBM-bound

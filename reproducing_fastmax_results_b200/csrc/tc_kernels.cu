@@ -429,8 +429,9 @@ struct ScanGeom {
   int nch;           // chunks of 128 positions
   int qc0, qc1;      // chunks that hold queries
   int kc0, kc1;      // chunks that hold keys
-  int nslices, tile_first, state_rows;
+  int nslices, tps, tile_first, state_rows;
 };
+static int device_sms();
 static ScanGeom scan_geom(const fastmax_problem* pb) {
   ScanGeom g{};
   g.k0 = pb->causal ? pb->nk - pb->nq : (pb->nk + tc::CH - 1) / tc::CH * tc::CH;
@@ -440,7 +441,12 @@ static ScanGeom scan_geom(const fastmax_problem* pb) {
   g.qc1 = pb->nq > 0 ? (g.k0 + pb->nq - 1) / tc::CH : g.qc0 - 1;
   g.kc0 = 0;
   g.kc1 = (pb->nk - 1) / tc::CH;
-  g.nslices = pb->order == 2 ? 5 : 1;
+  // Order 2: 19 feature tiles per head, four per thread block (5 slices).  When even that leaves SMs without a block
+  // (fewer than 30 heads on 148 SMs) three per block (7 slices: more, shorter blocks).  Measured on B8..B1 x H16 x
+  // N4096: 4 tiles win from 32 heads up (0.82 vs 0.84 ms, 1.44 vs 1.51 ms), 3 tiles by 2 % at 16 heads.
+  g.tps = 4;
+  if (pb->order == 2 && (long long)pb->batch * pb->heads * 5 < (long long)device_sms()) g.tps = 3;
+  g.nslices = pb->order == 2 ? (tc::NTILES + g.tps - 1) / g.tps : 1;
   g.tile_first = pb->order == 2 ? 0 : tc::NTILES - 1;
   g.state_rows = pb->order == 2 ? 64 * 36 + 65 : 65;
   return g;
@@ -570,7 +576,7 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
     A.c0 = P.c0; A.c1 = P.c1; A.c2 = P.c2;
     A.state_out = a->state_out; A.state_in = a->state_in;
     A.sc = make_sched(G, false, a->state_in != nullptr, want_o, a->state_out != nullptr);
-    A.nslices = G.nslices; A.tile_first = G.tile_first; A.state_rows = G.state_rows;
+    A.nslices = G.nslices; A.tps = G.tps; A.tile_first = G.tile_first; A.state_rows = G.state_rows;
     tc::s2::scan_apply_kernel<false><<<dim3(G.nslices * bh), tc::s2::THREADS, tc::s2::SMEM_BYTES, ss[0]>>>(tmq, tmkt, tmv, A);
   }
   e = cudaGetLastError();
@@ -695,7 +701,7 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
     A.nchunks = G.nch; A.c0 = c0; A.c1 = c1; A.c2 = c2;
     A.state_out = a->dstate_out; A.state_in = a->dstate_in;
     A.sc = make_sched(G, true, a->dstate_in != nullptr, want_apply, a->dstate_out != nullptr);
-    A.nslices = G.nslices; A.tile_first = G.tile_first; A.state_rows = G.state_rows;
+    A.nslices = G.nslices; A.tps = G.tps; A.tile_first = G.tile_first; A.state_rows = G.state_rows;
     return A;
   };
   if (!want_grads) {
@@ -772,7 +778,7 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
     C.nchunks = G.nch; C.c1 = c1; C.c2 = c2;
     C.state_in = dk ? a->dstate_in : a->state_in;
     C.sc = make_sched(G, dk, C.state_in != nullptr, true, false);
-    C.nslices = G.nslices; C.tile_first = G.tile_first; C.state_rows = G.state_rows;
+    C.nslices = G.nslices; C.tps = G.tps; C.tile_first = G.tile_first; C.state_rows = G.state_rows;
     return C;
   };
   {

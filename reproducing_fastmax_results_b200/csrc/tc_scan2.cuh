@@ -74,7 +74,8 @@ struct ApplyParams {
                            // [BH][state_rows][68] (exchange layout)
   const float* state_in;   // optional: the state the scan starts from (same layout); sc.h = 1
   Sched sc;                // which chunks apply / update
-  int nslices;             // thread blocks per head (order 2: 5; order 1: 1)
+  int nslices;             // thread blocks per head (order 2: 5 slices of 4 tiles, or 7 of 3; order 1: 1)
+  int tps;                 // feature tiles per slice (at most 4: the TMEM accumulators)
   int tile_first;          // first feature tile of the problem (order 2: 0; order 1: the linear/constant tile)
   int state_rows;          // rows of the exchange layout (order 2: 64 * 36 + 65; order 1: 65)
 };
@@ -206,8 +207,8 @@ scan_apply_kernel(const __grid_constant__ CUtensorMap tmz, const __grid_constant
   // q / k / v tiles through L2.  gridDim.x = 5 * batch * heads.
   const int head = (int)blockIdx.x / P.nslices, slice = (int)blockIdx.x - P.nslices * head;
   const int b_idx = head / P.heads, h_idx = head - b_idx * P.heads;
-  const int tile0 = P.tile_first + slice * 4;
-  const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
+  const int tile0 = P.tile_first + slice * P.tps;
+  const int ntl = (NTILES - tile0) < P.tps ? (NTILES - tile0) : P.tps;
   const int nch = P.nchunks;
   const Sched sc = P.sc;
   const bool lin_slice = (tile0 + ntl == NTILES);   // this slice holds the linear/constant tile: weights go into Sb

@@ -69,7 +69,7 @@ struct ChainParams {
   const float* state_in;   // optional: the state the scan starts from (dq: moments of earlier keys; dk: gradient moments of
                            // later queries), float32 [BH][state_rows][68]; sc.h = 1
   Sched sc;                // which chunks run the chain rule ("apply") / update the state
-  int nslices, tile_first, state_rows;   // as in s2::ApplyParams
+  int nslices, tps, tile_first, state_rows;   // as in s2::ApplyParams
 };
 
 template <int R> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R)); }
@@ -110,8 +110,8 @@ scan_chain_kernel(const __grid_constant__ CUtensorMap tmxt, const __grid_constan
   // q / k / v tiles through L2.  gridDim.x = 5 * batch * heads.
   const int head = (int)blockIdx.x / P.nslices, slice = (int)blockIdx.x - P.nslices * head;
   const int b_idx = head / P.heads, h_idx = head - b_idx * P.heads;
-  const int tile0 = P.tile_first + slice * 4;
-  const int ntl = (NTILES - tile0) < 4 ? (NTILES - tile0) : 4;
+  const int tile0 = P.tile_first + slice * P.tps;
+  const int ntl = (NTILES - tile0) < P.tps ? (NTILES - tile0) : P.tps;
   const int nch = P.nchunks;
   const Sched sc = P.sc;
   auto chunk_of = [&](int i) -> int { return DK ? (nch - 1 - i) : i; };  // i-th chunk of the scan
