@@ -409,6 +409,23 @@ static cudaError_t join_streams(SideStreams* p, cudaStream_t st, int n) {
   return cudaSuccess;
 }
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel) instead of on every call: the attribute
+// sticks to the function on that device.  `slot` numbers the kernels of this file.
+template <typename K>
+static cudaError_t ensure_smem(K kernel, int bytes, int slot) {
+  static std::mutex mu;
+  static bool done[64][8] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || slot < 0 || slot >= 8) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  std::lock_guard<std::mutex> lk(mu);
+  if (done[dev][slot]) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done[dev][slot] = true;
+  return e;
+}
+
 // Joins the side streams back into the caller's stream when a call leaves between its fork and its join (an error
 // return): the side streams must never be left holding work the caller's stream does not wait for.
 struct JoinOnExit {
@@ -511,7 +528,7 @@ static int tc_p1_forward(const fastmax_problem* pb, const fastmax_forward_args* 
       !make_map(&tmv, a->v, pb->batch, pb->heads, pb->nk, 8, tc::CH, false) ||
       !make_map(&tmo, a->o, pb->batch, pb->heads, pb->nq, 64, 32, true))   // output: 32-row boxes, one per epilogue warp
     return FASTMAX_TC_NOT_HANDLED;
-  cudaError_t e = cudaFuncSetAttribute(tc::p1::p1_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::p1::SMEM_BYTES);
+  cudaError_t e = ensure_smem(tc::p1::p1_forward_kernel, tc::p1::SMEM_BYTES, 0);
   if (e != cudaSuccess) return report_cuda_error(e);
   tc::p1::P1Params P{View{a->g.ptr, a->g.stride_b, a->g.stride_h, a->g.stride_n},
                      pb->heads, pb->nq, pb->nk, pb->a0, pb->a1 * pb->inv_temperature};
@@ -558,9 +575,9 @@ int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* w
   P.c0 = pb->a0;
   P.c1 = pb->a1 * pb->inv_temperature;
   P.c2 = pb->order == 2 ? pb->a2 * pb->inv_temperature * pb->inv_temperature : 0.f;
-  e = cudaFuncSetAttribute(tc::s2::scan_apply_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s2::SMEM_BYTES);
+  e = ensure_smem(tc::s2::scan_apply_kernel<false>, tc::s2::SMEM_BYTES, 1);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(tc::intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::I_SMEM_BYTES);
+    e = ensure_smem(tc::intra_fwd_kernel, tc::I_SMEM_BYTES, 2);
   if (e != cudaSuccess) return report_cuda_error(e);
   // the scan and the intra-chunk kernel both ADD into the O' accumulator: independent, side by side
   const bool intra = want_o && pb->causal;
@@ -693,7 +710,7 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   if (e != cudaSuccess) return report_cuda_error(e);
   const float c0 = pb->a0, c1 = pb->a1 * pb->inv_temperature;
   const float c2 = pb->order == 2 ? pb->a2 * pb->inv_temperature * pb->inv_temperature : 0.f;
-  e = cudaFuncSetAttribute(tc::s2::scan_apply_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s2::SMEM_BYTES);
+  e = ensure_smem(tc::s2::scan_apply_kernel<true>, tc::s2::SMEM_BYTES, 3);
   if (e != cudaSuccess) return report_cuda_error(e);
   auto dv_params = [&](bool want_apply) {
     tc::s2::ApplyParams A{};
@@ -725,11 +742,11 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
            f0.numRegs >= tc::s3::REG_LAUNCH && f1.numRegs >= tc::s3::REG_LAUNCH;
   }();
   if (!chain_ok) return FASTMAX_TC_NOT_HANDLED;
-  e = cudaFuncSetAttribute(tc::s3::scan_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s3::SMEM_BYTES);
+  e = ensure_smem(tc::s3::scan_chain_kernel<false>, tc::s3::SMEM_BYTES, 4);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(tc::s3::scan_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::s3::SMEM_BYTES);
+    e = ensure_smem(tc::s3::scan_chain_kernel<true>, tc::s3::SMEM_BYTES, 5);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(tc::intra_bwd_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::IP_SMEM_BYTES);
+    e = ensure_smem(tc::intra_bwd_pipe_kernel, tc::IP_SMEM_BYTES, 6);
   if (e != cudaSuccess) return report_cuda_error(e);
   // Causal: the intra-chunk kernel goes first: it STORES its part into every row of the three accumulators (no
   // memset).  It fills all SMs by itself (one CTA per SM), so nothing is lost by letting the scans wait for it.  The
