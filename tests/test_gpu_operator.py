@@ -185,8 +185,8 @@ def test_fastmax_keeps_the_head_split_layout_so_the_merge_is_free():
 
 
 def test_extension_calls_release_the_gil():
-    """A Python thread keeps running while another one is inside the extension (SURVEY of the boundary: the
-    reference holds the GIL and synchronises the device; this extension does neither)."""
+    """A Python thread keeps running while another one is inside the extension (the reference's binding holds the GIL
+    and synchronises the device, fastmax_cuda_forward.cu:423-444; this extension does neither)."""
     import threading
     import time
 
