@@ -39,6 +39,9 @@ WORKLOADS = {
     # matching backward), on the same tensor-memory scans
     "nc_bf16_noncausal_p2_B8_H16_N4096_D64": (8, 16, 4096, 64, 2, False, "bf16", 1.0),
     "ncprof_bf16_noncausal_p2_B4_H16_N4096_D64": (4, 16, 4096, 64, 2, False, "bf16", 1.0),
+    # one long causal sequence with few heads in bf16 / D=64 (config 3's shape at the tensor-memory engine's dtype and
+    # head dim): the library cuts it into segments so that the scans still cover the GPU
+    "long_bf16_causal_p2_B1_H8_N131072_D64": (1, 8, 131072, 64, 2, True, "bf16", 1.0),
     # BASELINE config 3: one long causal sequence, cut into contiguous pieces across the ranks (strong scaling)
     "cfg3_f32_causal_p2_B1_H8_N131072_D32": (1, 8, 131072, 32, 2, True, "f32", 1.0),
     # BASELINE config 4: order 1, non-causal, wide batch, forward (run with --mode fwd): HBM-bound

@@ -85,15 +85,29 @@ struct Plan {
   int q_chunks, q_nseg, q_cps;
 };
 
-static int pick_nseg(int bh, int nslices, int nchunks, int min_chunks_per_seg) {
-  long long ctas = (long long)bh * nslices;
-  int target = 2 * sm_count();
-  if (ctas >= sm_count()) return 1;
-  int nseg = (int)((target + ctas - 1) / ctas);
+// Segments per head for a call whose (head, slice) thread blocks alone would leave SMs idle.  `per_sm` thread blocks
+// of the scan kernels are resident per SM (registers and shared memory: one, or two for the forward and dq scans at
+// head dims up to 32), so the time goes with (waves of thread blocks) x (chunks per segment): the count that
+// minimises that product is taken, e.g. 9 segments (288 blocks = 1.95 waves of 148) rather than 10 (320 blocks =
+// 2.16 waves, i.e. three rounds) for 32 blocks per segment.
+static int pick_nseg(int bh, int nslices, int nchunks, int min_chunks_per_seg, int per_sm) {
+  const long long ctas = (long long)bh * nslices;
+  const int sms = sm_count() * per_sm;
+  if (ctas >= sms || nchunks <= 0) return 1;
   int cap = nchunks / min_chunks_per_seg;
   if (cap < 1) cap = 1;
-  if (nseg > cap) nseg = cap;
-  return nseg < 1 ? 1 : nseg;
+  const int limit = (int)((4ll * sms + ctas - 1) / ctas);   // up to about four waves
+  if (cap > limit) cap = limit;
+  int best = 1;
+  long long best_cost = (long long)nchunks;                 // one wave, every chunk in sequence
+  for (int want = 2; want <= cap; ++want) {
+    const int cps = (nchunks + want - 1) / want;
+    const int nseg = (nchunks + cps - 1) / cps;
+    const long long waves = (ctas * nseg + sms - 1) / sms;
+    const long long cost = waves * cps;
+    if (cost < best_cost) { best_cost = cost; best = nseg; }
+  }
+  return best;
 }
 
 static void split(int nchunks, int want, int& nseg, int& cps) {
@@ -106,7 +120,7 @@ static void split(int nchunks, int want, int& nseg, int& cps) {
   nseg = (nchunks + cps - 1) / cps;
 }
 
-static int make_plan(const fastmax_problem* pb, Plan& pl) {
+static int make_plan(const fastmax_problem* pb, Plan& pl, bool backward = false) {
   if (!pb) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (pb->batch <= 0 || pb->heads <= 0 || pb->nq < 0 || pb->nk < 0) return FASTMAX_ERR_INVALID_ARGUMENT;
   if (pb->dtype != FASTMAX_F32 && pb->dtype != FASTMAX_BF16) return FASTMAX_ERR_INVALID_ARGUMENT;
@@ -127,8 +141,10 @@ static int make_plan(const fastmax_problem* pb, Plan& pl) {
   pl.k_chunks = (pb->nk + pl.C - 1) / pl.C;
   pl.q_chunks = (pb->nq + pl.C - 1) / pl.C;
   // causal scans pay one extra moment pass when split into segments: only split when the GPU would idle
-  int want_k = pick_nseg(pl.bh, pl.nslices, pl.k_chunks, pb->causal ? 8 : 2);
-  int want_q = pick_nseg(pl.bh, pl.nslices, pl.q_chunks, 2);
+  // the dk/dv scan (the longest kernel of a backward call) keeps one thread block per SM, see scan_min_blocks
+  const int per_sm = (pb->d <= 32 && !backward) ? 2 : 1;
+  int want_k = pick_nseg(pl.bh, pl.nslices, pl.k_chunks, pb->causal ? 8 : 2, per_sm);
+  int want_q = pick_nseg(pl.bh, pl.nslices, pl.q_chunks, 2, per_sm);
   split(pl.k_chunks, want_k, pl.k_nseg, pl.k_cps);
   split(pl.q_chunks, want_q, pl.q_nseg, pl.q_cps);
   return FASTMAX_OK;
@@ -516,7 +532,7 @@ static void bwd_layout(const fastmax_problem* pb, const fastmax_backward_args* a
 
 size_t fastmax_backward_workspace(const fastmax_problem* pb, const fastmax_backward_args* args) {
   Plan pl;
-  if (!args || make_plan(pb, pl) != FASTMAX_OK) return 0;
+  if (!args || make_plan(pb, pl, true) != FASTMAX_OK) return 0;
   BwdLayout L;
   bwd_layout(pb, args, pl, L);
   size_t tc = tc_backward_workspace(pb, args);
@@ -527,7 +543,7 @@ int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args*
                          void* stream) {
   Plan pl;
   if (!a) return FASTMAX_ERR_INVALID_ARGUMENT;
-  int rc = make_plan(pb, pl);
+  int rc = make_plan(pb, pl, true);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   BwdLayout L;

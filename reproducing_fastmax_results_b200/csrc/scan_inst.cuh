@@ -8,7 +8,7 @@ namespace fm {
 template <typename T, int D, int MODE, bool CAUSAL>
 static cudaError_t launch_scan_one(const ScanParams& P, dim3 grid, cudaStream_t st) {
   auto kern = scan_kernel<T, D, MODE, CAUSAL>;
-  constexpr size_t smem = scan_smem_bytes<D>();
+  constexpr size_t smem = scan_smem_bytes<D, MODE>();
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   {

@@ -348,21 +348,42 @@ __device__ __forceinline__ void flush_rows(const float* Red, float* gout, int gl
 // ------------------------------------------------------------------------------------------------
 // the scan kernel
 // ------------------------------------------------------------------------------------------------
-template <typename T, int D, int MODE, bool CAUSAL>
-__global__ void __launch_bounds__(Cfg<D>::NT, 1) scan_kernel(const ScanParams P) {
+// Shared memory of one scan CTA, in floats: only the tiles the mode uses are laid out, so that for head dims up to 32
+// two CTAs of the forward and of the dq scan fit on an SM (their register need allows it too).
+template <int D, int MODE>
+struct ScanSmem {
   using G = Geo<D>;
   using K = Cfg<D>;
+  static constexpr int S = 0;
+  static constexpr int Q = S + K::SROWS * G::LDS;                                   // q tile  [C][LDX]
+  static constexpr int KK = Q + K::C * G::LDX;                                      // k tile  [C][LDX]
+  static constexpr int V = KK + K::C * G::LDX;                                      // [V|1]   [C][LDY]
+  static constexpr int O = V + K::C * G::LDY;                                       // dO'     [C][LDY]   (backward)
+  static constexpr int RED = O + (MODE != MODE_FWD ? K::C * G::LDY : 0);            // output staging [C][LDY]
+  static constexpr int RED2 = RED + K::C * G::LDY;                                  // second output (dv)   (dk/dv scan)
+  static constexpr int A = RED2 + (MODE == MODE_BWD_KV ? K::C * G::LDY : 0);        // tril f(QK^T) [C][LDA]   (not dq)
+  static constexpr int DM = A + (MODE != MODE_BWD_Q ? K::C * K::LDA : 0);           // tril (dO' V'^T) f'      (backward)
+  static constexpr int TOTAL = DM + (MODE != MODE_FWD ? K::C * K::LDA : 0);
+};
+template <int D, int MODE>
+constexpr int scan_min_blocks() { return (D <= 32 && MODE != MODE_BWD_KV) ? 2 : 1; }
+
+template <typename T, int D, int MODE, bool CAUSAL>
+__global__ void __launch_bounds__(Cfg<D>::NT, scan_min_blocks<D, MODE>()) scan_kernel(const ScanParams P) {
+  using G = Geo<D>;
+  using K = Cfg<D>;
+  using L = ScanSmem<D, MODE>;
   constexpr int C = K::C, NT = K::NT, NSUB = K::NSUB, LDA = K::LDA;
   extern __shared__ __align__(16) float smem[];
-  float* Ss = smem;
-  float* Qs = Ss + K::SROWS * G::LDS;            // q tile  [C][LDX]
-  float* Ks = Qs + C * G::LDX;                   // k tile  [C][LDX]
-  float* Vs = Ks + C * G::LDX;                   // [V|1]   [C][LDY]
-  float* Os = Vs + C * G::LDY;                   // dO'     [C][LDY]
-  float* Red = Os + C * G::LDY;                  // output staging [C][LDY]
-  float* Red2 = Red + C * G::LDY;                // second output (dv) [C][LDY]
-  float* Am = Red2 + C * G::LDY;                 // tril f(QK^T)            [C][LDA]
-  float* Dm = Am + C * LDA;                      // tril (dO' V'^T) f'      [C][LDA]
+  float* Ss = smem + L::S;
+  float* Qs = smem + L::Q;
+  float* Ks = smem + L::KK;
+  float* Vs = smem + L::V;
+  float* Os = smem + L::O;       // the pointers of tiles a mode does not have alias the next tile and are never used
+  float* Red = smem + L::RED;
+  float* Red2 = smem + L::RED2;
+  float* Am = smem + L::A;
+  float* Dm = smem + L::DM;
 
   const int tid = threadIdx.x;
   const int slice = blockIdx.x, seg = blockIdx.y, head = blockIdx.z;
@@ -543,11 +564,9 @@ __global__ void __launch_bounds__(Cfg<D>::NT, 1) scan_kernel(const ScanParams P)
   }
 }
 
-template <int D>
+template <int D, int MODE>
 constexpr size_t scan_smem_bytes() {
-  using G = Geo<D>;
-  using K = Cfg<D>;
-  return sizeof(float) * (size_t)(K::SROWS * G::LDS + 2 * K::C * G::LDX + 4 * K::C * G::LDY + 2 * K::C * K::LDA);
+  return sizeof(float) * (size_t)ScanSmem<D, MODE>::TOTAL;
 }
 
 // ------------------------------------------------------------------------------------------------

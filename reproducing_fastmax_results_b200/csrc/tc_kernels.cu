@@ -266,6 +266,23 @@ intra_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant_
 #include "tc_scan3.cuh"
 #include "tc_p1.cuh"
 
+// Exclusive running sum over the segments of the states st[seg][head][n] (in place): forward order (prefix) or
+// reverse (suffix), starting from init[head][n] when given; total_out[head][n] (optional) = init + all segments.
+__global__ void seg_state_scan_kernel(float* __restrict__ st, int nseg, int heads, long long n, const float* __restrict__ init,
+                                      float* __restrict__ total_out, int reverse) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // over heads * n
+  if (idx >= (long long)heads * n) return;
+  float run = init ? init[idx] : 0.f;
+  for (int i = 0; i < nseg; ++i) {
+    const int sgi = reverse ? nseg - 1 - i : i;
+    float* p = st + (long long)sgi * heads * n + idx;
+    const float t = *p;
+    *p = run;
+    run += t;
+  }
+  if (total_out) total_out[idx] = run;
+}
+
 // Test-only kernel for the bounded-wait failure path: one thread waits, with a limit of `cycles` SM clocks, on an
 // mbarrier that nobody ever arrives on, then records wait site `code` exactly as a production role would
 // (s2::fail_record: histogram, abort flag, status word) and returns normally.  No TMA, MMA or TMEM is involved.
@@ -486,13 +503,49 @@ static tc::Sched make_sched(const ScanGeom& g, bool reverse, bool has_init, bool
   return sc;
 }
 
-static bool tc_common_supported(const fastmax_problem* pb) {
+static bool tc_kernels_cover(const fastmax_problem* pb) {
   if (pb->flags & FASTMAX_FLAG_NO_TENSOR_CORES) return false;
   if (pb->dtype != FASTMAX_BF16 || pb->d != 64 || (pb->order != 1 && pb->order != 2)) return false;
   if (pb->nk <= 0) return false;
-  if ((long long)pb->batch * pb->heads * (pb->order == 2 ? 5 : 1) < 64) return false;  // too few thread blocks: the segmented CUDA-core engine does better
   if ((long long)pb->nk + pb->nq + 2 * tc::CH >= (1ll << 30)) return false;
   return true;
+}
+static bool tc_enough_blocks(const fastmax_problem* pb) {
+  return (long long)pb->batch * pb->heads * (pb->order == 2 ? 5 : 1) >= 64;   // one scan CTA per (head, slice)
+}
+static bool tc_common_supported(const fastmax_problem* pb) { return tc_kernels_cover(pb) && tc_enough_blocks(pb); }
+
+// Long causal sequences with few heads (one scan CTA per (head, slice) would leave most SMs idle): the sequence of a
+// batch-1 call is cut into `nseg` segments that the kernels see as the batch dimension (segment s of every tensor
+// is the view starting at token s * L, so nothing is copied).  Three steps, all on the tensor-memory kernels:
+// (1) the moment state of every segment's keys (update-only scans), (2) an exclusive prefix over the segments,
+// (3) the ordinary call on the segment view with the prefixes as carried states.  The backward does the same for
+// the gradient moments with an exclusive suffix.  Returns the number of segments, or 0 when the call does not
+// qualify (then the CUDA-core engine, which segments on its own, takes it).
+static int tc_segments(const fastmax_problem* pb) {
+  if (!tc_kernels_cover(pb) || tc_enough_blocks(pb)) return 0;
+  if (!pb->causal || pb->batch != 1 || pb->nq != pb->nk || pb->nq < 4 * tc::CH) return 0;
+  const long long per_seg = (long long)pb->heads * (pb->order == 2 ? 5 : 1);
+  int nseg = 2;
+  while (per_seg * nseg < 2ll * device_sms() && nseg < 4096) nseg *= 2;     // about two waves of scan CTAs
+  while (nseg > 1 && (pb->nq % (nseg * tc::CH) != 0 || pb->nq / nseg < 2 * tc::CH)) nseg /= 2;
+  if (nseg < 2 || per_seg * nseg < 64) return 0;
+  return nseg;
+}
+static fastmax_tensor seg_view(const fastmax_tensor& t, int seg_len) {
+  fastmax_tensor v = t;
+  v.stride_b = (int64_t)seg_len * t.stride_n;
+  return v;
+}
+static fastmax_problem seg_problem(const fastmax_problem* pb, int nseg) {
+  fastmax_problem vp = *pb;
+  vp.batch = nseg;
+  vp.nq = vp.nk = pb->nq / nseg;
+  return vp;
+}
+static size_t seg_state_bytes(const fastmax_problem* pb, int nseg) {
+  const size_t rows = pb->order == 2 ? 64 * 36 + 65 : 65;
+  return ((size_t)nseg * pb->heads * rows * 68 * sizeof(float) + 255) / 256 * 256;
 }
 
 static bool tc_forward_supported(const fastmax_problem* pb, const fastmax_forward_args* a) {
@@ -504,7 +557,19 @@ static bool tc_forward_supported(const fastmax_problem* pb, const fastmax_forwar
   return true;
 }
 
+static bool tc_forward_segmentable(const fastmax_problem* pb, const fastmax_forward_args* a) {
+  return tc_segments(pb) > 0 && a->o.ptr && a->q.ptr && a->k.ptr && a->v.ptr && a->g.ptr;
+}
+
 size_t tc_forward_workspace(const fastmax_problem* pb, const fastmax_forward_args* a) {
+  if (tc_forward_segmentable(pb, a)) {
+    // segment states + the workspace of the larger of the two inner calls (the full call: it also has the output)
+    const int nseg = tc_segments(pb);
+    const fastmax_problem vp = seg_problem(pb, nseg);
+    fastmax_forward_args in = *a;
+    in.state_in = nullptr; in.state_out = nullptr;
+    return seg_state_bytes(pb, nseg) + tc_forward_workspace(&vp, &in);
+  }
   if (!tc_forward_supported(pb, a)) return 0;
   const bool want_o = a->o.ptr && pb->nq > 0;
   return (want_o ? ((size_t)pb->batch * pb->heads * pb->nq * 68 * sizeof(float) + 255) / 256 * 256 : 0) +
@@ -540,8 +605,44 @@ static int tc_p1_forward(const fastmax_problem* pb, const fastmax_forward_args* 
   return e == cudaSuccess ? FASTMAX_OK : report_cuda_error(e);
 }
 
+static int launch_seg_scan(float* seg, int nseg, const fastmax_problem* pb, const float* init, float* total_out, bool reverse,
+                           cudaStream_t st) {
+  const long long n = (long long)(pb->order == 2 ? 64 * 36 + 65 : 65) * 68;
+  const long long total = (long long)pb->heads * n;
+  {
+    LaunchScope ls(KK_STATE_SCAN, st);
+    tc::seg_state_scan_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(seg, nseg, pb->heads, n, init, total_out, reverse ? 1 : 0);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FASTMAX_OK : report_cuda_error(e);
+}
+
+// forward of a long batch-1 sequence cut into segments (see tc_segments)
+static int tc_forward_segmented(const fastmax_problem* pb, const fastmax_forward_args* a, void* ws, size_t ws_bytes, cudaStream_t st) {
+  const int nseg = tc_segments(pb);
+  if (ws_bytes < tc_forward_workspace(pb, a)) return FASTMAX_ERR_WORKSPACE;
+  const fastmax_problem vp = seg_problem(pb, nseg);
+  float* seg = (float*)ws;
+  void* inner = (char*)ws + seg_state_bytes(pb, nseg);
+  const size_t inner_bytes = ws_bytes - seg_state_bytes(pb, nseg);
+  fastmax_forward_args t{};   // (1) moments of every segment's keys
+  t.q = seg_view(a->k, vp.nk); t.k = seg_view(a->k, vp.nk); t.v = seg_view(a->v, vp.nk);
+  t.state_out = seg;
+  int rc = tc_forward(&vp, &t, inner, inner_bytes, st);
+  if (rc != FASTMAX_OK) return rc == FASTMAX_TC_NOT_HANDLED ? FASTMAX_ERR_UNSUPPORTED : rc;
+  rc = launch_seg_scan(seg, nseg, pb, a->state_in, a->state_out, false, st);   // (2) exclusive prefix, total = state_out
+  if (rc != FASTMAX_OK) return rc;
+  fastmax_forward_args m{};   // (3) every segment from its prefix
+  m.q = seg_view(a->q, vp.nq); m.k = seg_view(a->k, vp.nk); m.v = seg_view(a->v, vp.nk);
+  m.o = seg_view(a->o, vp.nq); m.g = seg_view(a->g, vp.nq);
+  m.state_in = seg;
+  rc = tc_forward(&vp, &m, inner, inner_bytes, st);
+  return rc == FASTMAX_TC_NOT_HANDLED ? FASTMAX_ERR_UNSUPPORTED : rc;
+}
+
 int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (tc_p1_supported(pb, a)) return tc_p1_forward(pb, a, st);
+  if (tc_forward_segmentable(pb, a)) return tc_forward_segmented(pb, a, ws, ws_bytes, st);
   if (!tc_forward_supported(pb, a)) return FASTMAX_TC_NOT_HANDLED;
   if (ws_bytes < tc_forward_workspace(pb, a)) return FASTMAX_ERR_WORKSPACE;
   const bool want_o = a->o.ptr && pb->nq > 0;
@@ -654,14 +755,66 @@ static void tc_bwd_layout(const fastmax_problem* pb, bool want_grads, TcBwdLayou
   L.total = off;
 }
 
+static bool tc_backward_segmentable(const fastmax_problem* pb, const fastmax_backward_args* a) {
+  if (tc_segments(pb) <= 0 || !(a->dq.ptr && a->dk.ptr && a->dv.ptr)) return false;
+  for (const fastmax_tensor* t : {&a->o, &a->d_out})
+    if (((uintptr_t)t->ptr & 3) || (t->stride_b & 1) || (t->stride_h & 1) || (t->stride_n & 1)) return false;
+  return true;
+}
+
 size_t tc_backward_workspace(const fastmax_problem* pb, const fastmax_backward_args* a) {
+  if (tc_backward_segmentable(pb, a)) {
+    const int nseg = tc_segments(pb);
+    const fastmax_problem vp = seg_problem(pb, nseg);
+    fastmax_backward_args in = *a;
+    in.state_in = nullptr; in.dstate_in = nullptr; in.dstate_out = nullptr;
+    fastmax_forward_args f{};
+    f.q = a->k; f.k = a->k; f.v = a->v;
+    float dummy = 0.f;
+    f.state_out = &dummy;   // sizes the state-only inner call
+    const size_t inner_f = tc_forward_workspace(&vp, &f), inner_b = tc_backward_workspace(&vp, &in);
+    return 2 * seg_state_bytes(pb, nseg) + (inner_f > inner_b ? inner_f : inner_b);
+  }
   if (!tc_backward_supported(pb, a)) return 0;
   TcBwdLayout L;
   tc_bwd_layout(pb, a->dq.ptr != nullptr, L);
   return L.total;
 }
 
+// backward of a long batch-1 sequence cut into segments (see tc_segments)
+static int tc_backward_segmented(const fastmax_problem* pb, const fastmax_backward_args* a, void* ws, size_t ws_bytes, cudaStream_t st) {
+  const int nseg = tc_segments(pb);
+  if (ws_bytes < tc_backward_workspace(pb, a)) return FASTMAX_ERR_WORKSPACE;
+  const fastmax_problem vp = seg_problem(pb, nseg);
+  const size_t sb = seg_state_bytes(pb, nseg);
+  float* segS = (float*)ws;
+  float* segD = (float*)((char*)ws + sb);
+  void* inner = (char*)ws + 2 * sb;
+  const size_t inner_bytes = ws_bytes - 2 * sb;
+  auto fix = [](int rc) { return rc == FASTMAX_TC_NOT_HANDLED ? (int)FASTMAX_ERR_UNSUPPORTED : rc; };
+  fastmax_forward_args t{};   // key moments of every segment, exclusive prefix (what dq needs)
+  t.q = seg_view(a->k, vp.nk); t.k = seg_view(a->k, vp.nk); t.v = seg_view(a->v, vp.nk);
+  t.state_out = segS;
+  int rc = tc_forward(&vp, &t, inner, inner_bytes, st);
+  if (rc != FASTMAX_OK) return fix(rc);
+  rc = launch_seg_scan(segS, nseg, pb, a->state_in, nullptr, false, st);
+  if (rc != FASTMAX_OK) return rc;
+  fastmax_backward_args m{};
+  m.q = seg_view(a->q, vp.nq); m.k = seg_view(a->k, vp.nk); m.v = seg_view(a->v, vp.nk);
+  m.o = seg_view(a->o, vp.nq); m.g = seg_view(a->g, vp.nq); m.d_out = seg_view(a->d_out, vp.nq);
+  fastmax_backward_args gmom = m;   // gradient moments of every segment, exclusive suffix (what dk, dv need)
+  gmom.dstate_out = segD;
+  rc = tc_backward(&vp, &gmom, inner, inner_bytes, st);
+  if (rc != FASTMAX_OK) return fix(rc);
+  rc = launch_seg_scan(segD, nseg, pb, a->dstate_in, a->dstate_out, true, st);
+  if (rc != FASTMAX_OK) return rc;
+  m.dq = seg_view(a->dq, vp.nq); m.dk = seg_view(a->dk, vp.nk); m.dv = seg_view(a->dv, vp.nk);
+  m.state_in = segS; m.dstate_in = segD;
+  return fix(tc_backward(&vp, &m, inner, inner_bytes, st));
+}
+
 int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (tc_backward_segmentable(pb, a)) return tc_backward_segmented(pb, a, ws, ws_bytes, st);
   if (!tc_backward_supported(pb, a)) return FASTMAX_TC_NOT_HANDLED;
   const bool want_grads = a->dq.ptr != nullptr;
   TcBwdLayout L;

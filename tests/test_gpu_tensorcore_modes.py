@@ -170,3 +170,41 @@ def test_decoder_prefill_continuation_on_tensor_memory():
         o_ref, _ = orc.fastmax_naive(host(q[b, h]), host(k[b, h]), host(v[b, h]), True, poly)
         got = np.concatenate([host(o1[b, h]), host(o2[b, h])] + [host(s[b, h]).reshape(1, D) for s in steps], 0)
         assert orc.max_norm_err(got, o_ref) < 2e-2
+
+
+@pytest.mark.parametrize("shape", [(4, 2048, 2), (8, 4096, 2), (2, 4096, 2), (8, 16384, 1)])
+def test_long_sequence_with_few_heads_is_cut_into_segments(shape):
+    """Batch 1, few heads, long causal sequence: too few (head, slice) thread blocks for the scans, so the call is cut
+    into segments that the tensor-memory kernels see as the batch dimension (segment moments -> exclusive prefix ->
+    the call on the segment view with carried states; the backward with the gradient moments and a suffix)."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    H, N, order = shape
+    q, k, v, do = inputs(1, H, N, N, N + H, 0.7)
+    poly = orc.Poly(1.0, 1.0, 0.5, 1.0 / (2.0 * math.sqrt(D)), order)
+    L.profile_collect()
+    L.profile(True)
+    o, g, state = L.forward(q, k, v, True, poly.inv_temp, order=order, want_state=True)
+    dq, dk, dv, _ = L.backward(q, k, v, o, g, do, True, poly.inv_temp, order=order)
+    L.check_status()
+    L.profile(False)
+    prof = L.profile_collect()
+    assert TC_SCANS <= set(prof) and not (FFMA & set(prof)) and "state_scan" in prof, prof
+    # forward: key-moments pass + main pass; backward: key moments again, gradient moments, then the main scans
+    assert prof["tc_scan_fwd"][1] == 3 and prof["tc_scan_bwd_dv"][1] == 2 and prof["tc_scan_bwd_q"][1] == 1, prof
+    _, _, state_ref = L.forward(q, k, v, True, poly.inv_temp, order=order, want_state=True, flags=L.FLAG_NO_TENSOR_CORES)
+    torch.cuda.synchronize()
+    assert orc.max_norm_err(host(state), host(state_ref)) < 5e-3
+    rows = torch.tensor([0, 1, 127, 128, N // 2 - 1, N // 2, N - 129, N - 1], device="cuda")
+    for h in (0, H - 1):
+        a = [host(t[0, h]) for t in (q, k, v, do)]
+        oh, gh = host(o[0, h]), host(g[0, h])
+        r = rows.cpu().numpy()
+        o_ref, g_ref = orc.sampled_forward_rows(a[0], a[1], a[2], r, True, poly)
+        assert orc.max_norm_err(oh[r], o_ref) < 2e-2 and orc.max_norm_err(gh[r], g_ref) < 2e-2
+        dq_ref = orc.sampled_dq_rows(a[0], a[1], a[2], oh, gh, a[3], r, True, poly)
+        dk_ref, dv_ref = orc.sampled_dkv_cols(a[0], a[1], a[2], oh, gh, a[3], r, True, poly)
+        scale = lambda t: np.abs(host(t[0, h])).max()
+        assert np.abs(host(dq[0, h])[r] - dq_ref).max() < 2e-2 * scale(dq)
+        assert np.abs(host(dk[0, h])[r] - dk_ref).max() < 2e-2 * scale(dk)
+        assert np.abs(host(dv[0, h])[r] - dv_ref).max() < 2e-2 * scale(dv)
