@@ -729,6 +729,24 @@ def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq
         # bf16 autocast: q, k, v reach the tensor-memory kernels as strided bf16 views
         "bf16_autocast_zero_copy": dict(autocast=True, swap=True),
     }
+    if world > 1:
+        # the collective alone: one all-reduce of a tensor as large as the model's gradients, nothing else running
+        buf = torch.zeros(70944337, device=dev)
+        for _ in range(2):
+            dist.all_reduce(buf)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(5):
+            dist.all_reduce(buf)
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / 5], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ar_ms = float(t.item())
+        out["allreduce_alone"] = {"bytes": 4 * buf.numel(), "ms": ar_ms,
+                                  "bus_gbs": 2.0 * (world - 1) / world * 4 * buf.numel() / (ar_ms * 1e-3) / 1e9}
+        del buf
     for vname, vcfg in variants.items():
         torch.manual_seed(0)
         net = model.Transformer(**CFG5).to(dev)
@@ -737,7 +755,7 @@ def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq
         if world > 1:
             from torch.nn.parallel import DistributedDataParallel as DDP
 
-            ddp = DDP(net, device_ids=[dev.index])
+            ddp = DDP(net, device_ids=[dev.index], gradient_as_bucket_view=True)
         opt = torch.optim.AdamW(net.parameters(), lr=3e-4)
         gen = torch.Generator(device=dev).manual_seed(rank)
         ids = torch.randint(0, CFG5["vocab_size"], (batch, seq + 1), device=dev, generator=gen)
