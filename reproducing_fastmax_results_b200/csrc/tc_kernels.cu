@@ -1,12 +1,15 @@
-// tcgen05 / TMEM kernels of the Fastmax engine: bf16 operands, fp32 accumulation in tensor memory; causal, head
-// dim 64, order 2.  The 2369 feature rows of the state are cut into 19 tiles of 128 rows (18 tiles of two 8x8-block
-// pair units + the tile with the linear and constant features); a scan CTA = (batch*head, slice of 4 tiles).
+// tcgen05 / TMEM kernels of the Fastmax engine: bf16 operands, fp32 accumulation in tensor memory; head dim 64,
+// order 1 and 2, with and without a mask, carried moment states in and out.  The 2369 feature rows of the order-2
+// state are cut into 19 tiles of 128 rows (18 tiles of two 8x8-block pair units + the tile with the linear and
+// constant features); a scan CTA = (batch*head, slice of up to 4 tiles); order 1 is the last tile alone.
 // This file holds what the scans share and the host side:
+//   Sched              which chunks of a scan apply the state / update it / refresh its bf16 copy
 //   intra_fwd_kernel   O'_c += tril f(Q_c K_c^T) [V_c | 1], one CTA per (chunk, head), parallel over chunks
 //   tc_bwd.cuh         intra-chunk backward kernel, dO' prologue
 //   tc_scan2.cuh       forward scan and dv scan ("apply + update", Phi operands in tensor memory)
 //   tc_scan3.cuh       dq and dk scans (dphi + chain rule + update)
-//   tc_forward / tc_backward: tensor maps, workspace layout, launch sequences
+//   tc_forward / tc_backward: scan geometry and schedules, tensor maps, workspace layout, launch sequences,
+//                      segmentation of long batch-1 sequences with few heads
 // Every device-side wait is bounded: on a timeout a role records an error code, raises the CTA's abort flag, and
 // the CTA frees its TMEM and returns.
 #include <cuda.h>

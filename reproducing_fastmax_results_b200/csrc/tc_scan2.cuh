@@ -1,11 +1,14 @@
-// Causal "apply + update" scans with the Phi operands in tensor memory.  Included by tc_kernels.cu inside fm::tc.
+// "Apply + update" scans with the Phi operands in tensor memory.  Included by tc_kernels.cu inside fm::tc.
 //
 // One kernel template serves two scans that have the same shape:
 //   forward (DV = false), chunks ascending:    O'_c  = Phi(Q_c) Sb_{<c}           S  += Phi(K_c)^T [V_c | 1]
 //   dv scan (DV = true),  chunks descending:   dV_c  = Phi(K_c) dSb_{>c}[:, :64]  dS += Phi(Q_c)^T dO'_c
 // In both, "Z" is the raw [token][64] tile whose Phi multiplies the state copy (Q | K), "X" the tile whose Phi^T
 // builds the state (K | Q, read from a transposed copy [64][tokens]) and "Y" the 80-column right-hand side of the
-// update ([V|1] | dO').  The intra-chunk (masked) terms are added by separate kernels.
+// update ([V|1] | dO').  The intra-chunk (masked) terms are added by separate kernels.  Which chunks apply, which
+// update and where the bf16 state copy is refreshed comes from the call's schedule (Sched, tc_kernels.cu): causal
+// calls do both in every chunk, a non-causal call updates over the key chunks and then applies over the query
+// chunks, a state-only call only updates; the scan may start from a caller-provided state and write its final one.
 //
 // Why tensor memory: an SS tcgen05.mma with N = 80 reads 4 KB of A and 2.5 KB of B from shared memory per K = 16
 // step (52 clocks of the 128 B/clock shared-memory pipe against 40 clocks of math), and a Phi tile that goes
@@ -20,7 +23,8 @@
 // An apply slab holds 64 features of Phi(Z) (thread = token, from the raw tile); an update slab holds 64 tokens of
 // Phi(X)^T (thread = feature, from the transposed tile, rows of 144 bytes); both cost two 128-bit shared loads
 // per eight products.  Slab order per (chunk, tile): A0 U0 A1 U1 (A0 A1 U0 U1 in the last tile, so the output drain
-// overlaps the updates; U0 U1 only in the first chunk, which has no earlier state).  Three producer sets of four
+// overlaps the updates); U0 U1 in a chunk that only updates (e.g. the first chunk, which has no earlier state),
+// A0 A1 in a chunk that only applies.  Three producer sets of four
 // warps each own one ring slot (set s makes the slabs s, s+3, ... of the slab sequence); two issuer warps issue the
 // apply and the update MMAs (independent accumulator chains) and wait on per-kind `full` barriers; every barrier
 // has one producer and one consumer, so no waiter is ever more than one phase away from the barrier it polls.

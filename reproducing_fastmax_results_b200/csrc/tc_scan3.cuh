@@ -7,6 +7,8 @@
 // "G" is the 80-column tile that multiplies the state copy (dO' | [V|1]), "Y" the right-hand side of the state
 // update ([V|1] | dO'), "X" the tile whose Phi^T builds the state (K | Q, from the transposed copies) and "Z" the
 // rows the chain rule differentiates (Q | K, read straight from global memory by the chain-rule threads).
+// Which chunks run the chain rule, which update the state and where its bf16 copy is refreshed comes from the
+// call's schedule (Sched, tc_kernels.cu); the scan may start from a caller-provided state.
 // Per 128-token chunk and 128-row feature tile t of the CTA's slice:
 //   dphi    D_u (128 tok x 64 feat) = G_c (128 x 80, smem, K-major) * Sb_t[unit u]^T     per 64-feature unit u, SS MMA
 //   update  S_t (128 feat x 80)    += Phi_t(X_c)^T (TMEM slabs, as in tc_scan2.cuh) * Y_c (128 tok x 80, smem)
