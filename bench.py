@@ -755,7 +755,7 @@ def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq
         if world > 1:
             from torch.nn.parallel import DistributedDataParallel as DDP
 
-            ddp = DDP(net, device_ids=[dev.index], gradient_as_bucket_view=True)
+            ddp = DDP(net, device_ids=[dev.index])
         opt = torch.optim.AdamW(net.parameters(), lr=3e-4)
         gen = torch.Generator(device=dev).manual_seed(rank)
         ids = torch.randint(0, CFG5["vocab_size"], (batch, seq + 1), device=dev, generator=gen)
@@ -764,13 +764,14 @@ def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq
             model.fastmax_custom = pkg.fastmax_custom
         try:
             def step(sync=True):
-                ctx = contextlib.nullcontext() if (sync or world == 1) else ddp.no_sync()
-                with ctx:
-                    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=vcfg["autocast"]):
-                        logits = ddp(ids[:, :-1])
-                    loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), ids[:, 1:].reshape(-1))
-                    opt.zero_grad(set_to_none=True)
-                    loss.backward()
+                # sync=False: the same step on the bare module (no DDP hooks, no gradient all-reduce): the replicas
+                # drift apart, so it is only used for the last timing of a variant
+                fwd = ddp if sync else net
+                with torch.autocast("cuda", dtype=torch.bfloat16, enabled=vcfg["autocast"]):
+                    logits = fwd(ids[:, :-1])
+                loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), ids[:, 1:].reshape(-1))
+                opt.zero_grad(set_to_none=True)
+                loss.backward()
                 opt.step()
                 return loss
 
@@ -800,13 +801,16 @@ def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq
                 l0 = lib.fastmax_launch_count()
                 ms, loss1 = timed(steps)
                 launches = lib.fastmax_launch_count() - l0
-                ms_nosync = timed(steps, sync=False)[0] if world > 1 else None
                 _lib.profile_collect()
                 _lib.profile(True)
                 step()
                 torch.cuda.synchronize()
                 _lib.profile(False)
-            prof = _lib.profile_collect()
+                prof = _lib.profile_collect()
+                ms_nosync = None
+                if world > 1:
+                    step(sync=False)
+                    ms_nosync = timed(steps, sync=False)[0]
             lib_ms = sum(m for m, _ in prof.values())
             out[vname] = {
                 "value": world * batch * seq / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "parameters": nparams,
@@ -817,7 +821,7 @@ def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq
                     "bytes_per_step": 4 * nparams, "ms_per_step_without_gradient_sync": ms_nosync,
                     "exposed_ms_per_step": ms - ms_nosync,
                     "note": "DDP buckets the all-reduce under the backward pass; exposed = step time minus the same step "
-                            "run under no_sync()"},
+                            "of the bare module (no DDP hooks, no all-reduce), timed right after"},
             }
         finally:
             model.fastmax_custom = saved

@@ -86,8 +86,7 @@ struct Plan {
 };
 
 // Segments per head for a call whose (head, slice) thread blocks alone would leave SMs idle.  `per_sm` thread blocks
-// of the scan kernels are resident per SM (registers and shared memory: one, or two for the forward and dq scans at
-// head dims up to 32), so the time goes with (waves of thread blocks) x (chunks per segment): the count that
+// of the scan kernels are resident per SM (registers and shared memory: two at head dims up to 32, else one), so the time goes with (waves of thread blocks) x (chunks per segment): the count that
 // minimises that product is taken, e.g. 9 segments (288 blocks = 1.95 waves of 148) rather than 10 (320 blocks =
 // 2.16 waves, i.e. three rounds) for 32 blocks per segment.
 static int pick_nseg(int bh, int nslices, int nchunks, int min_chunks_per_seg, int per_sm) {
@@ -141,8 +140,8 @@ static int make_plan(const fastmax_problem* pb, Plan& pl, bool backward = false)
   pl.k_chunks = (pb->nk + pl.C - 1) / pl.C;
   pl.q_chunks = (pb->nq + pl.C - 1) / pl.C;
   // causal scans pay one extra moment pass when split into segments: only split when the GPU would idle
-  // the dk/dv scan (the longest kernel of a backward call) keeps one thread block per SM, see scan_min_blocks
-  const int per_sm = (pb->d <= 32 && !backward) ? 2 : 1;
+  (void)backward;
+  const int per_sm = pb->d <= 32 ? 2 : 1;   // thread blocks of the scan kernels resident per SM, see scan_min_blocks
   int want_k = pick_nseg(pl.bh, pl.nslices, pl.k_chunks, pb->causal ? 8 : 2, per_sm);
   int want_q = pick_nseg(pl.bh, pl.nslices, pl.q_chunks, 2, per_sm);
   split(pl.k_chunks, want_k, pl.k_nseg, pl.k_cps);

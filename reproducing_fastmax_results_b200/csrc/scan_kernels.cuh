@@ -348,8 +348,9 @@ __device__ __forceinline__ void flush_rows(const float* Red, float* gout, int gl
 // ------------------------------------------------------------------------------------------------
 // the scan kernel
 // ------------------------------------------------------------------------------------------------
-// Shared memory of one scan CTA, in floats: only the tiles the mode uses are laid out, so that for head dims up to 32
-// two CTAs of the forward and of the dq scan fit on an SM (their register need allows it too).
+// Shared memory of one scan CTA, in floats: only the tiles the mode uses are laid out and the two intra-chunk
+// matrices are stored as packed triangles, so that for head dims up to 32 two CTAs fit on an SM (93 / 94 / 111 KB for
+// the forward / dq / dk-dv scans; their register need, capped at 128 by the launch bounds, allows it without spills).
 template <int D, int MODE>
 struct ScanSmem {
   using G = Geo<D>;
@@ -361,19 +362,21 @@ struct ScanSmem {
   static constexpr int O = V + K::C * G::LDY;                                       // dO'     [C][LDY]   (backward)
   static constexpr int RED = O + (MODE != MODE_FWD ? K::C * G::LDY : 0);            // output staging [C][LDY]
   static constexpr int RED2 = RED + K::C * G::LDY;                                  // second output (dv)   (dk/dv scan)
-  static constexpr int A = RED2 + (MODE == MODE_BWD_KV ? K::C * G::LDY : 0);        // tril f(QK^T) [C][LDA]   (not dq)
-  static constexpr int DM = A + (MODE != MODE_BWD_Q ? K::C * K::LDA : 0);           // tril (dO' V'^T) f'      (backward)
-  static constexpr int TOTAL = DM + (MODE != MODE_FWD ? K::C * K::LDA : 0);
+  static constexpr int TRI = K::C * (K::C + 1) / 2;    // a lower-triangular [C][C] matrix, packed: (l, j <= l) at l (l + 1) / 2 + j
+  static constexpr int A = RED2 + (MODE == MODE_BWD_KV ? K::C * G::LDY : 0);        // tril f(QK^T)            (not dq)
+  static constexpr int DM = A + (MODE != MODE_BWD_Q ? TRI : 0);                     // tril (dO' V'^T) f'      (backward)
+  static constexpr int TOTAL = DM + (MODE != MODE_FWD ? TRI : 0);
 };
 template <int D, int MODE>
-constexpr int scan_min_blocks() { return (D <= 32 && MODE != MODE_BWD_KV) ? 2 : 1; }
+constexpr int scan_min_blocks() { return D <= 32 ? 2 : 1; }
+__device__ __forceinline__ int tri_index(int l, int j) { return ((l * (l + 1)) >> 1) + j; }
 
 template <typename T, int D, int MODE, bool CAUSAL>
 __global__ void __launch_bounds__(Cfg<D>::NT, scan_min_blocks<D, MODE>()) scan_kernel(const ScanParams P) {
   using G = Geo<D>;
   using K = Cfg<D>;
   using L = ScanSmem<D, MODE>;
-  constexpr int C = K::C, NT = K::NT, NSUB = K::NSUB, LDA = K::LDA;
+  constexpr int C = K::C, NT = K::NT, NSUB = K::NSUB;
   extern __shared__ __align__(16) float smem[];
   float* Ss = smem + L::S;
   float* Qs = smem + L::Q;
@@ -464,8 +467,10 @@ __global__ void __launch_bounds__(Cfg<D>::NT, scan_min_blocks<D, MODE>()) scan_k
             ds = ((p0 + p1) + (p2 + p3)) * (P.c1 + 2.f * P.c2 * s);
           }
         }
-        if (MODE != MODE_BWD_Q) Am[l * LDA + j] = a;
-        if (MODE != MODE_FWD) Dm[l * LDA + j] = ds;
+        if (j <= l) {   // entries above the diagonal are zero and not stored
+          if (MODE != MODE_BWD_Q) Am[tri_index(l, j)] = a;
+          if (MODE != MODE_FWD) Dm[tri_index(l, j)] = ds;
+        }
       }
       __syncthreads();
     }
@@ -479,7 +484,7 @@ __global__ void __launch_bounds__(Cfg<D>::NT, scan_min_blocks<D, MODE>()) scan_k
       if (do_intra) {
         const int jmax = l | 31;
         for (int j = sub; j <= jmax; j += NSUB) {
-          const float a = Am[l * LDA + j];
+          const float a = j <= l ? Am[tri_index(l, j)] : 0.f;   // the loop bound is warp-uniform: up to 31 zeros
           const float4* vrow = reinterpret_cast<const float4*>(Vs + j * G::LDY);
 #pragma unroll
           for (int j4 = 0; j4 < G::LDY / 4; ++j4) {
@@ -498,7 +503,7 @@ __global__ void __launch_bounds__(Cfg<D>::NT, scan_min_blocks<D, MODE>()) scan_k
         for (int d = 0; d < D; ++d) acc[d] = 0.f;
         const int jmax = l | 31;
         for (int j = sub; j <= jmax; j += NSUB) {
-          const float ds = Dm[l * LDA + j];
+          const float ds = j <= l ? Dm[tri_index(l, j)] : 0.f;
           const float4* krow = reinterpret_cast<const float4*>(Ks + j * G::LDX);
 #pragma unroll
           for (int d4 = 0; d4 < D / 4; ++d4) {
@@ -524,8 +529,8 @@ __global__ void __launch_bounds__(Cfg<D>::NT, scan_min_blocks<D, MODE>()) scan_k
         for (int d = 0; d < D; ++d) dkacc[d] = 0.f;
         const int lmin = l & ~31;
         for (int ll = lmin + sub; ll < C; ll += NSUB) {
-          const float ds = Dm[ll * LDA + l];
-          const float a = Am[ll * LDA + l];
+          const float ds = ll >= l ? Dm[tri_index(ll, l)] : 0.f;
+          const float a = ll >= l ? Am[tri_index(ll, l)] : 0.f;
           const float4* qrow = reinterpret_cast<const float4*>(Qs + ll * G::LDX);
           const float4* orow = reinterpret_cast<const float4*>(Os + ll * G::LDY);
 #pragma unroll
