@@ -278,6 +278,59 @@ def cpu_sample_reference(workload, n_sample=512, heads=1):
     return total, heads * n_sample, threads
 
 
+def config1_record(torch, dev):
+    """BASELINE config 1 exactly (order 2, no mask, float32, B2 H4 N256 D32, q, k, v ~ N(0,1) from seed 0, upstream
+    gradient of ones), the one configuration the reference's CPU code runs whole: its forward + backward time on the
+    host cores, this library's on the GPU (through the C ABI), and the largest max-normalised difference between the
+    two sets of results (o, dq, dk, dv): the reference itself as the checker, on this machine."""
+    from reproducing_fastmax_results_b200 import _lib
+
+    ein = reference_einops()
+    if ein is None:
+        return None
+    B, H, N, D = 2, 4, 256, 32
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(B, H, N, D) for _ in range(3))
+    do = torch.ones(B, H, N, D)
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+
+    def ref_step():
+        qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k, v))
+        o = ein.fastmax(qq, kk, vv, mask=False, normalize_term=8, tensors_normalized=False, p=2)
+        o.backward(do)
+        return o.detach(), qq.grad, kk.grad, vv.grad
+
+    ref_step()
+    t0 = time.perf_counter()
+    reps = 5
+    for _ in range(reps):
+        ref = ref_step()
+    cpu_ms = (time.perf_counter() - t0) / reps * 1e3
+    qd, kd, vd, dod = (t.to(dev) for t in (q, k, v, do))
+    inv_temp = 1.0 / (8.0 * math.sqrt(D))
+
+    def gpu_step():
+        o, g, _ = _lib.forward(qd, kd, vd, False, inv_temp, order=2)
+        return (o,) + tuple(_lib.backward(qd, kd, vd, o, g, dod, False, inv_temp, order=2)[:3])
+
+    for _ in range(5):
+        got = gpu_step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(50):
+        gpu_step()
+    b.record()
+    torch.cuda.synchronize()
+    gpu_ms = a.elapsed_time(b) / 50
+    err = max(float((x.cpu().double() - r.double()).abs().max() / r.double().abs().max()) for x, r in zip(got, ref))
+    return {"config": "order 2, no mask, float32, B2 H4 N256 D32, forward + backward, upstream gradient of ones",
+            "reference_cpu_ms": cpu_ms, "cores": threads, "gpu_ms": gpu_ms,
+            "reference_cpu_ktokens_per_s": B * N / cpu_ms, "gpu_ktokens_per_s": B * N / gpu_ms,
+            "max_normalised_difference": err, "tolerance": 1e-4}
+
+
 def cpu_baseline_record(workload, n_sample, heads):
     """CPU figure for the JSON line: the reference's einops code when it is present (kind "reference"), with the oracle's
     restatement as a second figure; the restatement alone (kind "port") otherwise."""
@@ -1111,6 +1164,11 @@ def main():
     cpu = None
     if rank == 0 and not args.no_cpu and world == 1:   # the CPU leg runs at N = 1 only
         cpu = cpu_baseline_record(args.workload, args.cpu_tokens, args.cpu_heads)
+        if args.workload == DEFAULT:
+            try:
+                cpu["config1"] = config1_record(torch, dev)
+            except Exception as e:   # reported, never fatal for the headline line
+                cpu["config1"] = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     input_mb = 4 * q.numel() * q.element_size() >> 20
     others = None
