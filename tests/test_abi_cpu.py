@@ -94,3 +94,16 @@ def test_python_extension_module_is_importable_under_reference_name():
 
     assert ext is fastmax_cuda
     assert hasattr(ext, "forwardpass") and hasattr(ext, "backwardpass")
+
+
+def test_optional_steps_validate_before_launching():
+    lib = _lib.load()
+    t = _lib.Tensor(4096, 64 * 32, 32 * 64, 32)
+    assert lib.fastmax_key_prologue(1, 2, 64, 48, 0, 1.0, C.byref(t), None, None) == 2      # head dim not supported
+    assert lib.fastmax_key_prologue(1, 2, 64, 32, 9, 1.0, C.byref(t), None, None) == 1      # bad dtype
+    assert lib.fastmax_key_prologue(1, 2, 64, 32, 0, 1.0, None, None, None) == 1            # no tensor
+    assert lib.fastmax_key_prologue(1, 2, 0, 32, 0, 1.0, C.byref(t), None, None) == 0       # nothing to do
+    bad = _lib.Tensor(4100, 64 * 32, 32 * 64, 32)
+    assert lib.fastmax_key_prologue(1, 2, 64, 32, 0, 1.0, C.byref(bad), None, None) == 6    # misaligned base
+    assert lib.fastmax_output_noise(1, 2, 64, 32, 0, 0.1, C.byref(t), None, C.byref(t), None) == 1
+    assert lib.fastmax_output_noise(1, 2, 64, 16, 1, 0.1, C.byref(t), C.byref(bad), C.byref(t), None) == 6
