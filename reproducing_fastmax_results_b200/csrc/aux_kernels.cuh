@@ -1,6 +1,7 @@
 // Memory-bound helper kernels: segment-state scans, forward combine/divide, backward prologue, output casts
 // and the q/k normalisation.
 #pragma once
+#include <cooperative_groups.h>
 #include "common.cuh"
 
 namespace fm {
@@ -420,6 +421,169 @@ __global__ void norm_bwd_apply_vec_kernel(View y, View dy, View dx, int n, int h
 #pragma unroll
   for (int i = 0; i < 8; ++i) o[i] = sc * (g[i] - gmean) + extra * a[i];
   store8<T>(reinterpret_cast<T*>(const_cast<void*>(dx.ptr)) + (long long)r.b * dx.sb + (long long)r.h * dx.sh + (long long)r.l * dx.sn + r.c, o);
+}
+
+// ---- one-launch variants: a thread-block cluster per (batch, head) ---------------------------------------------
+// gridDim = (CL, batch*heads) with CL blocks of 256 threads per cluster.  Pass 1: every block walks its share of the
+// head's tokens and reduces (max squared norm / sum dy.y); the CL partial results meet through distributed shared
+// memory (each block reads its peers' partial after a cluster barrier, in rank order, so the sum does not depend on
+// timing).  Pass 2 walks the same tokens in the opposite order and writes the result; what it reads again comes from
+// L2 as far as the tensors in flight fit there.  No atomics, no zeroed scratch, one launch per direction.
+// (Measured against this form on B8 H16 N4096 D64 bf16, forward + backward, 0.113 ms: blocks of 1024 threads, one
+// per SM, that keep their loads in registers between the passes took 0.156 ms, since with one block per SM nothing
+// overlaps the barrier between the passes; fewer resident blocks of this form, for more L2 hits, took 0.119 ms.)
+template <typename T, int LPR>
+__global__ void __launch_bounds__(256) norm_fused_vec_kernel(View x, View y, int n, int heads, unsigned long long* stats, float lim) {
+  constexpr int D = 8 * LPR, RPI = 256 / LPR;
+  namespace cgx = cooperative_groups;
+  cgx::cluster_group cluster = cgx::this_cluster();
+  const int cl = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+  __shared__ unsigned long long part[8];
+  __shared__ unsigned long long mine;     // this block's partial: read by the peers
+  __shared__ unsigned long long total;
+  const int head = blockIdx.y, b = head / heads, h = head - b * heads;
+  const T* xb = reinterpret_cast<const T*>(x.ptr) + (long long)b * x.sb + (long long)h * x.sh;
+  T* yb = reinterpret_cast<T*>(const_cast<void*>(y.ptr)) + (long long)b * y.sb + (long long)h * y.sh;
+  const int iters = (n + RPI * cl - 1) / (RPI * cl);
+  const int lrow = (int)threadIdx.x / LPR, c = ((int)threadIdx.x - lrow * LPR) * 8;
+  unsigned long long best = 0ull;
+#pragma unroll 4
+  for (int it = 0; it < iters; ++it) {
+    const int l = (it * cl + rank) * RPI + lrow;
+    const bool valid = l < n;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    if (valid) load8<T>(xb + (long long)l * x.sn + c, v);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += v[i];
+    const float mean = row_sum<LPR>(s) / (float)D;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q += (v[i] - mean) * (v[i] - mean);
+    q = row_sum<LPR>(q);
+    if (valid && c == 0) {
+      const unsigned long long packed = ((unsigned long long)__float_as_uint(q) << 32) | (unsigned long long)(0xffffffffu - (unsigned)l);
+      best = packed > best ? packed : best;
+    }
+  }
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) {
+    const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, k);
+    best = o > best ? o : best;
+  }
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) best = part[i] > best ? part[i] : best;
+    mine = best;
+  }
+  cluster.sync();                         // every block's partial is written and every block is known to run
+  if (threadIdx.x == 0) {
+    unsigned long long t = 0ull;
+    for (int r = 0; r < cl; ++r) {
+      const unsigned long long o = *cluster.map_shared_rank(&mine, r);
+      t = o > t ? o : t;
+    }
+    total = t;
+    if (rank == 0) stats[head] = t;
+  }
+  __syncthreads();
+  const float sc = lim / sqrtf(__uint_as_float((unsigned)(total >> 32)));
+#pragma unroll 4
+  for (int it = iters - 1; it >= 0; --it) {
+    const int l = (it * cl + rank) * RPI + lrow;
+    const bool valid = l < n;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    if (valid) load8<T>(xb + (long long)l * x.sn + c, v);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += v[i];
+    const float mean = row_sum<LPR>(s) / (float)D;
+    if (valid) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = (v[i] - mean) * sc;
+      store8<T>(yb + (long long)l * y.sn + c, v);
+    }
+  }
+  cluster.sync();                         // no block leaves while a peer may still read its partial
+}
+
+template <typename T, int LPR>
+__global__ void __launch_bounds__(256) norm_bwd_fused_vec_kernel(View y, View dy, View dx, int n, int heads,
+                                                                  const unsigned long long* stats, float lim) {
+  constexpr int D = 8 * LPR, RPI = 256 / LPR;
+  namespace cgx = cooperative_groups;
+  cgx::cluster_group cluster = cgx::this_cluster();
+  const int cl = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+  __shared__ float part[8];
+  __shared__ float mine;
+  __shared__ float total;
+  const int head = blockIdx.y, b = head / heads, h = head - b * heads;
+  const T* yb = reinterpret_cast<const T*>(y.ptr) + (long long)b * y.sb + (long long)h * y.sh;
+  const T* gb = reinterpret_cast<const T*>(dy.ptr) + (long long)b * dy.sb + (long long)h * dy.sh;
+  T* ob = reinterpret_cast<T*>(const_cast<void*>(dx.ptr)) + (long long)b * dx.sb + (long long)h * dx.sh;
+  const int iters = (n + RPI * cl - 1) / (RPI * cl);
+  const int lrow = (int)threadIdx.x / LPR, c = ((int)threadIdx.x - lrow * LPR) * 8;
+  float q = 0.f;
+#pragma unroll 4
+  for (int it = 0; it < iters; ++it) {
+    const int l = (it * cl + rank) * RPI + lrow;
+    if (l < n) {
+      float a[8], g[8];
+      load8<T>(yb + (long long)l * y.sn + c, a);
+      load8<T>(gb + (long long)l * dy.sn + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q += a[i] * g[i];
+    }
+  }
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) q += __shfl_xor_sync(0xffffffffu, q, k);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = q;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) q += part[i];
+    mine = q;
+  }
+  cluster.sync();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int r = 0; r < cl; ++r) t += *cluster.map_shared_rank(&mine, r);
+    total = t;
+  }
+  __syncthreads();
+  const unsigned long long st = stats[head];
+  const float m = sqrtf(__uint_as_float((unsigned)(st >> 32)));
+  const int am = (int)(0xffffffffu - (unsigned)(st & 0xffffffffu));
+  const float sc = lim / m;
+  const float extra_am = -total / (lim * m);
+#pragma unroll 4
+  for (int it = iters - 1; it >= 0; --it) {
+    const int l = (it * cl + rank) * RPI + lrow;
+    const bool valid = l < n;
+    float a[8], g[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = g[i] = 0.f;
+    if (valid) {
+      load8<T>(yb + (long long)l * y.sn + c, a);
+      load8<T>(gb + (long long)l * dy.sn + c, g);
+    }
+    float sg = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sg += g[i];
+    const float gmean = row_sum<LPR>(sg) / (float)D;
+    if (valid) {
+      const float extra = (l == am) ? extra_am : 0.f;
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = sc * (g[i] - gmean) + extra * a[i];
+      store8<T>(ob + (long long)l * dx.sn + c, o);
+    }
+  }
+  cluster.sync();
 }
 
 // per head: scratch[head] = sum_{l,c} dy * y      (y = normalised output; x - mean = y * m / lim)

@@ -760,6 +760,42 @@ static bool norm_vec_ok(int d, int dtype, std::initializer_list<const fastmax_te
     }                                                                                                   \
   } while (0)
 
+// One launch with a thread-block cluster per (batch, head).  Used when there are enough heads to fill the device
+// with such clusters; a few long heads keep the two-launch form, whose blocks spread over all tokens.
+static int norm_cluster_size(int batch, int heads, int n, int d) {
+  const long long bh = (long long)batch * heads;
+  const int rows_per_iter = 256 / (d / 8);
+  int cl = 8;
+  while (cl > 1 && n < cl * rows_per_iter * 2) cl /= 2;
+  if (bh * cl < 2LL * sm_count()) return 0;
+  return cl;
+}
+#define FM_NORM_FUSED(KERNEL, CL, ...)                                                                  \
+  do {                                                                                                  \
+    cudaLaunchConfig_t cfg = {};                                                                        \
+    cfg.gridDim = dim3((unsigned)(CL), (unsigned)(batch * heads));                                      \
+    cfg.blockDim = dim3(256);                                                                           \
+    cfg.stream = st;                                                                                    \
+    cudaLaunchAttribute attr[1];                                                                        \
+    attr[0].id = cudaLaunchAttributeClusterDimension;                                                   \
+    attr[0].val.clusterDim.x = (unsigned)(CL);                                                          \
+    attr[0].val.clusterDim.y = 1;                                                                       \
+    attr[0].val.clusterDim.z = 1;                                                                       \
+    cfg.attrs = attr;                                                                                   \
+    cfg.numAttrs = 1;                                                                                   \
+    cudaError_t fe;                                                                                     \
+    if (dtype == FASTMAX_F32) {                                                                         \
+      if (d == 64) fe = cudaLaunchKernelEx(&cfg, KERNEL<float, 8>, __VA_ARGS__);                        \
+      else if (d == 32) fe = cudaLaunchKernelEx(&cfg, KERNEL<float, 4>, __VA_ARGS__);                   \
+      else fe = cudaLaunchKernelEx(&cfg, KERNEL<float, 2>, __VA_ARGS__);                                \
+    } else {                                                                                            \
+      if (d == 64) fe = cudaLaunchKernelEx(&cfg, KERNEL<__nv_bfloat16, 8>, __VA_ARGS__);                \
+      else if (d == 32) fe = cudaLaunchKernelEx(&cfg, KERNEL<__nv_bfloat16, 4>, __VA_ARGS__);           \
+      else fe = cudaLaunchKernelEx(&cfg, KERNEL<__nv_bfloat16, 2>, __VA_ARGS__);                        \
+    }                                                                                                   \
+    FM_CUDA(fe);                                                                                        \
+  } while (0)
+
 int32_t fastmax_normalize_forward(int32_t batch, int32_t heads, int32_t n, int32_t d, int32_t dtype, float lim,
                                   const fastmax_tensor* x, const fastmax_tensor* y, uint64_t* stats, void* stream) {
   if (!x || !y || !x->ptr || !y->ptr || !stats || batch <= 0 || heads <= 0 || n < 0 || d <= 0 || !(lim > 0.f))
@@ -773,6 +809,11 @@ int32_t fastmax_normalize_forward(int32_t batch, int32_t heads, int32_t n, int32
   unsigned blocks = (unsigned)((nrows * 32 + threads - 1) / threads);
   unsigned long long* sp = reinterpret_cast<unsigned long long*>(stats);
   if (norm_vec_ok(d, dtype, {x, y}) && (long long)batch * heads <= 65535) {
+    if (const int cl = norm_cluster_size(batch, heads, n, d)) {
+      LaunchScope ls(KK_NORMALIZE, st);
+      FM_NORM_FUSED(norm_fused_vec_kernel, cl, to_view(*x), to_view(*y), (int)n, (int)heads, sp, lim);
+      return FASTMAX_OK;
+    }
     {
       LaunchScope ls(KK_NORMALIZE, st);
       FM_NORM_VEC(norm_stats_vec_kernel, NORM_ITERS, to_view(*x), n, heads, sp, nrows);
@@ -817,6 +858,11 @@ int32_t fastmax_normalize_backward(int32_t batch, int32_t heads, int32_t n, int3
   unsigned blocks = (unsigned)((nrows * 32 + threads - 1) / threads);
   const unsigned long long* sp = reinterpret_cast<const unsigned long long*>(stats);
   if (norm_vec_ok(d, dtype, {y, dy, dx}) && (long long)batch * heads <= 65535) {
+    if (const int cl = norm_cluster_size(batch, heads, n, d)) {
+      LaunchScope ls(KK_NORMALIZE, st);
+      FM_NORM_FUSED(norm_bwd_fused_vec_kernel, cl, to_view(*y), to_view(*dy), to_view(*dx), (int)n, (int)heads, sp, lim);
+      return FASTMAX_OK;
+    }
     {
       LaunchScope ls(KK_NORMALIZE, st);
       FM_NORM_VEC(norm_bwd_dot_vec_kernel, NORM_ITERS, to_view(*y), to_view(*dy), n, heads, scratch, nrows);
