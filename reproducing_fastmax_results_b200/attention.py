@@ -21,12 +21,31 @@ def _ext():
     return load_extension()
 
 
+def _alert_not_deterministic(what):
+    """PyTorch's convention for operators whose results can differ in the last bits from run to run: under
+    torch.use_deterministic_algorithms(True) they raise, with warn_only=True they warn.  The scans sum the partial
+    results of their feature slices with floating-point reduce-adds whose order depends on timing."""
+    if not torch.are_deterministic_algorithms_enabled():
+        return
+    msg = (f"{what} does not have a deterministic implementation, but you set 'torch.use_deterministic_algorithms(True)'. "
+           "Its feature slices add their partial sums in an order that depends on timing, so the low bits of the "
+           "output and of the gradients can differ between runs. You can turn off determinism just for this operation, "
+           "or use 'torch.use_deterministic_algorithms(True, warn_only=True)'.")
+    if torch.is_deterministic_algorithms_warn_only_enabled():
+        import warnings
+
+        warnings.warn(msg, stacklevel=3)
+    else:
+        raise RuntimeError(msg)
+
+
 class FASTMultiHeadAttention_Function(torch.autograd.Function):
     """Behavioural twin of transformer/model.py:14-74 on top of the new `fastmax_cuda` extension."""
 
     @staticmethod
     def forward(ctx, q, k, v, drop_noise, rpe_matrix=None, mask=False, dropout=0.0, normalize=False,
                 temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2):
+        _alert_not_deterministic("FASTMultiHeadAttention_Function")
         ext = _ext()
         b = 0
         if q.dim() == 4:
@@ -89,6 +108,7 @@ class FastMax(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, drop_noise=None, rpe_matrix=None, mask=False, dropout=0.0, normalize=False,
                 temperature=1.0, a0=1.0, a1=1.0, a2=0.5, lim=1.0, p=2, apply_rpe=False, noise_dropout=False):
+        _alert_not_deterministic("FastMax (fastmax_custom)")
         ext = _ext()
         three_d = q.dim() == 3
         if three_d:

@@ -107,3 +107,27 @@ def test_optional_steps_validate_before_launching():
     assert lib.fastmax_key_prologue(1, 2, 64, 32, 0, 1.0, C.byref(bad), None, None) == 6    # misaligned base
     assert lib.fastmax_output_noise(1, 2, 64, 32, 0, 0.1, C.byref(t), None, C.byref(t), None) == 1
     assert lib.fastmax_output_noise(1, 2, 64, 16, 1, 0.1, C.byref(t), C.byref(bad), C.byref(t), None) == 6
+
+
+def test_operators_follow_torch_deterministic_algorithms_setting():
+    """Under torch.use_deterministic_algorithms(True) the operators say that their reductions are not run-to-run
+    deterministic (PyTorch's convention: raise, or warn with warn_only=True) before anything is launched."""
+    import torch
+
+    from reproducing_fastmax_results_b200.attention import FASTMultiHeadAttention_Function, FastMax, _alert_not_deterministic
+
+    q = torch.zeros(1, 1, 4, 16)
+    was, warn_only = torch.are_deterministic_algorithms_enabled(), torch.is_deterministic_algorithms_warn_only_enabled()
+    try:
+        torch.use_deterministic_algorithms(True)
+        with pytest.raises(RuntimeError, match="does not have a deterministic implementation"):
+            FastMax.apply(q, q, q)
+        with pytest.raises(RuntimeError, match="does not have a deterministic implementation"):
+            FASTMultiHeadAttention_Function.apply(q, q, q, q, torch.zeros(7, 16))
+        torch.use_deterministic_algorithms(True, warn_only=True)
+        with pytest.warns(UserWarning, match="does not have a deterministic implementation"):
+            _alert_not_deterministic("FastMax")
+        torch.use_deterministic_algorithms(False)
+        _alert_not_deterministic("FastMax")   # silent
+    finally:
+        torch.use_deterministic_algorithms(was, warn_only=warn_only)

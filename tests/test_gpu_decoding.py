@@ -183,3 +183,24 @@ def test_decode_steps_replay_from_a_cuda_graph():
     torch.cuda.synchronize()
     o_ref, _ = orc.fastmax_naive(host(q), host(k), host(v), True, poly)
     assert orc.max_norm_err(host(torch.stack(outs, 2)), o_ref) < 1e-4
+
+
+def test_decoding_is_bit_for_bit_repeatable():
+    """The decode step sums its partial results in a fixed order (rows of a block, then blocks of the cluster in rank
+    order): two runs over the same tokens give the same bits in every output and in the state."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    B, H, T, D, order = 3, 5, 24, 64, 2
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q, k, v = (torch.randn(B, H, T, D, device="cuda", generator=g) for _ in range(3))
+    runs = []
+    for _ in range(2):
+        state = L.new_state(B, H, D, order)
+        outs = []
+        for t in range(T):
+            o, gg = L.decode_step(q[:, :, t], k[:, :, t], v[:, :, t], state, 0.0625, 1.0, 1.0, 0.5, order)
+            outs += [o, gg]
+        torch.cuda.synchronize()
+        runs.append((outs, state))
+    assert all(torch.equal(a, b) for a, b in zip(runs[0][0], runs[1][0]))
+    assert torch.equal(runs[0][1], runs[1][1])
