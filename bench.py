@@ -331,6 +331,82 @@ def config1_record(torch, dev):
             "max_normalised_difference": err, "tolerance": 1e-4}
 
 
+def config4_record(torch, dev):
+    """BASELINE config 4 exactly (order 1, no mask, B64 H12 N1024 D64, bfloat16 values, forward only): the reference's
+    einops forward on the host cores (on the bf16-rounded inputs, in float32), this library's forward on the GPU
+    through the C ABI, and the max-normalised difference of the outputs (bfloat16 tolerance)."""
+    from reproducing_fastmax_results_b200 import _lib
+
+    ein = reference_einops()
+    if ein is None:
+        return None
+    B, H, N, D = 64, 12, 1024, 64
+    g = torch.Generator().manual_seed(0)
+    q, k, v = ((torch.randn(B, H, N, D, generator=g) * 0.5).bfloat16() for _ in range(3))
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    qf, kf, vf = q.float(), k.float(), v.float()
+    with torch.no_grad():
+        ref = ein.fastmax(qf, kf, vf, mask=False, normalize_term=8, tensors_normalized=False, p=1)
+        t0 = time.perf_counter()
+        reps = 3
+        for _ in range(reps):
+            ein.fastmax(qf, kf, vf, mask=False, normalize_term=8, tensors_normalized=False, p=1)
+        cpu_ms = (time.perf_counter() - t0) / reps * 1e3
+    qd, kd, vd = (t.to(dev) for t in (q, k, v))
+    inv_temp = 1.0 / (8.0 * math.sqrt(D))
+    for _ in range(5):
+        o, _, _ = _lib.forward(qd, kd, vd, False, inv_temp, order=1)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(50):
+        _lib.forward(qd, kd, vd, False, inv_temp, order=1)
+    b.record()
+    torch.cuda.synchronize()
+    gpu_ms = a.elapsed_time(b) / 50
+    err = float((o.float().cpu().double() - ref.double()).abs().max() / ref.double().abs().max())
+    return {"config": "order 1, no mask, bfloat16 values, B64 H12 N1024 D64, forward only",
+            "reference_cpu_ms": cpu_ms, "cores": threads, "gpu_ms": gpu_ms,
+            "reference_cpu_mtokens_per_s": B * N / cpu_ms / 1e3, "gpu_mtokens_per_s": B * N / gpu_ms / 1e3,
+            "max_normalised_difference": err, "tolerance": 2e-2}
+
+
+def score_function_sample(workload, n_sample=256):
+    """Second CPU figure: the reference's other CPU implementation (attention_mechanisms/score_function.py, autograd
+    backward) on one head of n_sample tokens of the workload.  Returns a record or None when the file is not placed."""
+    import importlib.util
+
+    import torch
+
+    path = os.path.join(os.path.dirname(REFERENCE_EINOPS), "score_function.py")
+    if not os.path.exists(path):
+        return None
+    name = "fastmax_reference_score_function"
+    if name in sys.modules:
+        mod = sys.modules[name]
+    else:
+        spec = importlib.util.spec_from_file_location(name, path)
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[name] = mod
+        spec.loader.exec_module(mod)
+    B, H, N, D, order, causal, dtype, scale = WORKLOADS[workload]
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    q, k, v, do = (torch.randn(1, 1, n_sample, D, generator=g) * scale for _ in range(4))
+    if dtype == "bf16":
+        q, k, v, do = (t.bfloat16().float() for t in (q, k, v, do))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    t0 = time.perf_counter()
+    o = mod.fastmax(q, k, v, mask=causal, denum_term=8, normalize=0, p=order)
+    o.backward(do)
+    sec = time.perf_counter() - t0
+    return {"value": (n_sample / H) / sec / 1e6, "unit": "Mtokens/s", "cores": threads, "seconds": sec,
+            "sample": f"the reference's score_function.fastmax (mask={causal}, p={order}, denum_term=8) forward + autograd "
+                      f"backward on 1 of {B * H} heads, {n_sample} of {N} tokens, D={D}; head-tokens / H = metric tokens"}
+
+
 def cpu_baseline_record(workload, n_sample, heads):
     """CPU figure for the JSON line: the reference's einops code when it is present (kind "reference"), with the oracle's
     restatement as a second figure; the restatement alone (kind "port") otherwise."""
@@ -926,12 +1002,56 @@ def measure_cfg2_strong(torch, dist, dev, rank, world, steps=10, warmup=3):
             "heads_per_rank": b * H, "engines": sorted(_lib.profile_collect())}
 
 
+def measure_reference_boundary(torch, dist, dev, rank, world, steps=3, warmup=1):
+    """Config 2's shape through the reference's own boundary, per rank (weak): float32 (b, h, n, d) tensors into
+    `FASTMultiHeadAttention_Function` (the twin of transformer/model.py:14-74: reshape, permute to (n, b*h, d) with
+    copies, `fastmax_cuda.forwardpass` / `backwardpass`, permute back), forward + backward.  float32 puts the call on
+    the CUDA-core engine; the figure says what a caller gets who changes nothing but the import."""
+    from reproducing_fastmax_results_b200.attention import FASTMultiHeadAttention_Function
+
+    B, H, N, D, order, causal, _, scale = WORKLOADS[DEFAULT]
+    gen = torch.Generator(device=dev).manual_seed(99 + rank)
+    q, k, v = ((torch.randn(B, H, N, D, device=dev, generator=gen) * scale).requires_grad_(True) for _ in range(3))
+    do = torch.randn(B, H, N, D, device=dev, generator=gen) * scale
+    noise = torch.zeros(B, H, N, D, device=dev)
+    rpe = torch.zeros(2 * N - 1, D, device=dev)
+    temperature = 8.0 * math.sqrt(D)
+
+    def step():
+        for t in (q, k, v):
+            t.grad = None
+        o = FASTMultiHeadAttention_Function.apply(q, k, v, noise, rpe, causal, 0.0, False, temperature, 1.0, 1.0, 0.5, 1.0, order)
+        o.backward(do)
+
+    for _ in range(warmup):
+        step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        step()
+    e.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(e)], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / steps
+    return {"ms_per_step": ms, "value": world * B * N / (ms * 1e-3) / 1e6, "unit": "Mtokens/s", "scaling": "weak", "dtype": "f32",
+            "api": "FASTMultiHeadAttention_Function.apply + backward: the reference wrapper's permutes and copies around "
+                   "fastmax_cuda.forwardpass / backwardpass (float32 contract, CUDA-core engine)"}
+
+
 def other_workloads(args, torch, dist, dev, rank, world):
     """Bounded extra measurements reported beside the headline (same process group, after its timed region)."""
     out = {}
     legs = [("cfg2_strong", lambda: measure_cfg2_strong(torch, dist, dev, rank, world)),
             ("cfg3", lambda: measure_sequence_sharded("cfg3_f32_causal_p2_B1_H8_N131072_D32", 3, 3, torch, dist, dev, rank, world)),
-            ("cfg5", lambda: measure_cfg5(torch, dist, dev, rank, world))]
+            ("cfg5", lambda: measure_cfg5(torch, dist, dev, rank, world)),
+            ("cfg2_reference_boundary_f32", lambda: measure_reference_boundary(torch, dist, dev, rank, world))]
     for name, fn in legs:
         t0 = time.perf_counter()
         try:
@@ -1169,6 +1289,14 @@ def main():
                 cpu["config1"] = config1_record(torch, dev)
             except Exception as e:   # reported, never fatal for the headline line
                 cpu["config1"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            try:
+                cpu["config4"] = config4_record(torch, dev)
+            except Exception as e:
+                cpu["config4"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            try:
+                cpu["score_function"] = score_function_sample(args.workload)
+            except Exception as e:
+                cpu["score_function"] = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     input_mb = 4 * q.numel() * q.element_size() >> 20
     others = None
