@@ -89,16 +89,27 @@ size_t fastmax_state_bytes(const fastmax_problem* pb); /* all batch*heads states
  *       g.ptr = o.ptr + d with the same strides.
  *   state_in  (optional): moments of keys that precede this call's keys (same (b,h) order); causal only.
  *   state_out (optional): state_in + moments of this call's keys.
- *   If o.ptr is NULL only state_out is produced (the "chunk total" a sequence-parallel rank publishes). */
+ *   If o.ptr is NULL only state_out is produced (the "chunk total" a sequence-parallel rank publishes).
+ *   key_moments_out / key_moments_in (optional, both may be NULL): when the CUDA-core engine cuts the keys into
+ *       segments it first sums Phi(K)^T [V | 1] per segment, one pass over k and v.  Those sums depend on k and v only
+ *       (not on state_in), so a caller that comes back with the same k and v -- the forward after a state-only call
+ *       of a sequence-parallel rank, the backward after the forward -- can hand them back and save that pass.
+ *       key_moments_out receives them (fastmax_key_moments_bytes() bytes, float32); key_moments_in must hold what an
+ *       earlier call with the same problem, k and v wrote.  No counterpart in the reference, which has no segments. */
 typedef struct {
   fastmax_tensor q, k, v;
   fastmax_tensor o;
   fastmax_tensor g;
   const float* state_in;
   float* state_out;
+  const float* key_moments_in;
+  float* key_moments_out;
 } fastmax_forward_args;
 
 size_t fastmax_forward_workspace(const fastmax_problem* pb, const fastmax_forward_args* args);
+/* Size of the key_moments arrays for this problem and these arguments, or 0 when this call would neither write nor
+ * read them (one segment per head, no keys, or a call the tensor-memory kernels take). */
+size_t fastmax_key_moments_bytes(const fastmax_problem* pb, const fastmax_forward_args* args);
 int32_t fastmax_forward(const fastmax_problem* pb, const fastmax_forward_args* args,
                         void* workspace, size_t workspace_bytes, void* cuda_stream);
 
@@ -125,13 +136,15 @@ int32_t fastmax_forward_static_scratch(const fastmax_problem* pb, const fastmax_
  *   state_in     : same array the forward call received (moments of earlier keys), or NULL.
  *   dstate_in    : gradient moments sum Phi(q)^T dO' of LATER queries (sequence-parallel), or NULL.
  *   dstate_out   : dstate_in + this call's gradient moments, or NULL.
- *   If dq.ptr, dk.ptr and dv.ptr are all NULL only dstate_out is produced. */
+ *   If dq.ptr, dk.ptr and dv.ptr are all NULL only dstate_out is produced.
+ *   key_moments_in (optional): what the forward call of the same problem, k and v wrote to key_moments_out. */
 typedef struct {
   fastmax_tensor q, k, v, o, g, d_out;
   fastmax_tensor dq, dk, dv;
   const float* state_in;
   const float* dstate_in;
   float* dstate_out;
+  const float* key_moments_in;
 } fastmax_backward_args;
 
 size_t fastmax_backward_workspace(const fastmax_problem* pb, const fastmax_backward_args* args);

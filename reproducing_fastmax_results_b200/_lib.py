@@ -18,7 +18,7 @@ FLAG_SINGLE_STREAM = 2
 
 EXPORTED_SYMBOLS = [
     "fastmax_state_rows", "fastmax_state_ld", "fastmax_state_bytes",
-    "fastmax_forward_workspace", "fastmax_forward",
+    "fastmax_forward_workspace", "fastmax_forward", "fastmax_key_moments_bytes",
     "fastmax_static_scratch_bytes", "fastmax_forward_static_scratch",
     "fastmax_backward_workspace", "fastmax_backward",
     "fastmax_decode_step",
@@ -46,13 +46,25 @@ class Problem(C.Structure):
 
 class ForwardArgs(C.Structure):
     _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("o", Tensor), ("g", Tensor),
-                ("state_in", C.c_void_p), ("state_out", C.c_void_p)]
+                ("state_in", C.c_void_p), ("state_out", C.c_void_p),
+                ("key_moments_in", C.c_void_p), ("key_moments_out", C.c_void_p)]
 
 
 class BackwardArgs(C.Structure):
     _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("o", Tensor), ("g", Tensor), ("d_out", Tensor),
                 ("dq", Tensor), ("dk", Tensor), ("dv", Tensor),
-                ("state_in", C.c_void_p), ("dstate_in", C.c_void_p), ("dstate_out", C.c_void_p)]
+                ("state_in", C.c_void_p), ("dstate_in", C.c_void_p), ("dstate_out", C.c_void_p),
+                ("key_moments_in", C.c_void_p)]
+
+
+class KeyMoments:
+    """Holder of the per-segment key moments of one (k, v) pair (fastmax_forward_args.key_moments_out/in): the first
+    call that is handed the holder fills it, later calls with the same problem, k and v (the forward after a
+    state-only call, the backward after the forward) read it and skip their pass over k and v.  Stays empty for
+    calls that have no such pass (one segment per head, tensor-memory kernels)."""
+
+    def __init__(self):
+        self.buf = None
 
 
 class DecodeArgs(C.Structure):
@@ -87,6 +99,8 @@ def load():
     lib.fastmax_state_bytes.argtypes = [C.POINTER(Problem)]
     lib.fastmax_forward_workspace.restype = C.c_size_t
     lib.fastmax_forward_workspace.argtypes = [C.POINTER(Problem), C.POINTER(ForwardArgs)]
+    lib.fastmax_key_moments_bytes.restype = C.c_size_t
+    lib.fastmax_key_moments_bytes.argtypes = [C.POINTER(Problem), C.POINTER(ForwardArgs)]
     lib.fastmax_forward.restype = C.c_int32
     lib.fastmax_forward.argtypes = [C.POINTER(Problem), C.POINTER(ForwardArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     lib.fastmax_static_scratch_bytes.restype = C.c_size_t
@@ -182,10 +196,26 @@ def _workspace(nbytes, device):
     return ws, C.c_void_p(ptr)
 
 
+def _attach_key_moments(lib, pb, fargs, key_moments, device, sink, allow_fill):
+    """Points sink.key_moments_in at the holder's buffer when it fits this call, or (allow_fill) gives the call a new
+    buffer to fill.  `fargs`: the ForwardArgs that describe the call to fastmax_key_moments_bytes."""
+    import torch
+
+    nbytes = lib.fastmax_key_moments_bytes(C.byref(pb), C.byref(fargs))
+    if nbytes == 0:
+        return
+    if key_moments.buf is not None and key_moments.buf.numel() * 4 == nbytes:
+        sink.key_moments_in = key_moments.buf.data_ptr()
+    elif allow_fill:
+        key_moments.buf = torch.empty(nbytes // 4, dtype=torch.float32, device=device)
+        sink.key_moments_out = key_moments.buf.data_ptr()
+
+
 def forward(q, k, v, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, order=2, state_in=None, want_state=False,
-            want_output=True, flags=0, out=None):
+            want_output=True, flags=0, out=None, key_moments=None):
     """Calls fastmax_forward on (b,h,n,d) CUDA tensors.  Returns (o, g, state_out).  `out`: optional (b,h,n,d) tensor
-    of any strides (unit stride on d) that receives o, e.g. the transposed view of a (b, n, h*d) buffer."""
+    of any strides (unit stride on d) that receives o, e.g. the transposed view of a (b, n, h*d) buffer.
+    `key_moments`: optional KeyMoments holder for this (k, v)."""
     import torch
 
     lib = load()
@@ -205,6 +235,8 @@ def forward(q, k, v, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, order=2, state_in
         sout = torch.empty((q.shape[0], q.shape[1], lib.fastmax_state_rows(pb.d, pb.order), lib.fastmax_state_ld(pb.d)),
                            dtype=torch.float32, device=q.device)
         args.state_out = sout.data_ptr()
+    if key_moments is not None:
+        _attach_key_moments(lib, pb, args, key_moments, q.device, args, True)
     need = lib.fastmax_forward_workspace(C.byref(pb), C.byref(args))
     ws, wptr = _workspace(need, q.device)
     check(lib.fastmax_forward(C.byref(pb), C.byref(args), wptr, need, _stream()), "fastmax_forward")
@@ -228,9 +260,10 @@ def forward_static_scratch(q, k, v, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, or
 
 
 def backward(q, k, v, o, g, d_out, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, order=2, state_in=None, dstate_in=None,
-             want_dstate=False, want_grads=True, flags=0, grads_out=None):
+             want_dstate=False, want_grads=True, flags=0, grads_out=None, key_moments=None):
     """Calls fastmax_backward on (b,h,n,d) CUDA tensors.  Returns (dq, dk, dv, dstate_out).  `grads_out`: optional
-    (dq, dk, dv) tensors of any strides (unit stride on d) that receive the gradients."""
+    (dq, dk, dv) tensors of any strides (unit stride on d) that receive the gradients.  `key_moments`: the holder the
+    forward call of the same q, k, v filled."""
     import torch
 
     lib = load()
@@ -251,6 +284,10 @@ def backward(q, k, v, o, g, d_out, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, ord
         dsout = torch.empty((q.shape[0], q.shape[1], lib.fastmax_state_rows(pb.d, pb.order), lib.fastmax_state_ld(pb.d)),
                             dtype=torch.float32, device=q.device)
         args.dstate_out = dsout.data_ptr()
+    if key_moments is not None and key_moments.buf is not None and want_grads:
+        fargs = ForwardArgs()
+        fargs.q, fargs.k, fargs.v, fargs.o, fargs.g = args.q, args.k, args.v, args.o, args.g
+        _attach_key_moments(lib, pb, fargs, key_moments, q.device, args, False)
     need = lib.fastmax_backward_workspace(C.byref(pb), C.byref(args))
     ws, wptr = _workspace(need, q.device)
     check(lib.fastmax_backward(C.byref(pb), C.byref(args), wptr, need, _stream()), "fastmax_backward")

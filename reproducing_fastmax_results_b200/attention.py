@@ -128,7 +128,10 @@ class FastMax(torch.autograd.Function):
                 raise ValueError("apply_rpe needs rpe_matrix, a (2n-1, d) tensor")
             k_op = ext.key_prologue(k.clone(), inv_t, rpe_matrix)   # k / temperature + rpe rows, on a private copy
             k_scale, inv_t = inv_t, 1.0
-        o, g, _ = ext.forward(q, k_op, v, bool(mask), inv_t, float(a0), float(a1), float(a2), int(p), None, False, True, 0)
+        # the fourth entry: per-segment key moments when the call computed some (long sequences with few heads on the
+        # CUDA-core engine); the backward reads them instead of passing over k and v again
+        o, g, _, kmom = ext.forward(q, k_op, v, bool(mask), inv_t, float(a0), float(a1), float(a2), int(p), None, False, True, 0,
+                                    None, None, True)
         noise = None
         out = o
         if noise_dropout and float(dropout) != 0.0:
@@ -140,6 +143,7 @@ class FastMax(torch.autograd.Function):
         ctx.save_for_backward(q, k_op, v, o, g, *extra, *([noise] if noise is not None else []))
         ctx.cfg = (bool(mask), inv_t, float(a0), float(a1), float(a2), int(p), bool(normalize), float(lim), three_d,
                    k_scale, float(dropout) if noise is not None else 0.0, bool(apply_rpe))
+        ctx.key_moments = kmom   # not an input or output of the function: kept on the context
         return out.squeeze(0) if three_d else out
 
     @staticmethod
@@ -153,7 +157,8 @@ class FastMax(torch.autograd.Function):
             grad_output = grad_output.contiguous()
         if noise_scale != 0.0:     # out = o * (1 + s * noise)  ->  d o = d out * (1 + s * noise)
             grad_output = ext.output_noise(grad_output, ctx.saved_tensors[-1], noise_scale)
-        dq, dk, dv, _ = ext.backward(q, k, v, o, g, grad_output, mask, inv_t, a0, a1, a2, p, None, None, False, True, 0)
+        dq, dk, dv, _ = ext.backward(q, k, v, o, g, grad_output, mask, inv_t, a0, a1, a2, p, None, None, False, True, 0,
+                                     None, ctx.key_moments)
         if k_scale != 1.0:         # the operator saw k / temperature + rpe rows
             dk = ext.key_prologue(dk, k_scale, None)
         if normalize:

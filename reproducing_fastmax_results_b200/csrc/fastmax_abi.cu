@@ -195,9 +195,23 @@ static void fill_coeffs(const fastmax_problem* pb, ScanParams& P) {
 // state (non-causal).  seg buffer: [bh][nseg][n_state].  Returns through P the seg_state pointers.
 //   src MOM_KV: Phi(K)^T [V|1]          (forward direction: exclusive prefix)
 //   src MOM_QG: Phi(Q)^T dO'            (reverse direction: exclusive suffix)
+// raw_in: the per-segment sums of an earlier call with the same x and v (the moment pass is skipped); raw_out: receives them.
 static int build_segment_states(const fastmax_problem* pb, const Plan& pl, int src, const View& x, const View& v,
                                 const float* dop, float* segbuf, int nseg, int cps, int nchunks,
-                                const float* init, float* total_out, int scan_op, cudaStream_t st) {
+                                const float* init, float* total_out, int scan_op, cudaStream_t st,
+                                const float* raw_in = nullptr, float* raw_out = nullptr) {
+  const size_t raw_bytes = (size_t)pl.bh * nseg * pl.n_state * sizeof(float);
+  if (raw_in != nullptr) {
+    FM_CUDA(cudaMemcpyAsync(segbuf, raw_in, raw_bytes, cudaMemcpyDeviceToDevice, st));
+    if (raw_out != nullptr && raw_out != raw_in) FM_CUDA(cudaMemcpyAsync(raw_out, raw_in, raw_bytes, cudaMemcpyDeviceToDevice, st));
+    long long total = (long long)pl.bh * pl.n_state;
+    {
+      LaunchScope ls(KK_STATE_SCAN, st);
+      state_scan_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(segbuf, nseg, pl.n_state, init, total_out, scan_op, total);
+    }
+    FM_CUDA(cudaGetLastError());
+    return FASTMAX_OK;
+  }
   MomentParams M{};
   M.x = x;
   M.v = v;
@@ -220,6 +234,7 @@ static int build_segment_states(const fastmax_problem* pb, const Plan& pl, int s
   M.npair_slices = pl.npair_slices;
   dim3 grid(pl.nslices, nseg, pl.bh);
   FM_CUDA(launch_moments(pb->d, pb->dtype, src, M, grid, st));
+  if (raw_out != nullptr) FM_CUDA(cudaMemcpyAsync(raw_out, segbuf, raw_bytes, cudaMemcpyDeviceToDevice, st));
   long long total = (long long)pl.bh * pl.n_state;
   int threads = 256;
   long long blocks = (total + threads - 1) / threads;
@@ -429,6 +444,15 @@ size_t fastmax_forward_workspace(const fastmax_problem* pb, const fastmax_forwar
   return (L.total > tc ? L.total : tc) + 256;
 }
 
+size_t fastmax_key_moments_bytes(const fastmax_problem* pb, const fastmax_forward_args* args) {
+  Plan pl;
+  if (!args || make_plan(pb, pl) != FASTMAX_OK || pb->nk == 0) return 0;
+  if (tc_forward_workspace(pb, args) != 0) return 0;   // the tensor-memory kernels take this call: no segment sums
+  FwdLayout L;
+  if (!fwd_layout(pb, args, pl, L)) return 0;
+  return (size_t)pl.bh * pl.k_nseg * pl.n_state * sizeof(float);
+}
+
 int32_t fastmax_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* ws, size_t ws_bytes,
                         void* stream) {
   Plan pl;
@@ -474,7 +498,7 @@ int32_t fastmax_forward(const fastmax_problem* pb, const fastmax_forward_args* a
       }
     } else {
       rc = build_segment_states(pb, pl, MOM_KV, k, v, nullptr, seg, pl.k_nseg, pl.k_cps, pl.k_chunks, a->state_in,
-                                a->state_out, pb->causal ? SCAN_PREFIX : SCAN_TOTAL, st);
+                                a->state_out, pb->causal ? SCAN_PREFIX : SCAN_TOTAL, st, a->key_moments_in, a->key_moments_out);
       if (rc) return rc;
     }
   }
@@ -628,7 +652,7 @@ int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args*
       FM_CUDA(cudaMemsetAsync(segS, 0, (size_t)pl.bh * pl.k_nseg * pl.n_state * sizeof(float), st));
     } else {
       rc = build_segment_states(pb, pl, MOM_KV, k, v, nullptr, segS, pl.k_nseg, pl.k_cps, pl.k_chunks, a->state_in,
-                                nullptr, pb->causal ? SCAN_PREFIX : SCAN_TOTAL, st);
+                                nullptr, pb->causal ? SCAN_PREFIX : SCAN_TOTAL, st, a->key_moments_in);
       if (rc) return rc;
     }
   }

@@ -142,10 +142,13 @@ fastmax_problem make_problem(const torch::Tensor& q, const torch::Tensor& k, boo
   return pb;
 }
 
-// returns (o, g, state_out or empty)
+// returns (o, g, state_out or empty); with key_moments given or want_key_moments set a fourth entry follows: the
+// per-segment key moments this call read or wrote (undefined when the call has none), to be handed to the next call
+// with the same k and v (fastmax_forward_args.key_moments_in / _out)
 std::vector<torch::Tensor> forward(torch::Tensor q, torch::Tensor k, torch::Tensor v, bool causal, double inv_temp,
                                    double a0, double a1, double a2, int64_t p, c10::optional<torch::Tensor> state_in,
-                                   bool want_state, bool want_output, int64_t flags, c10::optional<torch::Tensor> out) {
+                                   bool want_state, bool want_output, int64_t flags, c10::optional<torch::Tensor> out,
+                                   c10::optional<torch::Tensor> key_moments, bool want_key_moments) {
   CHECK_CUDA(q); CHECK_CUDA(k); CHECK_CUDA(v);
   TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "q, k, v must be (b, h, n, d)");
   TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(), "q, k, v dtypes differ");
@@ -181,9 +184,25 @@ std::vector<torch::Tensor> forward(torch::Tensor q, torch::Tensor k, torch::Tens
                         q.options().dtype(torch::kFloat32));
     a.state_out = (float*)sout.data_ptr();
   }
+  torch::Tensor km;
+  const bool km_given = key_moments.has_value() && key_moments->defined();
+  if (km_given || want_key_moments) {
+    const size_t nbytes = fastmax_key_moments_bytes(&pb, &a);
+    if (nbytes != 0) {
+      if (km_given && key_moments->is_contiguous() && key_moments->scalar_type() == torch::kFloat32 &&
+          (size_t)key_moments->numel() * 4 == nbytes) {
+        km = *key_moments;
+        a.key_moments_in = (const float*)km.data_ptr();
+      } else {
+        km = torch::empty({(int64_t)(nbytes / 4)}, q.options().dtype(torch::kFloat32));
+        a.key_moments_out = (float*)km.data_ptr();
+      }
+    }
+  }
   size_t need = fastmax_forward_workspace(&pb, &a);
   auto ws = workspace(need, q);
   check_status(fastmax_forward(&pb, &a, aligned(ws), need, stream), "fastmax forward");
+  if (km_given || want_key_moments) return {o, g, sout, km};
   return {o, g, sout};
 }
 
@@ -192,7 +211,8 @@ std::vector<torch::Tensor> backward(torch::Tensor q, torch::Tensor k, torch::Ten
                                     torch::Tensor d_out, bool causal, double inv_temp, double a0, double a1, double a2,
                                     int64_t p, c10::optional<torch::Tensor> state_in,
                                     c10::optional<torch::Tensor> dstate_in, bool want_dstate, bool want_grads,
-                                    int64_t flags, c10::optional<std::vector<torch::Tensor>> grads_out) {
+                                    int64_t flags, c10::optional<std::vector<torch::Tensor>> grads_out,
+                                    c10::optional<torch::Tensor> key_moments) {
   CHECK_CUDA(q); CHECK_CUDA(k); CHECK_CUDA(v); CHECK_CUDA(o); CHECK_CUDA(g); CHECK_CUDA(d_out);
   TORCH_CHECK(g.scalar_type() == torch::kFloat32, "g must be float32");
   const c10::cuda::CUDAGuard guard(q.device());
@@ -224,6 +244,15 @@ std::vector<torch::Tensor> backward(torch::Tensor q, torch::Tensor k, torch::Ten
     dsout = torch::empty({q.size(0), q.size(1), fastmax_state_rows(pb.d, pb.order), fastmax_state_ld(pb.d)},
                          q.options().dtype(torch::kFloat32));
     a.dstate_out = (float*)dsout.data_ptr();
+  }
+  if (want_grads && key_moments.has_value() && key_moments->defined()) {
+    // what the forward call of the same q, k, v wrote: valid when it has the size this problem's segments give
+    fastmax_forward_args fa{};
+    fa.q = a.q; fa.k = a.k; fa.v = a.v; fa.o = a.o; fa.g = a.g;
+    const size_t nbytes = fastmax_key_moments_bytes(&pb, &fa);
+    if (nbytes != 0 && key_moments->is_contiguous() && key_moments->scalar_type() == torch::kFloat32 &&
+        (size_t)key_moments->numel() * 4 == nbytes)
+      a.key_moments_in = (const float*)key_moments->data_ptr();
   }
   size_t need = fastmax_backward_workspace(&pb, &a);
   auto ws = workspace(need, q);
@@ -302,12 +331,13 @@ PYBIND11_MODULE(fastmax_cuda, m) {
   m.def("forward", &forward, "strided (b,h,n,d) forward: returns [o, g, state_out]", py::arg("q"), py::arg("k"), py::arg("v"),
         py::arg("causal"), py::arg("inv_temp"), py::arg("a0"), py::arg("a1"), py::arg("a2"), py::arg("p"),
         py::arg("state_in") = py::none(), py::arg("want_state") = false, py::arg("want_output") = true,
-        py::arg("flags") = 0, py::arg("out") = py::none(), release());
+        py::arg("flags") = 0, py::arg("out") = py::none(), py::arg("key_moments") = py::none(),
+        py::arg("want_key_moments") = false, release());
   m.def("backward", &backward, "strided (b,h,n,d) backward: returns [dq, dk, dv, dstate_out]", py::arg("q"), py::arg("k"),
         py::arg("v"), py::arg("o"), py::arg("g"), py::arg("d_out"), py::arg("causal"), py::arg("inv_temp"), py::arg("a0"),
         py::arg("a1"), py::arg("a2"), py::arg("p"), py::arg("state_in") = py::none(), py::arg("dstate_in") = py::none(),
         py::arg("want_dstate") = false, py::arg("want_grads") = true, py::arg("flags") = 0,
-        py::arg("grads_out") = py::none(), release());
+        py::arg("grads_out") = py::none(), py::arg("key_moments") = py::none(), release());
   m.def("normalize_forward", &normalize_forward, "q/k normalisation: returns [y, stats]", release());
   m.def("normalize_backward", &normalize_backward, "gradient of the q/k normalisation", release());
   m.def("key_prologue", &key_prologue, "k <- k * inv_temp + rpe rows, in place", py::arg("k"), py::arg("inv_temp"),

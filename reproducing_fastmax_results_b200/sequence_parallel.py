@@ -53,8 +53,19 @@ def exclusive_suffix(local: torch.Tensor, group=None) -> torch.Tensor:
     return out
 
 
+class KeyMoments:
+    """Per-segment key moments of one piece's k and v (see fastmax_forward_args.key_moments_out): written by the first
+    call that gets the holder, read by the later calls on the same k and v, which then skip their pass over them."""
+
+    def __init__(self):
+        self.buf = None
+
+
 class CudaEngine:
-    """The library's kernels through the `fastmax_cuda` extension ((b, h, n, d) CUDA tensors)."""
+    """The library's kernels through the `fastmax_cuda` extension ((b, h, n, d) CUDA tensors).  `moments`: a KeyMoments
+    holder that belongs to the k and v of the call; sequence_parallel.forward / backward create one per piece."""
+
+    reuses_key_moments = True
 
     def __init__(self, inv_temp, a0=1.0, a1=1.0, a2=0.5, p=2):
         from . import load_extension
@@ -62,41 +73,60 @@ class CudaEngine:
         self.ext = load_extension()
         self.cfg = (float(inv_temp), float(a0), float(a1), float(a2), int(p))
 
-    def key_state(self, k, v):
+    def key_state(self, k, v, moments=None):
         it, a0, a1, a2, p = self.cfg
-        return self.ext.forward(k, k, v, True, it, a0, a1, a2, p, None, True, False, 0)[2]
+        if moments is None:
+            return self.ext.forward(k, k, v, True, it, a0, a1, a2, p, None, True, False, 0)[2]
+        res = self.ext.forward(k, k, v, True, it, a0, a1, a2, p, None, True, False, 0, None, moments.buf, True)
+        moments.buf = res[3]
+        return res[2]
 
-    def forward(self, q, k, v, state_in):
+    def forward(self, q, k, v, state_in, moments=None):
         it, a0, a1, a2, p = self.cfg
-        o, g, _ = self.ext.forward(q, k, v, True, it, a0, a1, a2, p, state_in, False, True, 0)
-        return o, g
+        if moments is None:
+            o, g, _ = self.ext.forward(q, k, v, True, it, a0, a1, a2, p, state_in, False, True, 0)
+            return o, g
+        res = self.ext.forward(q, k, v, True, it, a0, a1, a2, p, state_in, False, True, 0, None, moments.buf, True)
+        moments.buf = res[3]
+        return res[0], res[1]
 
     def grad_state(self, q, k, v, o, g, do, state_in):
         it, a0, a1, a2, p = self.cfg
         return self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, None, True, False, 0)[3]
 
-    def backward(self, q, k, v, o, g, do, state_in, dstate_in):
+    def backward(self, q, k, v, o, g, do, state_in, dstate_in, moments=None):
         it, a0, a1, a2, p = self.cfg
-        dq, dk, dv, _ = self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, dstate_in, False, True, 0)
+        dq, dk, dv, _ = self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, dstate_in, False, True, 0,
+                                          None, None if moments is None else moments.buf)
         return dq, dk, dv
 
 
+def _moments_kw(engine, carry=None):
+    if not getattr(engine, "reuses_key_moments", False):
+        return {}
+    return {"moments": KeyMoments() if carry is None else carry[1]}
+
+
 def forward(engine, q, k, v, group=None):
-    """Returns (o, g, prefix_state) for this rank's piece (prefix_state is None when there is one rank)."""
+    """Returns (o, g, carry) for this rank's piece; hand `carry` (the prefix state of the earlier ranks, None when there
+    is one rank, and the piece's key moments) to backward()."""
+    kw = _moments_kw(engine)
     if _world(group)[0] == 1:
-        o, g = engine.forward(q, k, v, None)
-        return o, g, None
-    prefix = exclusive_prefix(engine.key_state(k, v), group)
-    o, g = engine.forward(q, k, v, prefix)
-    return o, g, prefix
+        o, g = engine.forward(q, k, v, None, **kw)
+        return o, g, (None, kw.get("moments"))
+    prefix = exclusive_prefix(engine.key_state(k, v, **kw), group)
+    o, g = engine.forward(q, k, v, prefix, **kw)
+    return o, g, (prefix, kw.get("moments"))
 
 
-def backward(engine, q, k, v, o, g, do, prefix, group=None):
-    """Returns (dq, dk, dv) for this rank's piece; `prefix` is what forward() returned."""
+def backward(engine, q, k, v, o, g, do, carry, group=None):
+    """Returns (dq, dk, dv) for this rank's piece; `carry` is what forward() returned."""
+    prefix = carry[0]
+    kw = _moments_kw(engine, carry)
     if _world(group)[0] == 1:
-        return engine.backward(q, k, v, o, g, do, prefix, None)
+        return engine.backward(q, k, v, o, g, do, prefix, None, **kw)
     suffix = exclusive_suffix(engine.grad_state(q, k, v, o, g, do, prefix), group)
-    return engine.backward(q, k, v, o, g, do, prefix, suffix)
+    return engine.backward(q, k, v, o, g, do, prefix, suffix, **kw)
 
 
 class SequenceParallelFastMax(torch.autograd.Function):
@@ -105,9 +135,9 @@ class SequenceParallelFastMax(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, temperature=1.0, a0=1.0, a1=1.0, a2=0.5, p=2, group=None):
         engine = CudaEngine(1.0 / float(temperature), a0, a1, a2, p)
-        o, g, prefix = forward(engine, q, k, v, group)
+        o, g, (prefix, moments) = forward(engine, q, k, v, group)
         ctx.save_for_backward(q, k, v, o, g, *([] if prefix is None else [prefix]))
-        ctx.engine, ctx.group = engine, group
+        ctx.engine, ctx.group, ctx.moments = engine, group, moments
         return o
 
     @staticmethod
@@ -116,5 +146,5 @@ class SequenceParallelFastMax(torch.autograd.Function):
         prefix = ctx.saved_tensors[5] if len(ctx.saved_tensors) > 5 else None
         if grad_output.stride(-1) != 1:
             grad_output = grad_output.contiguous()
-        dq, dk, dv = backward(ctx.engine, q, k, v, o, g, grad_output, prefix, ctx.group)
+        dq, dk, dv = backward(ctx.engine, q, k, v, o, g, grad_output, (prefix, ctx.moments), ctx.group)
         return dq, dk, dv, None, None, None, None, None, None

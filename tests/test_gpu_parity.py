@@ -277,3 +277,61 @@ def test_no_queries_still_produce_the_key_state_and_zero_key_gradients():
     dq, dk, dv, _ = L.backward(q, k, v, o, g, do, True, poly.inv_temp, order=2)
     torch.cuda.synchronize()
     assert dq.shape[2] == 0 and float(dk.abs().max()) == 0.0 and float(dv.abs().max()) == 0.0
+
+
+def _launches(L, fn):
+    L.profile_collect()
+    L.profile(True)
+    out = fn()
+    torch.cuda.synchronize()
+    L.profile(False)
+    return out, {k: v[1] for k, v in L.profile_collect().items()}
+
+
+@pytest.mark.parametrize("causal,order,D", [(True, 2, 32), (True, 1, 64), (False, 2, 32)])
+def test_key_moments_are_reused_by_later_calls(causal, order, D):
+    """A long sequence with few heads is cut into segments; the per-segment key moments of the first call (a
+    state-only call here, as a sequence-parallel rank makes) are handed to the forward and to the backward, which then
+    skip their pass over k and v.  Same results as the calls that recompute them, one moment launch instead of three."""
+    L = lib()
+    B, H, N = 1, 2, 8192
+    g = torch.Generator(device="cuda").manual_seed(17)
+    q, k, v, do = (torch.randn(B, H, N, D, device="cuda", generator=g) * 0.8 for _ in range(4))
+    it = 1.0 / (2.0 * D ** 0.5)
+    state_in = None
+    if causal:
+        k0, v0 = (torch.randn(B, H, 256, D, device="cuda", generator=g) * 0.8 for _ in range(2))
+        _, _, state_in = L.forward(k0, k0, v0, True, it, order=order, want_state=True, want_output=False)
+
+    def plain():
+        o, gg, _ = L.forward(q, k, v, causal, it, order=order, state_in=state_in)
+        return (o, gg) + tuple(L.backward(q, k, v, o, gg, do, causal, it, order=order, state_in=state_in)[:3])
+
+    def reusing():
+        km = L.KeyMoments()
+        _, _, total = L.forward(k, k, v, causal, it, order=order, want_state=True, want_output=False, key_moments=km)
+        assert km.buf is not None
+        o, gg, _ = L.forward(q, k, v, causal, it, order=order, state_in=state_in, key_moments=km)
+        return (o, gg) + tuple(L.backward(q, k, v, o, gg, do, causal, it, order=order, state_in=state_in, key_moments=km)[:3]) + (total,)
+
+    ref, n_plain = _launches(L, plain)
+    got, n_reuse = _launches(L, reusing)
+    assert n_plain["moments_kv"] == 2 and n_reuse["moments_kv"] == 1, (n_plain, n_reuse)
+    for a, b in zip(got[:5], ref):
+        assert orc.max_norm_err(host(a), host(b)) < 2e-6
+    _, _, total_ref = L.forward(k, k, v, causal, it, order=order, want_state=True, want_output=False)
+    assert orc.max_norm_err(host(got[5]), host(total_ref)) < 2e-6
+
+
+def test_key_moments_holder_stays_empty_without_segments():
+    """One segment per head (many heads) or a call the tensor-memory kernels take: nothing to reuse, nothing allocated."""
+    L = lib()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for dtype, shape in ((torch.float32, (4, 40, 256, 32)), (torch.bfloat16, (2, 16, 512, 64))):
+        q, k, v = (torch.randn(*shape, device="cuda", generator=g).to(dtype) for _ in range(3))
+        km = L.KeyMoments()
+        o, gg, _ = L.forward(q, k, v, True, 0.1, order=2, key_moments=km)
+        assert km.buf is None
+        L.backward(q, k, v, o, gg, q, True, 0.1, order=2, key_moments=km)
+    torch.cuda.synchronize()
+    assert L.load().fastmax_check_status() == 0

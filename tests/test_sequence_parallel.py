@@ -116,14 +116,15 @@ def test_cuda_engine_pieces_match_whole_sequence(D, dtype, pieces):
     bounds = [0] + [128 * (i + 1) - 17 * i for i in range(pieces - 1)] + [N]
     sl = [slice(bounds[i], bounds[i + 1]) for i in range(pieces)]
     cut = lambda t, s: t[:, :, s].contiguous()
-    totals = [eng.key_state(cut(k, s), cut(v, s)) for s in sl]
+    kms = [sp.KeyMoments() for _ in sl]   # one holder per piece: its key moments go from call to call
+    totals = [eng.key_state(cut(k, s), cut(v, s), moments=kms[i]) for i, s in enumerate(sl)]
     prefixes = [sum(totals[:i], torch.zeros_like(totals[0])) for i in range(pieces)]
-    outs = [eng.forward(cut(q, s), cut(k, s), cut(v, s), prefixes[i]) for i, s in enumerate(sl)]
+    outs = [eng.forward(cut(q, s), cut(k, s), cut(v, s), prefixes[i], moments=kms[i]) for i, s in enumerate(sl)]
     gtot = [eng.grad_state(cut(q, s), cut(k, s), cut(v, s), outs[i][0], outs[i][1], cut(do, s), prefixes[i])
             for i, s in enumerate(sl)]
     suffixes = [sum(gtot[i + 1:], torch.zeros_like(gtot[0])) for i in range(pieces)]
-    grads = [eng.backward(cut(q, s), cut(k, s), cut(v, s), outs[i][0], outs[i][1], cut(do, s), prefixes[i], suffixes[i])
-             for i, s in enumerate(sl)]
+    grads = [eng.backward(cut(q, s), cut(k, s), cut(v, s), outs[i][0], outs[i][1], cut(do, s), prefixes[i], suffixes[i],
+                          moments=kms[i]) for i, s in enumerate(sl)]
     torch.cuda.synchronize()
     _lib.profile(False)
     kinds = set(_lib.profile_collect())
