@@ -137,7 +137,10 @@ int32_t fastmax_forward_static_scratch(const fastmax_problem* pb, const fastmax_
  *   dstate_in    : gradient moments sum Phi(q)^T dO' of LATER queries (sequence-parallel), or NULL.
  *   dstate_out   : dstate_in + this call's gradient moments, or NULL.
  *   If dq.ptr, dk.ptr and dv.ptr are all NULL only dstate_out is produced.
- *   key_moments_in (optional): what the forward call of the same problem, k and v wrote to key_moments_out. */
+ *   key_moments_in (optional): what the forward call of the same problem, k and v wrote to key_moments_out.
+ *   grad_moments_out / grad_moments_in (optional): the same for the per-segment sums Phi(Q)^T dO' of this call's
+ *       q, o, g and d_out: the state-only call of a sequence-parallel rank writes them, its gradient call reads them
+ *       (fastmax_grad_moments_bytes() bytes, float32). */
 typedef struct {
   fastmax_tensor q, k, v, o, g, d_out;
   fastmax_tensor dq, dk, dv;
@@ -145,9 +148,13 @@ typedef struct {
   const float* dstate_in;
   float* dstate_out;
   const float* key_moments_in;
+  const float* grad_moments_in;
+  float* grad_moments_out;
 } fastmax_backward_args;
 
 size_t fastmax_backward_workspace(const fastmax_problem* pb, const fastmax_backward_args* args);
+/* Size of the grad_moments arrays, or 0 when this call would neither write nor read them. */
+size_t fastmax_grad_moments_bytes(const fastmax_problem* pb, const fastmax_backward_args* args);
 int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args* args,
                          void* workspace, size_t workspace_bytes, void* cuda_stream);
 

@@ -20,7 +20,7 @@ EXPORTED_SYMBOLS = [
     "fastmax_state_rows", "fastmax_state_ld", "fastmax_state_bytes",
     "fastmax_forward_workspace", "fastmax_forward", "fastmax_key_moments_bytes",
     "fastmax_static_scratch_bytes", "fastmax_forward_static_scratch",
-    "fastmax_backward_workspace", "fastmax_backward",
+    "fastmax_backward_workspace", "fastmax_backward", "fastmax_grad_moments_bytes",
     "fastmax_decode_step",
     "fastmax_normalize_forward", "fastmax_normalize_backward",
     "fastmax_key_prologue", "fastmax_output_noise",
@@ -54,7 +54,7 @@ class BackwardArgs(C.Structure):
     _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("o", Tensor), ("g", Tensor), ("d_out", Tensor),
                 ("dq", Tensor), ("dk", Tensor), ("dv", Tensor),
                 ("state_in", C.c_void_p), ("dstate_in", C.c_void_p), ("dstate_out", C.c_void_p),
-                ("key_moments_in", C.c_void_p)]
+                ("key_moments_in", C.c_void_p), ("grad_moments_in", C.c_void_p), ("grad_moments_out", C.c_void_p)]
 
 
 class KeyMoments:
@@ -65,6 +65,7 @@ class KeyMoments:
 
     def __init__(self):
         self.buf = None
+        self.grad_buf = None   # the same for the gradient moments Phi(Q)^T dO' (fastmax_backward_args.grad_moments_*)
 
 
 class DecodeArgs(C.Structure):
@@ -108,6 +109,8 @@ def load():
     lib.fastmax_forward_static_scratch.argtypes = [C.POINTER(Problem), C.POINTER(ForwardArgs), C.c_void_p]
     lib.fastmax_backward_workspace.restype = C.c_size_t
     lib.fastmax_backward_workspace.argtypes = [C.POINTER(Problem), C.POINTER(BackwardArgs)]
+    lib.fastmax_grad_moments_bytes.restype = C.c_size_t
+    lib.fastmax_grad_moments_bytes.argtypes = [C.POINTER(Problem), C.POINTER(BackwardArgs)]
     lib.fastmax_backward.restype = C.c_int32
     lib.fastmax_backward.argtypes = [C.POINTER(Problem), C.POINTER(BackwardArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     lib.fastmax_decode_step.restype = C.c_int32
@@ -288,6 +291,14 @@ def backward(q, k, v, o, g, d_out, causal, inv_temp, a0=1.0, a1=1.0, a2=0.5, ord
         fargs = ForwardArgs()
         fargs.q, fargs.k, fargs.v, fargs.o, fargs.g = args.q, args.k, args.v, args.o, args.g
         _attach_key_moments(lib, pb, fargs, key_moments, q.device, args, False)
+    if key_moments is not None:
+        nbytes = lib.fastmax_grad_moments_bytes(C.byref(pb), C.byref(args))
+        if nbytes:
+            if key_moments.grad_buf is not None and key_moments.grad_buf.numel() * 4 == nbytes:
+                args.grad_moments_in = key_moments.grad_buf.data_ptr()
+            else:
+                key_moments.grad_buf = torch.empty(nbytes // 4, dtype=torch.float32, device=q.device)
+                args.grad_moments_out = key_moments.grad_buf.data_ptr()
     need = lib.fastmax_backward_workspace(C.byref(pb), C.byref(args))
     ws, wptr = _workspace(need, q.device)
     check(lib.fastmax_backward(C.byref(pb), C.byref(args), wptr, need, _stream()), "fastmax_backward")

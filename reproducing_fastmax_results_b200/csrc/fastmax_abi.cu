@@ -562,6 +562,18 @@ size_t fastmax_backward_workspace(const fastmax_problem* pb, const fastmax_backw
   return (L.total > tc ? L.total : tc) + 256;
 }
 
+size_t fastmax_grad_moments_bytes(const fastmax_problem* pb, const fastmax_backward_args* args) {
+  Plan pl;
+  if (!args || make_plan(pb, pl, true) != FASTMAX_OK) return 0;
+  if (tc_backward_workspace(pb, args) != 0) return 0;   // the tensor-memory kernels take this call: no segment sums
+  BwdLayout L;
+  bwd_layout(pb, args, pl, L);
+  const int nsegD = pb->causal ? pl.k_nseg : pl.q_nseg;
+  const int chunksD = pb->causal ? pl.k_chunks : pl.q_chunks;
+  if (!L.need_segD || chunksD == 0) return 0;
+  return (size_t)pl.bh * nsegD * pl.n_state * sizeof(float);
+}
+
 int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void* ws, size_t ws_bytes,
                          void* stream) {
   Plan pl;
@@ -640,7 +652,7 @@ int32_t fastmax_backward(const fastmax_problem* pb, const fastmax_backward_args*
       FM_CUDA(cudaMemsetAsync(segD, 0, (size_t)pl.bh * nsegD * pl.n_state * sizeof(float), st));
     } else {
       rc = build_segment_states(pb, pl, MOM_QG, q, v, dop, segD, nsegD, cpsD, chunksD, a->dstate_in, a->dstate_out,
-                                pb->causal ? SCAN_SUFFIX : SCAN_TOTAL, st);
+                                pb->causal ? SCAN_SUFFIX : SCAN_TOTAL, st, a->grad_moments_in, a->grad_moments_out);
       if (rc) return rc;
     }
   }

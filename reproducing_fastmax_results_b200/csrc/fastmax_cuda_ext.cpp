@@ -212,7 +212,8 @@ std::vector<torch::Tensor> backward(torch::Tensor q, torch::Tensor k, torch::Ten
                                     int64_t p, c10::optional<torch::Tensor> state_in,
                                     c10::optional<torch::Tensor> dstate_in, bool want_dstate, bool want_grads,
                                     int64_t flags, c10::optional<std::vector<torch::Tensor>> grads_out,
-                                    c10::optional<torch::Tensor> key_moments) {
+                                    c10::optional<torch::Tensor> key_moments, c10::optional<torch::Tensor> grad_moments,
+                                    bool want_grad_moments) {
   CHECK_CUDA(q); CHECK_CUDA(k); CHECK_CUDA(v); CHECK_CUDA(o); CHECK_CUDA(g); CHECK_CUDA(d_out);
   TORCH_CHECK(g.scalar_type() == torch::kFloat32, "g must be float32");
   const c10::cuda::CUDAGuard guard(q.device());
@@ -254,9 +255,26 @@ std::vector<torch::Tensor> backward(torch::Tensor q, torch::Tensor k, torch::Ten
         (size_t)key_moments->numel() * 4 == nbytes)
       a.key_moments_in = (const float*)key_moments->data_ptr();
   }
+  // the per-segment gradient moments this call reads or writes (fifth entry of the result when asked for)
+  torch::Tensor gm;
+  const bool gm_given = grad_moments.has_value() && grad_moments->defined();
+  if (gm_given || want_grad_moments) {
+    const size_t nbytes = fastmax_grad_moments_bytes(&pb, &a);
+    if (nbytes != 0) {
+      if (gm_given && grad_moments->is_contiguous() && grad_moments->scalar_type() == torch::kFloat32 &&
+          (size_t)grad_moments->numel() * 4 == nbytes) {
+        gm = *grad_moments;
+        a.grad_moments_in = (const float*)gm.data_ptr();
+      } else {
+        gm = torch::empty({(int64_t)(nbytes / 4)}, q.options().dtype(torch::kFloat32));
+        a.grad_moments_out = (float*)gm.data_ptr();
+      }
+    }
+  }
   size_t need = fastmax_backward_workspace(&pb, &a);
   auto ws = workspace(need, q);
   check_status(fastmax_backward(&pb, &a, aligned(ws), need, stream), "fastmax backward");
+  if (gm_given || want_grad_moments) return {dq, dk, dv, dsout, gm};
   return {dq, dk, dv, dsout};
 }
 
@@ -337,7 +355,8 @@ PYBIND11_MODULE(fastmax_cuda, m) {
         py::arg("v"), py::arg("o"), py::arg("g"), py::arg("d_out"), py::arg("causal"), py::arg("inv_temp"), py::arg("a0"),
         py::arg("a1"), py::arg("a2"), py::arg("p"), py::arg("state_in") = py::none(), py::arg("dstate_in") = py::none(),
         py::arg("want_dstate") = false, py::arg("want_grads") = true, py::arg("flags") = 0,
-        py::arg("grads_out") = py::none(), py::arg("key_moments") = py::none(), release());
+        py::arg("grads_out") = py::none(), py::arg("key_moments") = py::none(), py::arg("grad_moments") = py::none(),
+        py::arg("want_grad_moments") = false, release());
   m.def("normalize_forward", &normalize_forward, "q/k normalisation: returns [y, stats]", release());
   m.def("normalize_backward", &normalize_backward, "gradient of the q/k normalisation", release());
   m.def("key_prologue", &key_prologue, "k <- k * inv_temp + rpe rows, in place", py::arg("k"), py::arg("inv_temp"),

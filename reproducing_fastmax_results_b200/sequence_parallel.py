@@ -59,6 +59,7 @@ class KeyMoments:
 
     def __init__(self):
         self.buf = None
+        self.grad_buf = None   # the same for the gradient moments of the piece's q, o, g and upstream gradient
 
 
 class CudaEngine:
@@ -90,15 +91,20 @@ class CudaEngine:
         moments.buf = res[3]
         return res[0], res[1]
 
-    def grad_state(self, q, k, v, o, g, do, state_in):
+    def grad_state(self, q, k, v, o, g, do, state_in, moments=None):
         it, a0, a1, a2, p = self.cfg
-        return self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, None, True, False, 0)[3]
+        if moments is None:
+            return self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, None, True, False, 0)[3]
+        res = self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, None, True, False, 0, None, None,
+                                moments.grad_buf, True)
+        moments.grad_buf = res[4]
+        return res[3]
 
     def backward(self, q, k, v, o, g, do, state_in, dstate_in, moments=None):
         it, a0, a1, a2, p = self.cfg
-        dq, dk, dv, _ = self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, dstate_in, False, True, 0,
-                                          None, None if moments is None else moments.buf)
-        return dq, dk, dv
+        km, gm = (None, None) if moments is None else (moments.buf, moments.grad_buf)
+        return tuple(self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, dstate_in, False, True, 0,
+                                       None, km, gm, False)[:3])
 
 
 def _moments_kw(engine, carry=None):
@@ -125,7 +131,7 @@ def backward(engine, q, k, v, o, g, do, carry, group=None):
     kw = _moments_kw(engine, carry)
     if _world(group)[0] == 1:
         return engine.backward(q, k, v, o, g, do, prefix, None, **kw)
-    suffix = exclusive_suffix(engine.grad_state(q, k, v, o, g, do, prefix), group)
+    suffix = exclusive_suffix(engine.grad_state(q, k, v, o, g, do, prefix, **kw), group)
     return engine.backward(q, k, v, o, g, do, prefix, suffix, **kw)
 
 

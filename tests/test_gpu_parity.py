@@ -305,22 +305,28 @@ def test_key_moments_are_reused_by_later_calls(causal, order, D):
 
     def plain():
         o, gg, _ = L.forward(q, k, v, causal, it, order=order, state_in=state_in)
-        return (o, gg) + tuple(L.backward(q, k, v, o, gg, do, causal, it, order=order, state_in=state_in)[:3])
+        dtotal = L.backward(q, k, v, o, gg, do, causal, it, order=order, state_in=state_in, want_dstate=True, want_grads=False)[3]
+        return (o, gg) + tuple(L.backward(q, k, v, o, gg, do, causal, it, order=order, state_in=state_in)[:3]) + (dtotal,)
 
     def reusing():
         km = L.KeyMoments()
         _, _, total = L.forward(k, k, v, causal, it, order=order, want_state=True, want_output=False, key_moments=km)
         assert km.buf is not None
         o, gg, _ = L.forward(q, k, v, causal, it, order=order, state_in=state_in, key_moments=km)
-        return (o, gg) + tuple(L.backward(q, k, v, o, gg, do, causal, it, order=order, state_in=state_in, key_moments=km)[:3]) + (total,)
+        dtotal = L.backward(q, k, v, o, gg, do, causal, it, order=order, state_in=state_in, want_dstate=True, want_grads=False,
+                            key_moments=km)[3]
+        assert km.grad_buf is not None
+        grads = L.backward(q, k, v, o, gg, do, causal, it, order=order, state_in=state_in, key_moments=km)[:3]
+        return (o, gg) + tuple(grads) + (dtotal, total)
 
     ref, n_plain = _launches(L, plain)
     got, n_reuse = _launches(L, reusing)
     assert n_plain["moments_kv"] == 2 and n_reuse["moments_kv"] == 1, (n_plain, n_reuse)
-    for a, b in zip(got[:5], ref):
+    assert n_plain["moments_qg"] == 2 and n_reuse["moments_qg"] == 1, (n_plain, n_reuse)
+    for a, b in zip(got[:6], ref):
         assert orc.max_norm_err(host(a), host(b)) < 2e-6
     _, _, total_ref = L.forward(k, k, v, causal, it, order=order, want_state=True, want_output=False)
-    assert orc.max_norm_err(host(got[5]), host(total_ref)) < 2e-6
+    assert orc.max_norm_err(host(got[6]), host(total_ref)) < 2e-6
 
 
 def test_key_moments_holder_stays_empty_without_segments():

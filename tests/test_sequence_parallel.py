@@ -120,7 +120,7 @@ def test_cuda_engine_pieces_match_whole_sequence(D, dtype, pieces):
     totals = [eng.key_state(cut(k, s), cut(v, s), moments=kms[i]) for i, s in enumerate(sl)]
     prefixes = [sum(totals[:i], torch.zeros_like(totals[0])) for i in range(pieces)]
     outs = [eng.forward(cut(q, s), cut(k, s), cut(v, s), prefixes[i], moments=kms[i]) for i, s in enumerate(sl)]
-    gtot = [eng.grad_state(cut(q, s), cut(k, s), cut(v, s), outs[i][0], outs[i][1], cut(do, s), prefixes[i])
+    gtot = [eng.grad_state(cut(q, s), cut(k, s), cut(v, s), outs[i][0], outs[i][1], cut(do, s), prefixes[i], moments=kms[i])
             for i, s in enumerate(sl)]
     suffixes = [sum(gtot[i + 1:], torch.zeros_like(gtot[0])) for i in range(pieces)]
     grads = [eng.backward(cut(q, s), cut(k, s), cut(v, s), outs[i][0], outs[i][1], cut(do, s), prefixes[i], suffixes[i],
