@@ -131,3 +131,33 @@ def test_operators_follow_torch_deterministic_algorithms_setting():
         _alert_not_deterministic("FastMax")   # silent
     finally:
         torch.use_deterministic_algorithms(was, warn_only=warn_only)
+
+
+def test_ctypes_structures_match_the_c_header(tmp_path):
+    """The header compiles as plain C, and the ctypes mirrors in _lib.py have the sizes and field offsets the C
+    compiler gives the structures (a field added on one side only would shift everything after it)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "abi.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "fastmax_b200.h"\n'
+        "int main(void) {\n"
+        '  printf("%zu %zu %zu %zu %zu ", sizeof(fastmax_tensor), sizeof(fastmax_problem), sizeof(fastmax_forward_args),\n'
+        "         sizeof(fastmax_backward_args), sizeof(fastmax_decode_args));\n"
+        '  printf("%zu %zu %zu %zu %zu %zu\\n", offsetof(fastmax_forward_args, state_in), offsetof(fastmax_forward_args, key_moments_out),\n'
+        "         offsetof(fastmax_backward_args, dstate_out), offsetof(fastmax_backward_args, grad_moments_out),\n"
+        "         offsetof(fastmax_problem, inv_temperature), offsetof(fastmax_decode_args, state));\n"
+        "  return 0;\n}\n")
+    exe = tmp_path / "abi"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-I", os.path.join(root, "include"), str(src), "-o", str(exe)], check=True)
+    got = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    want = [C.sizeof(_lib.Tensor), C.sizeof(_lib.Problem), C.sizeof(_lib.ForwardArgs), C.sizeof(_lib.BackwardArgs),
+            C.sizeof(_lib.DecodeArgs), _lib.ForwardArgs.state_in.offset, _lib.ForwardArgs.key_moments_out.offset,
+            _lib.BackwardArgs.dstate_out.offset, _lib.BackwardArgs.grad_moments_out.offset,
+            _lib.Problem.inv_temperature.offset, _lib.DecodeArgs.state.offset]
+    assert got == want
