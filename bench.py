@@ -1126,10 +1126,13 @@ def main():
     lib = _lib.load()
 
     def step():
-        o, g, _ = _lib.forward(q, k, v, causal, inv_temp, order=order, flags=flags)
+        # a fresh holder per step: within the step the backward takes the forward's per-segment key moments (calls that
+        # are cut into segments; the default workload is not), nothing is carried from one step to the next
+        km = _lib.KeyMoments()
+        o, g, _ = _lib.forward(q, k, v, causal, inv_temp, order=order, flags=flags, key_moments=km)
         if args.mode == "fwd":
             return o
-        return _lib.backward(q, k, v, o, g, do, causal, inv_temp, order=order, flags=flags)
+        return _lib.backward(q, k, v, o, g, do, causal, inv_temp, order=order, flags=flags, key_moments=km)
 
     def barrier():
         if dist is not None:

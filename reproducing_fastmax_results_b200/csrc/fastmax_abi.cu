@@ -447,7 +447,8 @@ size_t fastmax_forward_workspace(const fastmax_problem* pb, const fastmax_forwar
 size_t fastmax_key_moments_bytes(const fastmax_problem* pb, const fastmax_forward_args* args) {
   Plan pl;
   if (!args || make_plan(pb, pl) != FASTMAX_OK || pb->nk == 0) return 0;
-  if (tc_forward_workspace(pb, args) != 0) return 0;   // the tensor-memory kernels take this call: no segment sums
+  if (const size_t t = tc_key_moments_bytes(pb, args)) return t;   // a long sequence cut into segments for the tensor-memory kernels
+  if (tc_forward_workspace(pb, args) != 0) return 0;   // the tensor-memory kernels take this call whole: no segment sums
   FwdLayout L;
   if (!fwd_layout(pb, args, pl, L)) return 0;
   return (size_t)pl.bh * pl.k_nseg * pl.n_state * sizeof(float);
@@ -565,7 +566,8 @@ size_t fastmax_backward_workspace(const fastmax_problem* pb, const fastmax_backw
 size_t fastmax_grad_moments_bytes(const fastmax_problem* pb, const fastmax_backward_args* args) {
   Plan pl;
   if (!args || make_plan(pb, pl, true) != FASTMAX_OK) return 0;
-  if (tc_backward_workspace(pb, args) != 0) return 0;   // the tensor-memory kernels take this call: no segment sums
+  if (const size_t t = tc_grad_moments_bytes(pb, args)) return t;
+  if (tc_backward_workspace(pb, args) != 0) return 0;   // the tensor-memory kernels take this call whole: no segment sums
   BwdLayout L;
   bwd_layout(pb, args, pl, L);
   const int nsegD = pb->causal ? pl.k_nseg : pl.q_nseg;

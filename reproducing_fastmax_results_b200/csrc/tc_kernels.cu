@@ -628,11 +628,21 @@ static int tc_forward_segmented(const fastmax_problem* pb, const fastmax_forward
   float* seg = (float*)ws;
   void* inner = (char*)ws + seg_state_bytes(pb, nseg);
   const size_t inner_bytes = ws_bytes - seg_state_bytes(pb, nseg);
-  fastmax_forward_args t{};   // (1) moments of every segment's keys
-  t.q = seg_view(a->k, vp.nk); t.k = seg_view(a->k, vp.nk); t.v = seg_view(a->v, vp.nk);
-  t.state_out = seg;
-  int rc = tc_forward(&vp, &t, inner, inner_bytes, st);
-  if (rc != FASTMAX_OK) return rc == FASTMAX_TC_NOT_HANDLED ? FASTMAX_ERR_UNSUPPORTED : rc;
+  int rc = FASTMAX_OK;
+  if (a->key_moments_in != nullptr) {   // (1) moments of every segment's keys: from an earlier call with the same k, v ...
+    cudaError_t e = cudaMemcpyAsync(seg, a->key_moments_in, seg_state_bytes(pb, nseg), cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return report_cuda_error(e);
+  } else {                              // ... or summed here
+    fastmax_forward_args t{};
+    t.q = seg_view(a->k, vp.nk); t.k = seg_view(a->k, vp.nk); t.v = seg_view(a->v, vp.nk);
+    t.state_out = seg;
+    rc = tc_forward(&vp, &t, inner, inner_bytes, st);
+    if (rc != FASTMAX_OK) return rc == FASTMAX_TC_NOT_HANDLED ? FASTMAX_ERR_UNSUPPORTED : rc;
+  }
+  if (a->key_moments_out != nullptr && a->key_moments_out != a->key_moments_in) {
+    cudaError_t e = cudaMemcpyAsync(a->key_moments_out, seg, seg_state_bytes(pb, nseg), cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return report_cuda_error(e);
+  }
   rc = launch_seg_scan(seg, nseg, pb, a->state_in, a->state_out, false, st);   // (2) exclusive prefix, total = state_out
   if (rc != FASTMAX_OK) return rc;
   fastmax_forward_args m{};   // (3) every segment from its prefix
@@ -641,6 +651,10 @@ static int tc_forward_segmented(const fastmax_problem* pb, const fastmax_forward
   m.state_in = seg;
   rc = tc_forward(&vp, &m, inner, inner_bytes, st);
   return rc == FASTMAX_TC_NOT_HANDLED ? FASTMAX_ERR_UNSUPPORTED : rc;
+}
+
+size_t tc_key_moments_bytes(const fastmax_problem* pb, const fastmax_forward_args* a) {
+  return tc_forward_segmentable(pb, a) ? seg_state_bytes(pb, tc_segments(pb)) : 0;
 }
 
 int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* ws, size_t ws_bytes, cudaStream_t st) {
@@ -795,25 +809,47 @@ static int tc_backward_segmented(const fastmax_problem* pb, const fastmax_backwa
   void* inner = (char*)ws + 2 * sb;
   const size_t inner_bytes = ws_bytes - 2 * sb;
   auto fix = [](int rc) { return rc == FASTMAX_TC_NOT_HANDLED ? (int)FASTMAX_ERR_UNSUPPORTED : rc; };
-  fastmax_forward_args t{};   // key moments of every segment, exclusive prefix (what dq needs)
-  t.q = seg_view(a->k, vp.nk); t.k = seg_view(a->k, vp.nk); t.v = seg_view(a->v, vp.nk);
-  t.state_out = segS;
-  int rc = tc_forward(&vp, &t, inner, inner_bytes, st);
-  if (rc != FASTMAX_OK) return fix(rc);
-  rc = launch_seg_scan(segS, nseg, pb, a->state_in, nullptr, false, st);
-  if (rc != FASTMAX_OK) return rc;
+  int rc = FASTMAX_OK;
+  const bool want_grads = a->dq.ptr != nullptr;
+  if (want_grads) {   // key moments of every segment, exclusive prefix (what dq needs): handed over by the forward call, or summed here
+    if (a->key_moments_in != nullptr) {
+      cudaError_t e = cudaMemcpyAsync(segS, a->key_moments_in, sb, cudaMemcpyDeviceToDevice, st);
+      if (e != cudaSuccess) return report_cuda_error(e);
+    } else {
+      fastmax_forward_args t{};
+      t.q = seg_view(a->k, vp.nk); t.k = seg_view(a->k, vp.nk); t.v = seg_view(a->v, vp.nk);
+      t.state_out = segS;
+      rc = tc_forward(&vp, &t, inner, inner_bytes, st);
+      if (rc != FASTMAX_OK) return fix(rc);
+    }
+    rc = launch_seg_scan(segS, nseg, pb, a->state_in, nullptr, false, st);
+    if (rc != FASTMAX_OK) return rc;
+  }
   fastmax_backward_args m{};
   m.q = seg_view(a->q, vp.nq); m.k = seg_view(a->k, vp.nk); m.v = seg_view(a->v, vp.nk);
   m.o = seg_view(a->o, vp.nq); m.g = seg_view(a->g, vp.nq); m.d_out = seg_view(a->d_out, vp.nq);
-  fastmax_backward_args gmom = m;   // gradient moments of every segment, exclusive suffix (what dk, dv need)
-  gmom.dstate_out = segD;
-  rc = tc_backward(&vp, &gmom, inner, inner_bytes, st);
-  if (rc != FASTMAX_OK) return fix(rc);
+  if (a->grad_moments_in != nullptr) {   // gradient moments of every segment, exclusive suffix (what dk, dv need)
+    cudaError_t e = cudaMemcpyAsync(segD, a->grad_moments_in, sb, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return report_cuda_error(e);
+  } else {
+    fastmax_backward_args gmom = m;
+    gmom.dstate_out = segD;
+    rc = tc_backward(&vp, &gmom, inner, inner_bytes, st);
+    if (rc != FASTMAX_OK) return fix(rc);
+  }
+  if (a->grad_moments_out != nullptr && a->grad_moments_out != a->grad_moments_in) {
+    cudaError_t e = cudaMemcpyAsync(a->grad_moments_out, segD, sb, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return report_cuda_error(e);
+  }
   rc = launch_seg_scan(segD, nseg, pb, a->dstate_in, a->dstate_out, true, st);
   if (rc != FASTMAX_OK) return rc;
   m.dq = seg_view(a->dq, vp.nq); m.dk = seg_view(a->dk, vp.nk); m.dv = seg_view(a->dv, vp.nk);
   m.state_in = segS; m.dstate_in = segD;
   return fix(tc_backward(&vp, &m, inner, inner_bytes, st));
+}
+
+size_t tc_grad_moments_bytes(const fastmax_problem* pb, const fastmax_backward_args* a) {
+  return tc_backward_segmentable(pb, a) ? seg_state_bytes(pb, tc_segments(pb)) : 0;
 }
 
 int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void* ws, size_t ws_bytes, cudaStream_t st) {

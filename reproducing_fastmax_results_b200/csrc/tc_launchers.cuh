@@ -10,6 +10,9 @@ namespace fm {
 enum { FASTMAX_TC_NOT_HANDLED = -1 };
 size_t tc_forward_workspace(const fastmax_problem* pb, const fastmax_forward_args* a);
 size_t tc_backward_workspace(const fastmax_problem* pb, const fastmax_backward_args* a);
+// Bytes of the per-segment moment arrays a segmented tensor-memory call reads or writes (0: the call is not segmented).
+size_t tc_key_moments_bytes(const fastmax_problem* pb, const fastmax_forward_args* a);
+size_t tc_grad_moments_bytes(const fastmax_problem* pb, const fastmax_backward_args* a);
 int tc_forward(const fastmax_problem* pb, const fastmax_forward_args* a, void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void* ws, size_t ws_bytes, cudaStream_t st);
 // Reads (and clears) the device-side error word the bounded waits of the tensor-core kernels set.

@@ -210,6 +210,33 @@ def test_long_sequence_with_few_heads_is_cut_into_segments(shape):
         assert np.abs(host(dv[0, h])[r] - dv_ref).max() < 2e-2 * scale(dv)
 
 
+def test_segmented_call_hands_its_key_moments_to_the_backward():
+    """The segmented form sums the key moments of every segment first; with a KeyMoments holder the backward takes the
+    forward's sums instead of running that pass again: one update-only scan less, same gradients."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    H, N, order = 2, 4096, 2
+    q, k, v, do = inputs(1, H, N, N, 77, 0.7)
+    it = 1.0 / (2.0 * math.sqrt(D))
+
+    def run(km):
+        L.profile_collect()
+        L.profile(True)
+        o, g, _ = L.forward(q, k, v, True, it, order=order, key_moments=km)
+        grads = L.backward(q, k, v, o, g, do, True, it, order=order, key_moments=km)[:3]
+        L.check_status()
+        L.profile(False)
+        return (o, g) + tuple(grads), L.profile_collect()
+
+    ref, prof_ref = run(None)
+    km = L.KeyMoments()
+    got, prof = run(km)
+    assert km.buf is not None
+    assert prof_ref["tc_scan_fwd"][1] == 3 and prof["tc_scan_fwd"][1] == 2, (prof_ref, prof)
+    for a, b in zip(got, ref):
+        assert orc.max_norm_err(host(a), host(b)) < 4e-3   # same arithmetic; the order of the float32 reduce-adds can flip a bf16 rounding
+
+
 def test_random_call_shapes_agree_with_the_cuda_core_engine():
     """Seeded random shapes (order, mask, nq, nk, heads, carried states, state outputs) through the tensor-memory
     kernels and through the CUDA-core engine (FASTMAX_FLAG_NO_TENSOR_CORES): every output within the bf16 tolerance,
