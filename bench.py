@@ -853,10 +853,14 @@ def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq
     lib = _lib.load()
     variants = {
         # the model exactly as the reference runs it: float32, its own autograd Function over fastmax_cuda.forwardpass
-        "f32_reference_function": dict(autocast=False, swap=False),
+        "f32_reference_function": dict(autocast=False, swap=False, medium=False),
+        # the same unmodified float32 model after torch.set_float32_matmul_precision("medium"), PyTorch's switch that lets
+        # float32 matmuls (the model's Linear layers included) compute in bfloat16: forwardpass / backwardpass then run
+        # the attention on the tensor-memory kernels through bfloat16 copies
+        "f32_reference_function_medium_matmul_precision": dict(autocast=False, swap=False, medium=True),
         # same call site (model.py:303), module-level fastmax_custom replaced by this package's zero-copy FastMax,
         # bf16 autocast: q, k, v reach the tensor-memory kernels as strided bf16 views
-        "bf16_autocast_zero_copy": dict(autocast=True, swap=True),
+        "bf16_autocast_zero_copy": dict(autocast=True, swap=True, medium=False),
     }
     if world > 1:
         # the collective alone: one all-reduce of a tensor as large as the model's gradients, nothing else running
@@ -889,8 +893,11 @@ def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq
         gen = torch.Generator(device=dev).manual_seed(rank)
         ids = torch.randint(0, CFG5["vocab_size"], (batch, seq + 1), device=dev, generator=gen)
         saved = model.fastmax_custom
+        saved_precision = torch.get_float32_matmul_precision()
         if vcfg["swap"]:
             model.fastmax_custom = pkg.fastmax_custom
+        if vcfg["medium"]:
+            torch.set_float32_matmul_precision("medium")
         try:
             def step(sync=True):
                 # sync=False: the same step on the bare module (no DDP hooks, no gradient all-reduce): the replicas
@@ -954,6 +961,7 @@ def measure_cfg5(torch, dist, dev, rank, world, steps=5, warmup=3, batch=16, seq
             }
         finally:
             model.fastmax_custom = saved
+            torch.set_float32_matmul_precision(saved_precision)
         del net, ddp, opt
         torch.cuda.empty_cache()
     return out
@@ -1040,9 +1048,31 @@ def measure_reference_boundary(torch, dist, dev, rank, world, steps=3, warmup=1)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item()) / steps
+    # the same calls after torch.set_float32_matmul_precision("medium"): forwardpass / backwardpass may compute in bfloat16
+    saved_precision = torch.get_float32_matmul_precision()
+    torch.set_float32_matmul_precision("medium")
+    try:
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(10):
+            step()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(e)], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_medium = float(t.item()) / 10
+    finally:
+        torch.set_float32_matmul_precision(saved_precision)
     return {"ms_per_step": ms, "value": world * B * N / (ms * 1e-3) / 1e6, "unit": "Mtokens/s", "scaling": "weak", "dtype": "f32",
             "api": "FASTMultiHeadAttention_Function.apply + backward: the reference wrapper's permutes and copies around "
-                   "fastmax_cuda.forwardpass / backwardpass (float32 contract, CUDA-core engine)"}
+                   "fastmax_cuda.forwardpass / backwardpass (float32 contract, CUDA-core engine)",
+            "medium_matmul_precision": {"ms_per_step": ms_medium, "value": world * B * N / (ms_medium * 1e-3) / 1e6,
+                                        "note": "same float32 tensors and calls after torch.set_float32_matmul_precision('medium'): "
+                                                "the extension converts q, k, v and the upstream gradient to bfloat16 and runs the "
+                                                "tensor-memory kernels (bfloat16 tolerance, not float32 parity)"}}
 
 
 def other_workloads(args, torch, dist, dev, rank, world):

@@ -107,6 +107,10 @@ typedef struct {
 } fastmax_forward_args;
 
 size_t fastmax_forward_workspace(const fastmax_problem* pb, const fastmax_forward_args* args);
+/* Which engine takes this forward call: 1 = the tensor-memory (tcgen05) kernels, 0 = the CUDA-core engine.  A host
+ * that holds float32 tensors and is allowed to compute in bfloat16 (PyTorch's float32 matmul precision "medium") asks
+ * this for the bfloat16 form of its problem before it converts anything. */
+int32_t fastmax_forward_engine(const fastmax_problem* pb, const fastmax_forward_args* args);
 /* Size of the key_moments arrays for this problem and these arguments, or 0 when this call would neither write nor
  * read them (one segment per head, no keys, or a call the tensor-memory kernels take). */
 size_t fastmax_key_moments_bytes(const fastmax_problem* pb, const fastmax_forward_args* args);

@@ -18,7 +18,7 @@ FLAG_SINGLE_STREAM = 2
 
 EXPORTED_SYMBOLS = [
     "fastmax_state_rows", "fastmax_state_ld", "fastmax_state_bytes",
-    "fastmax_forward_workspace", "fastmax_forward", "fastmax_key_moments_bytes",
+    "fastmax_forward_workspace", "fastmax_forward", "fastmax_key_moments_bytes", "fastmax_forward_engine",
     "fastmax_static_scratch_bytes", "fastmax_forward_static_scratch",
     "fastmax_backward_workspace", "fastmax_backward", "fastmax_grad_moments_bytes",
     "fastmax_decode_step",
@@ -100,6 +100,8 @@ def load():
     lib.fastmax_state_bytes.argtypes = [C.POINTER(Problem)]
     lib.fastmax_forward_workspace.restype = C.c_size_t
     lib.fastmax_forward_workspace.argtypes = [C.POINTER(Problem), C.POINTER(ForwardArgs)]
+    lib.fastmax_forward_engine.restype = C.c_int32
+    lib.fastmax_forward_engine.argtypes = [C.POINTER(Problem), C.POINTER(ForwardArgs)]
     lib.fastmax_key_moments_bytes.restype = C.c_size_t
     lib.fastmax_key_moments_bytes.argtypes = [C.POINTER(Problem), C.POINTER(ForwardArgs)]
     lib.fastmax_forward.restype = C.c_int32

@@ -128,9 +128,18 @@ class FastMax(torch.autograd.Function):
                 raise ValueError("apply_rpe needs rpe_matrix, a (2n-1, d) tensor")
             k_op = ext.key_prologue(k.clone(), inv_t, rpe_matrix)   # k / temperature + rpe rows, on a private copy
             k_scale, inv_t = inv_t, 1.0
+        # float32 tensors under torch.set_float32_matmul_precision("medium") (PyTorch's switch for bfloat16 inside
+        # float32 matmuls): the attention itself runs on bfloat16 copies when that puts it on the tensor-memory
+        # kernels; the normalisation above, its gradient and everything the caller sees stay float32
+        qc, kc, vc = q, k_op, v
+        if q.dtype == torch.float32 and torch.get_float32_matmul_precision() == "medium":
+            qb, kb, vb = q.bfloat16(), k_op.bfloat16(), v.bfloat16()
+            if ext.forward_engine(qb, kb, vb, bool(mask), int(p)) == 1:
+                qc, kc, vc = qb, kb, vb
+        cast = qc is not q
         # the fourth entry: per-segment key moments when the call computed some (long sequences with few heads on the
         # CUDA-core engine); the backward reads them instead of passing over k and v again
-        o, g, _, kmom = ext.forward(q, k_op, v, bool(mask), inv_t, float(a0), float(a1), float(a2), int(p), None, False, True, 0,
+        o, g, _, kmom = ext.forward(qc, kc, vc, bool(mask), inv_t, float(a0), float(a1), float(a2), int(p), None, False, True, 0,
                                     None, None, True)
         noise = None
         out = o
@@ -139,8 +148,12 @@ class FastMax(torch.autograd.Function):
                 raise ValueError("noise_dropout needs drop_noise, a tensor shaped like q")
             noise = drop_noise.to(o.dtype)
             out = ext.output_noise(o, noise, float(dropout))
+        if cast:
+            out = out.float()
         extra = ([stats_q, stats_k] if normalize else []) + ([k] if (normalize and apply_rpe) else [])
-        ctx.save_for_backward(q, k_op, v, o, g, *extra, *([noise] if noise is not None else []))
+        extra += [q, k] if (normalize and cast) else []   # the float32 normalised tensors, for the normalisation's gradient
+        ctx.save_for_backward(qc, kc, vc, o, g, *extra, *([noise] if noise is not None else []))
+        ctx.cast = cast
         ctx.cfg = (bool(mask), inv_t, float(a0), float(a1), float(a2), int(p), bool(normalize), float(lim), three_d,
                    k_scale, float(dropout) if noise is not None else 0.0, bool(apply_rpe))
         ctx.key_moments = kmom   # not an input or output of the function: kept on the context
@@ -155,16 +168,22 @@ class FastMax(torch.autograd.Function):
             grad_output = grad_output.unsqueeze(0)
         if grad_output.stride(-1) != 1:
             grad_output = grad_output.contiguous()
+        if ctx.cast:               # the attention ran on bfloat16 copies (float32 matmul precision "medium")
+            grad_output = grad_output.to(o.dtype)
         if noise_scale != 0.0:     # out = o * (1 + s * noise)  ->  d o = d out * (1 + s * noise)
             grad_output = ext.output_noise(grad_output, ctx.saved_tensors[-1], noise_scale)
         dq, dk, dv, _ = ext.backward(q, k, v, o, g, grad_output, mask, inv_t, a0, a1, a2, p, None, None, False, True, 0,
                                      None, ctx.key_moments)
+        if ctx.cast:
+            dq, dk, dv = dq.float(), dk.float(), dv.float()
         if k_scale != 1.0:         # the operator saw k / temperature + rpe rows
             dk = ext.key_prologue(dk, k_scale, None)
         if normalize:
             stats_q, stats_k = ctx.saved_tensors[5:7]
-            dq = ext.normalize_backward(q, dq, stats_q, lim)
-            dk = ext.normalize_backward(ctx.saved_tensors[7] if apply_rpe else k, dk, stats_k, lim)
+            nxt = 8 if apply_rpe else 7
+            yq, yk = (ctx.saved_tensors[nxt], ctx.saved_tensors[nxt + 1]) if ctx.cast else (q, ctx.saved_tensors[7] if apply_rpe else k)
+            dq = ext.normalize_backward(yq, dq, stats_q, lim)
+            dk = ext.normalize_backward(yk, dk, stats_k, lim)
         if three_d:
             dq, dk, dv = dq.squeeze(0), dk.squeeze(0), dv.squeeze(0)
         return dq, dk, dv, None, None, None, None, None, None, None, None, None, None, None, None, None

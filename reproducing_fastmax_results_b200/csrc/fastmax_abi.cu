@@ -444,11 +444,17 @@ size_t fastmax_forward_workspace(const fastmax_problem* pb, const fastmax_forwar
   return (L.total > tc ? L.total : tc) + 256;
 }
 
+int32_t fastmax_forward_engine(const fastmax_problem* pb, const fastmax_forward_args* args) {
+  Plan pl;
+  if (!args || make_plan(pb, pl) != FASTMAX_OK) return 0;
+  return tc_takes_forward(pb, args) ? 1 : 0;
+}
+
 size_t fastmax_key_moments_bytes(const fastmax_problem* pb, const fastmax_forward_args* args) {
   Plan pl;
   if (!args || make_plan(pb, pl) != FASTMAX_OK || pb->nk == 0) return 0;
   if (const size_t t = tc_key_moments_bytes(pb, args)) return t;   // a long sequence cut into segments for the tensor-memory kernels
-  if (tc_forward_workspace(pb, args) != 0) return 0;   // the tensor-memory kernels take this call whole: no segment sums
+  if (tc_takes_forward(pb, args)) return 0;   // the tensor-memory kernels take this call whole: no segment sums
   FwdLayout L;
   if (!fwd_layout(pb, args, pl, L)) return 0;
   return (size_t)pl.bh * pl.k_nseg * pl.n_state * sizeof(float);
@@ -567,7 +573,7 @@ size_t fastmax_grad_moments_bytes(const fastmax_problem* pb, const fastmax_backw
   Plan pl;
   if (!args || make_plan(pb, pl, true) != FASTMAX_OK) return 0;
   if (const size_t t = tc_grad_moments_bytes(pb, args)) return t;
-  if (tc_backward_workspace(pb, args) != 0) return 0;   // the tensor-memory kernels take this call whole: no segment sums
+  if (tc_takes_backward(pb, args)) return 0;   // the tensor-memory kernels take this call whole: no segment sums
   BwdLayout L;
   bwd_layout(pb, args, pl, L);
   const int nsegD = pb->causal ? pl.k_nseg : pl.q_nseg;

@@ -37,9 +37,14 @@ int dtype_of(const torch::Tensor& t) {
   TORCH_CHECK(false, "fastmax: tensors must be float32 or bfloat16, got ", t.scalar_type());
 }
 
+// PyTorch's own switch for "float32 matmuls may run in bfloat16" (torch.set_float32_matmul_precision("medium")).
+// float32 callers that set it get the tensor-memory kernels: q, k, v (and the upstream gradient) are converted to
+// bfloat16 for the call and the results converted back; the default ("highest") keeps the exact float32 engine.
+bool float32_may_use_bf16() { return at::globalContext().float32MatmulPrecision() == at::Float32MatmulPrecision::MEDIUM; }
+
 // (n, bh, d) contiguous -> view with batch=1
 fastmax_tensor view_nbd(const torch::Tensor& t) {
-  return fastmax_tensor{t.data_ptr(), 0, t.stride(1), t.stride(0)};
+  return fastmax_tensor{t.data_ptr(), (int64_t)t.numel(), t.stride(1), t.stride(0)};   // one batch: its stride is never used as an offset
 }
 // (b, h, n, d) with unit innermost stride
 fastmax_tensor view_bhnd(const torch::Tensor& t) {
@@ -98,6 +103,23 @@ torch::Tensor forwardpass(torch::Tensor q, torch::Tensor k, torch::Tensor v, tor
   a.q = view_nbd(q); a.k = view_nbd(k); a.v = view_nbd(v);
   a.o = fastmax_tensor{o.data_ptr(), 0, o.stride(1), o.stride(0)};
   a.g = fastmax_tensor{(float*)o.data_ptr() + d, 0, o.stride(1), o.stride(0)};
+  if (float32_may_use_bf16()) {
+    // the same call on bfloat16 copies, if the tensor-memory kernels take it: o' comes back in bfloat16 and is widened
+    // into the first d columns of o; g goes straight into column d
+    auto qb = q.to(torch::kBFloat16), kb = k.to(torch::kBFloat16), vb = v.to(torch::kBFloat16);
+    auto ob = torch::empty({nq, bh, d}, qb.options());
+    fastmax_problem pbb = pb;
+    pbb.dtype = FASTMAX_BF16;
+    fastmax_forward_args ab = a;
+    ab.q = view_nbd(qb); ab.k = view_nbd(kb); ab.v = view_nbd(vb); ab.o = view_nbd(ob);
+    if (fastmax_forward_engine(&pbb, &ab) == 1) {
+      size_t need = fastmax_forward_workspace(&pbb, &ab);
+      auto ws = workspace(need, q);
+      check_status(fastmax_forward(&pbb, &ab, aligned(ws), need, stream), "fastmax forwardpass (bfloat16 compute)");
+      o.narrow(2, 0, d).copy_(ob);
+      return o;
+    }
+  }
   size_t need = fastmax_forward_workspace(&pb, &a);
   auto ws = workspace(need, q);
   check_status(fastmax_forward(&pb, &a, aligned(ws), need, stream), "fastmax forwardpass");
@@ -125,6 +147,25 @@ std::vector<torch::Tensor> backwardpass(torch::Tensor q, torch::Tensor k, torch:
   a.g = fastmax_tensor{(float*)o.data_ptr() + d, 0, o.stride(1), o.stride(0)};
   a.d_out = view_nbd(grad_output);
   a.dq = view_nbd(gradq); a.dk = view_nbd(gradk); a.dv = view_nbd(gradv);
+  if (float32_may_use_bf16()) {
+    auto qb = q.to(torch::kBFloat16), kb = k.to(torch::kBFloat16), vb = v.to(torch::kBFloat16);
+    auto ob = o.narrow(2, 0, d).to(torch::kBFloat16), gb = grad_output.to(torch::kBFloat16);   // contiguous (nq, bh, d) copies
+    fastmax_problem pbb = pb;
+    pbb.dtype = FASTMAX_BF16;
+    fastmax_forward_args fb{};   // which engine the bfloat16 form of the forward call goes to decides for the pair
+    fb.q = view_nbd(qb); fb.k = view_nbd(kb); fb.v = view_nbd(vb); fb.o = view_nbd(ob); fb.g = a.g;
+    if (fastmax_forward_engine(&pbb, &fb) == 1) {
+      auto dqb = torch::empty_like(qb), dkb = torch::empty_like(kb), dvb = torch::empty_like(vb);
+      fastmax_backward_args ab = a;
+      ab.q = fb.q; ab.k = fb.k; ab.v = fb.v; ab.o = fb.o; ab.d_out = view_nbd(gb);
+      ab.dq = view_nbd(dqb); ab.dk = view_nbd(dkb); ab.dv = view_nbd(dvb);
+      size_t need = fastmax_backward_workspace(&pbb, &ab);
+      auto ws = workspace(need, q);
+      check_status(fastmax_backward(&pbb, &ab, aligned(ws), need, stream), "fastmax backwardpass (bfloat16 compute)");
+      gradq.copy_(dqb); gradk.copy_(dkb); gradv.copy_(dvb);
+      return {gradq, gradk, gradv};
+    }
+  }
   size_t need = fastmax_backward_workspace(&pb, &a);
   auto ws = workspace(need, q);
   check_status(fastmax_backward(&pb, &a, aligned(ws), need, stream), "fastmax backwardpass");
@@ -336,6 +377,17 @@ torch::Tensor output_noise(torch::Tensor x, torch::Tensor noise, double scale) {
   return out;
 }
 
+// 1 when the tensor-memory kernels take a forward call on these (b, h, n, d) tensors, 0 for the CUDA-core engine
+int64_t forward_engine(torch::Tensor q, torch::Tensor k, torch::Tensor v, bool causal, int64_t p) {
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "q, k, v must be (b, h, n, d)");
+  fastmax_problem pb = make_problem(q, k, causal, 1.0, 1.0, 1.0, 0.5, p, 0);
+  fastmax_forward_args a{};
+  a.q = view_bhnd(q); a.k = view_bhnd(k); a.v = view_bhnd(v);
+  a.o = view_bhnd(q);   // placeholders of the right shape: nothing is read or written
+  a.g = fastmax_tensor{q.data_ptr(), q.size(1) * q.size(2), q.size(2), 1};
+  return fastmax_forward_engine(&pb, &a);
+}
+
 int64_t launch_count() { return (int64_t)fastmax_launch_count(); }
 
 }  // namespace
@@ -362,6 +414,7 @@ PYBIND11_MODULE(fastmax_cuda, m) {
   m.def("key_prologue", &key_prologue, "k <- k * inv_temp + rpe rows, in place", py::arg("k"), py::arg("inv_temp"),
         py::arg("rpe") = py::none(), release());
   m.def("output_noise", &output_noise, "x * (1 + scale * noise)", release());
+  m.def("forward_engine", &forward_engine, "1: tensor-memory kernels, 0: CUDA-core engine, for a forward call on these tensors");
   m.def("launch_count", &launch_count, "kernel launches issued by the library so far");
   m.def("version", []() { return std::string(fastmax_version()); });
 }

@@ -653,6 +653,10 @@ static int tc_forward_segmented(const fastmax_problem* pb, const fastmax_forward
   return rc == FASTMAX_TC_NOT_HANDLED ? FASTMAX_ERR_UNSUPPORTED : rc;
 }
 
+bool tc_takes_forward(const fastmax_problem* pb, const fastmax_forward_args* a) {
+  return tc_p1_supported(pb, a) || tc_forward_segmentable(pb, a) || tc_forward_supported(pb, a);
+}
+
 size_t tc_key_moments_bytes(const fastmax_problem* pb, const fastmax_forward_args* a) {
   return tc_forward_segmentable(pb, a) ? seg_state_bytes(pb, tc_segments(pb)) : 0;
 }
@@ -846,6 +850,10 @@ static int tc_backward_segmented(const fastmax_problem* pb, const fastmax_backwa
   m.dq = seg_view(a->dq, vp.nq); m.dk = seg_view(a->dk, vp.nk); m.dv = seg_view(a->dv, vp.nk);
   m.state_in = segS; m.dstate_in = segD;
   return fix(tc_backward(&vp, &m, inner, inner_bytes, st));
+}
+
+bool tc_takes_backward(const fastmax_problem* pb, const fastmax_backward_args* a) {
+  return tc_backward_segmentable(pb, a) || tc_backward_supported(pb, a);
 }
 
 size_t tc_grad_moments_bytes(const fastmax_problem* pb, const fastmax_backward_args* a) {

@@ -10,6 +10,10 @@ namespace fm {
 enum { FASTMAX_TC_NOT_HANDLED = -1 };
 size_t tc_forward_workspace(const fastmax_problem* pb, const fastmax_forward_args* a);
 size_t tc_backward_workspace(const fastmax_problem* pb, const fastmax_backward_args* a);
+// Whether the tensor-memory kernels take the call (they may still hand it back at run time when the copy engine
+// cannot describe a tensor's layout; the CUDA-core engine then runs it).
+bool tc_takes_forward(const fastmax_problem* pb, const fastmax_forward_args* a);
+bool tc_takes_backward(const fastmax_problem* pb, const fastmax_backward_args* a);
 // Bytes of the per-segment moment arrays a segmented tensor-memory call reads or writes (0: the call is not segmented).
 size_t tc_key_moments_bytes(const fastmax_problem* pb, const fastmax_forward_args* a);
 size_t tc_grad_moments_bytes(const fastmax_problem* pb, const fastmax_backward_args* a);

@@ -259,3 +259,60 @@ def test_fastmax_with_rpe_and_noise_dropout_switched_on():
     plain = pkg.fastmax_custom(qd, kd, vd, nd, rd, True, rate, False, t, 1.0, 1.0, 0.5, 1.0, 2)
     o_plain, _ = orc.fastmax_naive(q, k, v, True, orc.Poly(1.0, 1.0, 0.5, 1.0 / t, 2))
     assert orc.max_norm_err(host(plain), o_plain) < 1e-4
+
+
+@pytest.mark.parametrize("which", ["FastMax", "FASTMultiHeadAttention_Function"])
+@pytest.mark.parametrize("normalize", [False, True])
+def test_float32_callers_reach_the_tensor_memory_kernels_under_medium_matmul_precision(which, normalize):
+    """torch.set_float32_matmul_precision("medium") is PyTorch's permission to compute float32 matmuls in bfloat16.
+    With it, float32 q, k, v of a shape the tensor-memory kernels take run there (on bfloat16 copies; inputs, outputs and
+    gradients stay float32) and agree with the exact float32 engine to the bfloat16 tolerance; without it nothing changes."""
+    import reproducing_fastmax_results_b200 as pkg
+    from reproducing_fastmax_results_b200 import _lib
+    from reproducing_fastmax_results_b200.attention import FASTMultiHeadAttention_Function, FastMax
+
+    B, H, N, D = 2, 16, 384, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q0, k0, v0, do = (torch.randn(B, H, N, D, device="cuda", generator=g) * 0.6 for _ in range(4))
+    noise, rpe = torch.zeros_like(q0), torch.zeros(2 * N - 1, D, device="cuda")
+    temperature = 1.0 if normalize else 2.0 * math.sqrt(D)
+    if which == "FASTMultiHeadAttention_Function" and normalize:
+        pytest.skip("the reference's own Function ignores the normalisation in its backward")
+
+    def run():
+        q, k, v = (t.clone().requires_grad_(True) for t in (q0, k0, v0))
+        _lib.profile_collect()
+        _lib.profile(True)
+        if which == "FastMax":
+            o = FastMax.apply(q, k, v, noise, rpe, True, 0.0, normalize, temperature, 1.0, 1.0, 0.5, 1.0, 2)
+        else:
+            o = FASTMultiHeadAttention_Function.apply(q, k, v, noise, rpe, True, 0.0, normalize, temperature, 1.0, 1.0, 0.5, 1.0, 2)
+        o.backward(do)
+        torch.cuda.synchronize()
+        _lib.profile(False)
+        kinds = set(_lib.profile_collect())
+        assert o.dtype == torch.float32 and q.grad.dtype == torch.float32
+        return (o.detach(), q.grad, k.grad, v.grad), kinds
+
+    pkg.load_extension()
+    before = torch.get_float32_matmul_precision()
+    try:
+        torch.set_float32_matmul_precision("highest")
+        exact, kinds_exact = run()
+        assert "tc_scan_fwd" not in kinds_exact and "scan_fwd" in kinds_exact, kinds_exact
+        torch.set_float32_matmul_precision("medium")
+        fast, kinds_fast = run()
+        assert {"tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_scan_bwd_dv"} <= kinds_fast, kinds_fast
+        assert not ({"scan_fwd", "scan_bwd_q", "scan_bwd_kv"} & kinds_fast), kinds_fast
+        for a, b in zip(fast, exact):
+            assert orc.max_norm_err(host(a), host(b)) < 2e-2
+        # a shape the tensor-memory kernels do not take (head dim 32) stays on the exact engine, in float32
+        q, k, v = (torch.randn(2, 16, 128, 32, device="cuda", generator=g) for _ in range(3))
+        _lib.profile_collect()
+        _lib.profile(True)
+        FastMax.apply(q, k, v, None, None, True, 0.0, False, 8.0, 1.0, 1.0, 0.5, 1.0, 2)
+        torch.cuda.synchronize()
+        _lib.profile(False)
+        assert "scan_fwd" in set(_lib.profile_collect())
+    finally:
+        torch.set_float32_matmul_precision(before)
