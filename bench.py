@@ -46,6 +46,8 @@ WORKLOADS = {
     "cfg3_f32_causal_p2_B1_H8_N131072_D32": (1, 8, 131072, 32, 2, True, "f32", 1.0),
     # BASELINE config 4: order 1, non-causal, wide batch, forward (run with --mode fwd): HBM-bound
     "cfg4_bf16_noncausal_p1_B64_H12_N1024_D64": (64, 12, 1024, 64, 1, False, "bf16", 0.5),
+    # config 2's shape with narrower heads (bf16): zero-padded to 64 on the tensor-memory kernels
+    "d32_bf16_causal_p2_B8_H16_N4096_D32": (8, 16, 4096, 32, 2, True, "bf16", 1.0),
     # incremental decoding: one new token per (batch, head) per step against the carried state (N = prefix length is
     # irrelevant to the cost; 512 head states = 330 MB, larger than L2)
     "decode_bf16_p2_B32_H16_D64": (32, 16, 1, 64, 2, True, "bf16", 1.0),

@@ -52,7 +52,7 @@ void launch_end(int kind, cudaStream_t st) {
 }
 static const char* kKindNames[KK_COUNT] = {
     "moments_kv", "moments_qg", "state_scan", "scan_fwd", "scan_bwd_q", "scan_bwd_kv", "finalize_fwd",
-    "bwd_prologue", "cast_out", "normalize", "tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_moments", "p1_fwd", "tc_intra_fwd", "tc_intra_bwd", "tc_transpose", "tc_scan_bwd_dv", "decode_step", "key_prologue", "output_noise"};
+    "bwd_prologue", "cast_out", "normalize", "tc_scan_fwd", "tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_moments", "p1_fwd", "tc_intra_fwd", "tc_intra_bwd", "tc_transpose", "tc_scan_bwd_dv", "decode_step", "key_prologue", "output_noise", "tc_pad"};
 
 static int sm_count() {
   static int cached[64] = {0};

@@ -21,7 +21,7 @@ extern template cudaError_t launch_moments_d<64>(int, int, const MomentParams&, 
 // launch with CUDA events on its stream so per-kernel device time can be read back.
 enum KernelKind {
   KK_MOMENTS_KV = 0, KK_MOMENTS_QG, KK_STATE_SCAN, KK_SCAN_FWD, KK_SCAN_BWD_Q, KK_SCAN_BWD_KV, KK_FINALIZE,
-  KK_PROLOGUE, KK_CAST, KK_NORMALIZE, KK_TC_FWD, KK_TC_BWD_Q, KK_TC_BWD_KV, KK_TC_MOMENTS, KK_P1_FWD, KK_TC_INTRA_FWD, KK_TC_INTRA_BWD, KK_TC_TRANSPOSE, KK_TC_BWD_DV, KK_DECODE, KK_KEY_PROLOGUE, KK_OUTPUT_NOISE, KK_COUNT
+  KK_PROLOGUE, KK_CAST, KK_NORMALIZE, KK_TC_FWD, KK_TC_BWD_Q, KK_TC_BWD_KV, KK_TC_MOMENTS, KK_P1_FWD, KK_TC_INTRA_FWD, KK_TC_INTRA_BWD, KK_TC_TRANSPOSE, KK_TC_BWD_DV, KK_DECODE, KK_KEY_PROLOGUE, KK_OUTPUT_NOISE, KK_TC_PAD, KK_COUNT
 };
 bool profiling_on();   // per-kernel timing is enabled: launch sequences then stay on one stream so the times do not overlap
 void launch_begin(int kind, cudaStream_t st);

@@ -306,8 +306,8 @@ def test_float32_callers_reach_the_tensor_memory_kernels_under_medium_matmul_pre
         assert not ({"scan_fwd", "scan_bwd_q", "scan_bwd_kv"} & kinds_fast), kinds_fast
         for a, b in zip(fast, exact):
             assert orc.max_norm_err(host(a), host(b)) < 2e-2
-        # a shape the tensor-memory kernels do not take (head dim 32) stays on the exact engine, in float32
-        q, k, v = (torch.randn(2, 16, 128, 32, device="cuda", generator=g) for _ in range(3))
+        # a shape the tensor-memory kernels do not take (head dim 16) stays on the exact engine, in float32
+        q, k, v = (torch.randn(2, 16, 128, 16, device="cuda", generator=g) for _ in range(3))
         _lib.profile_collect()
         _lib.profile(True)
         FastMax.apply(q, k, v, None, None, True, 0.0, False, 8.0, 1.0, 1.0, 0.5, 1.0, 2)

@@ -237,6 +237,39 @@ def test_segmented_call_hands_its_key_moments_to_the_backward():
         assert orc.max_norm_err(host(a), host(b)) < 4e-3   # same arithmetic; the order of the float32 reduce-adds can flip a bf16 rounding
 
 
+@pytest.mark.parametrize("d", [32])
+@pytest.mark.parametrize("causal,order,nq,nk", [(True, 2, 300, 300), (False, 2, 200, 333), (True, 1, 256, 384), (True, 2, 4096, 4096)])
+def test_narrow_bf16_heads_run_zero_padded_on_the_tensor_memory_kernels(d, causal, order, nq, nk):
+    """bf16 heads of 32 dims are zero-padded to the 64 the kernels are built for (the padding contributes nothing):
+    same results as the CUDA-core engine on the narrow tensors, every scan on tensor memory, strided views in and out."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    # the long case: few heads, so the padded call is also cut into segments; order 1 has one scan block per head and needs 64
+    B, H = (1, 4) if nq == 4096 else ((2, 40) if order == 1 else (2, 16))
+    g = torch.Generator(device="cuda").manual_seed(100 * d + nq)
+    # head-split views of (b, n, h*d) buffers, as a model hands them over
+    mk = lambda n: (torch.randn(B, n, H * d, device="cuda", generator=g) * 0.8).bfloat16().view(B, n, H, d).transpose(1, 2)
+    q, do = mk(nq), mk(nq)
+    k, v = mk(nk), mk(nk)
+    it = 1.0 / (2.0 * math.sqrt(d))
+    out = torch.zeros(B, nq, H * d, device="cuda", dtype=torch.bfloat16).view(B, nq, H, d).transpose(1, 2)
+    L.profile_collect()
+    L.profile(True)
+    o, gg, _ = L.forward(q, k, v, causal, it, 0.9, 1.1, 0.45, order, out=out)
+    dq, dk, dv, _ = L.backward(q, k, v, o, gg, do, causal, it, 0.9, 1.1, 0.45, order)
+    L.check_status()
+    L.profile(False)
+    kinds = set(L.profile_collect())
+    assert "tc_pad" in kinds and not (FFMA & kinds), kinds
+    assert ("tc_scan_fwd" in kinds or "p1_fwd" in kinds) and {"tc_scan_bwd_q", "tc_scan_bwd_kv", "tc_scan_bwd_dv"} <= kinds, kinds
+    assert o.data_ptr() == out.data_ptr()
+    o2, g2, _ = L.forward(q, k, v, causal, it, 0.9, 1.1, 0.45, order, flags=L.FLAG_NO_TENSOR_CORES)
+    dq2, dk2, dv2, _ = L.backward(q, k, v, o2, g2, do, causal, it, 0.9, 1.1, 0.45, order, flags=L.FLAG_NO_TENSOR_CORES)
+    torch.cuda.synchronize()
+    for a, b, name in ((o, o2, "o"), (gg, g2, "g"), (dq, dq2, "dq"), (dk, dk2, "dk"), (dv, dv2, "dv")):
+        assert orc.max_norm_err(host(a), host(b)) < 2e-2, name
+
+
 def test_random_call_shapes_agree_with_the_cuda_core_engine():
     """Seeded random shapes (order, mask, nq, nk, heads, carried states, state outputs) through the tensor-memory
     kernels and through the CUDA-core engine (FASTMAX_FLAG_NO_TENSOR_CORES): every output within the bf16 tolerance,
