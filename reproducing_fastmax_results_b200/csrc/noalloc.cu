@@ -45,17 +45,23 @@ size_t fastmax_static_scratch_bytes(void) { return kScratchBytes; }
 
 int32_t fastmax_forward_static_scratch(const fastmax_problem* pb, const fastmax_forward_args* args, void* cuda_stream) {
   if (!pb || !args) return FASTMAX_ERR_INVALID_ARGUMENT;
-  const size_t need = fastmax_forward_workspace(pb, args);
+  fastmax_problem one = *pb;
+  one.flags |= FASTMAX_FLAG_SINGLE_STREAM;
+  size_t need = fastmax_forward_workspace(&one, args);
   if (need == 0) return fastmax_forward(pb, args, nullptr, 0, cuda_stream);  // reports what is wrong with the problem
-  if (need > kScratchBytes) return FASTMAX_ERR_SCRATCH_LIMIT;
+  if (need > kScratchBytes) {
+    // the tensor-memory kernels want more scratch than the CUDA-core engine (transposed and padded copies): a problem
+    // that only fits without them runs there
+    one.flags |= FASTMAX_FLAG_NO_TENSOR_CORES;
+    need = fastmax_forward_workspace(&one, args);
+    if (need == 0 || need > kScratchBytes) return FASTMAX_ERR_SCRATCH_LIMIT;
+  }
   void* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != FASTMAX_OK) return rc;
   // The launch sequence zeroes the accumulators it sums into and overwrites the rest, so what the previous
   // call left in the array does not matter.  Everything stays on the caller's stream: this entry point creates
   // nothing, not even the internal side streams the ordinary call may set up on its first use.
-  fastmax_problem one = *pb;
-  one.flags |= FASTMAX_FLAG_SINGLE_STREAM;
   return fastmax_forward(&one, args, scratch, kScratchBytes, cuda_stream);
 }
 

@@ -22,13 +22,16 @@ def _inputs(B, H, N, D, dtype, seed):
 
 
 @pytest.mark.parametrize("case", [
-    (1, 4, 300, 32, torch.float32, 1e-4),    # CUDA-core engine, ragged length
-    (2, 8, 512, 64, torch.bfloat16, 2e-2),   # tensor-core engine
+    (1, 4, 300, 32, torch.float32, 1e-4, 1e-4),    # CUDA-core engine, ragged length
+    (2, 8, 512, 64, torch.bfloat16, 2e-2, 1e-4),   # tensor-core engine
+    # the padded tensor-core form needs 16 MB of scratch, the CUDA-core engine 3 MB: it runs there, while the ordinary
+    # call it is compared with takes the tensor-core form (two engines: the denominators agree to bf16 accuracy)
+    (4, 20, 256, 32, torch.bfloat16, 2e-2, 5e-3),
 ])
 def test_static_scratch_forward_matches_workspace_forward_twice(case):
     from reproducing_fastmax_results_b200 import _lib as L
 
-    B, H, N, D, dtype, tol = case
+    B, H, N, D, dtype, tol, gtol = case
     inv_temp = 1.0 / (4.0 * math.sqrt(D))
     for call in range(2):  # second call: different data over the scratch the first call left behind
         q, k, v = _inputs(B, H, N, D, dtype, seed=100 + call)
@@ -37,7 +40,7 @@ def test_static_scratch_forward_matches_workspace_forward_twice(case):
         L.check_status()
         scale = float(o_ref.float().abs().max())
         assert float((o.float() - o_ref.float()).abs().max()) <= tol * scale
-        assert torch.allclose(g, g_ref, rtol=1e-4, atol=1e-4 * float(g_ref.abs().max()))
+        assert torch.allclose(g, g_ref, rtol=gtol, atol=gtol * float(g_ref.abs().max()))
 
 
 def test_static_scratch_rejects_problems_beyond_its_size():
