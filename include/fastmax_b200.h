@@ -123,8 +123,9 @@ int32_t fastmax_forward(const fastmax_problem* pb, const fastmax_forward_args* a
  * an FFI binding without an allocator, a "no allocation after start-up" rule): the scratch is a fixed array of
  * FASTMAX_STATIC_SCRATCH_BYTES inside the library's device image, present on every GPU that loads the library
  * until the process exits.  Inputs and outputs are still the caller's.  Same arguments and results as
- * fastmax_forward.  A problem whose fastmax_forward_workspace() exceeds the array is refused with
- * FASTMAX_ERR_SCRATCH_LIMIT.  The call itself performs no cudaMalloc / cudaFree.
+ * fastmax_forward.  A problem whose scratch exceeds the array is refused with FASTMAX_ERR_SCRATCH_LIMIT; when the
+ * tensor-memory kernels' scratch (transposed and padded copies) does not fit but the CUDA-core engine's does, the call
+ * runs on the latter.  The call itself performs no cudaMalloc / cudaFree.
  * The first call on each device looks the array's address up (cudaGetSymbolAddress): make that first call
  * before starting any stream capture.  All calls on a device share the one array: two calls whose kernels can
  * overlap on the GPU (different streams without an ordering between them) race; calls on one stream are safe. */
