@@ -599,8 +599,7 @@ def measure_sequence_sharded(workload, steps, warmup, torch, dist, dev, rank, wo
     _lib.profile(False)
     kernels = {name: {"ms_per_launch": ms / cnt, "launches_per_step": cnt / steps, "ms_per_step": ms / steps}
                for name, (ms, cnt) in _lib.profile_collect().items()}
-    parity = None
-    if check:
+    def parity_error():
         o, g, dq, dk, dv = step()
         full = []
         for x in (q, k, v, do, o, g):
@@ -626,14 +625,49 @@ def measure_sequence_sharded(workload, steps, warmup, torch, dist, dev, rank, wo
         te = torch.tensor([e], device=dev, dtype=torch.float64)
         if dist is not None:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        parity = {"max_normalised_error_all_ranks": float(te.item()), "tolerance": 1e-4 if dtype_name == "f32" else 2e-2,
-                  "rows_per_rank": int(rows.numel()),
+        return float(te.item()), int(rows.numel())
+
+    parity = None
+    if check:
+        e, nrows = parity_error()
+        parity = {"max_normalised_error_all_ranks": e, "tolerance": 1e-4 if dtype_name == "f32" else 2e-2,
+                  "rows_per_rank": nrows,
                   "how": "sampled rows of o, dq and sampled key positions of dk, dv on every rank against an exact float64 "
                          "row evaluation over the gathered sequence, on the device"}
+    medium = None
+    if check and dtype == torch.float32:
+        # the same float32 step after torch.set_float32_matmul_precision("medium"): the pieces run on bfloat16 copies on the
+        # tensor-memory kernels (32-wide heads zero-padded to 64), the exchanged states stay float32; bfloat16 tolerance
+        saved_precision = torch.get_float32_matmul_precision()
+        torch.set_float32_matmul_precision("medium")
+        try:
+            for _ in range(2):
+                step()
+            barrier()
+            ev0.record()
+            for _ in range(steps):
+                step()
+            ev1.record()
+            barrier()
+            tm = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
+            if dist is not None:
+                dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+            _lib.profile_collect()
+            _lib.profile(True)
+            step()
+            torch.cuda.synchronize()
+            _lib.profile(False)
+            kinds = sorted(_lib.profile_collect())
+            e, _ = parity_error()
+            medium = {"ms_per_step": float(tm.item()) / steps, "max_normalised_error_all_ranks": e, "tolerance": 2e-2,
+                      "engines": kinds}
+        finally:
+            torch.set_float32_matmul_precision(saved_precision)
     rows_state = (64 * (D // 8) * (D // 8 + 1) // 2) + D + 1
     return {"ms_per_step": ms_step, "value": B * N / (ms_step * 1e-3) / 1e6, "unit": "Mtokens/s", "exchange_ms_per_step": exchange_ms,
             "state_bytes_per_rank": B * H * rows_state * (D + 4) * 4, "tokens_per_rank": n_local, "kernels": kernels,
-            "gpu_launches": int(launches), "clocks": clocks, "parity": parity, "engines": sorted(kernels)}
+            "gpu_launches": int(launches), "clocks": clocks, "parity": parity, "engines": sorted(kernels),
+            "medium_matmul_precision": medium}
 
 
 def run_sequence_sharded(args, torch, dist, dev, rank, world):

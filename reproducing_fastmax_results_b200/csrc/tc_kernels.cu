@@ -555,8 +555,8 @@ static size_t seg_state_bytes(const fastmax_problem* pb, int nseg) {
 // The kernels are built for 64-wide heads.  A narrower bf16 head is zero-padded to 64 columns in the workspace: the
 // added dimensions contribute nothing to any score, moment, output or gradient, so the results are those of the
 // narrow problem.  Four times the arithmetic a 32-wide head strictly needs, on an engine that is about twenty times
-// faster per operation than the CUDA cores.  Calls with carried states keep the CUDA-core engine (the
-// state layout depends on D).
+// faster per operation than the CUDA cores.  Carried states are converted between the 32-wide and the 64-wide layout
+// on the way in and out (state_width_kernel).
 namespace tc {
 // x: strided [batch][heads][n][d] bf16 view, out: dense [batch*heads][n][64]; a thread moves eight columns
 __global__ void pad_cols_kernel(View x, int d, int n, int heads, uint4* __restrict__ out, long long nrows) {
@@ -583,7 +583,52 @@ __global__ void unpad_cols_kernel(const uint4* __restrict__ in, int d, int n, in
   *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(y.ptr)) + (long long)b * y.sb + (long long)h * y.sh +
                             (long long)l * y.sn + c8 * 8) = in[idx];
 }
+// Moment states between the 32-wide layout ([heads][rows32][36]: pair units of the 4 x 4 block grid, 32 linear rows, the
+// constant; columns 0..31 values, 32 the denominator moment) and the 64-wide one ([heads][rows64][68], 8 x 8 grid,
+// denominator in column 64).  Every row / column of the narrow state has one place in the wide one; the rest of the
+// wide state belongs to the padded dimensions and is zero.  widen: scatter into a zeroed wide state; else gather.
+__global__ void state_width_kernel(const float* __restrict__ src, float* __restrict__ dst, int order, int widen, long long total) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one element of the narrow state
+  if (idx >= total) return;
+  const int rows32 = order == 2 ? 673 : 33, rows64 = order == 2 ? 2369 : 65;
+  const int c = (int)(idx % 36);
+  const long long hr = idx / 36;
+  const int r = (int)(hr % rows32);
+  const long long head = hr / rows32;
+  int r64;
+  const int npair = order == 2 ? 640 : 0;
+  if (r < npair) {
+    int a, b;
+    pair_decode(r >> 6, 4, a, b);
+    r64 = 64 * (a * 8 - a * (a - 1) / 2 + (b - a)) + (r & 63);
+  } else if (r < npair + 32) {
+    r64 = (order == 2 ? 2304 : 0) + (r - npair);
+  } else {
+    r64 = rows64 - 1;
+  }
+  const int c64 = c < 32 ? c : (c == 32 ? 64 : -1);
+  const long long wide = (head * rows64 + r64) * 68 + c64;
+  if (widen) {
+    if (c64 >= 0) dst[wide] = src[idx];
+  } else {
+    dst[idx] = c64 >= 0 ? src[wide] : 0.f;
+  }
+}
 }  // namespace tc
+
+static size_t wide_state_bytes(const fastmax_problem* pb) {
+  return ((size_t)pb->batch * pb->heads * (pb->order == 2 ? 2369 : 65) * 68 * sizeof(float) + 255) / 256 * 256;
+}
+static cudaError_t launch_state_width(const float* src, float* dst, const fastmax_problem* pb, bool widen, cudaStream_t st) {
+  const long long total = (long long)pb->batch * pb->heads * (pb->order == 2 ? 673 : 33) * 36;
+  if (widen) {
+    cudaError_t e = cudaMemsetAsync(dst, 0, wide_state_bytes(pb), st);
+    if (e != cudaSuccess) return e;
+  }
+  LaunchScope ls(KK_TC_PAD, st);
+  tc::state_width_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(src, dst, pb->order, widen ? 1 : 0, total);
+  return cudaGetLastError();
+}
 
 static bool pad_view_ok(const fastmax_tensor& t) {   // 128-bit accesses on every row
   return t.ptr && ((uintptr_t)t.ptr & 15) == 0 && (t.stride_b & 7) == 0 && (t.stride_h & 7) == 0 && (t.stride_n & 7) == 0;
@@ -615,36 +660,51 @@ static cudaError_t launch_unpad(const void* in, const fastmax_problem* pb, int n
                                                                            View{y.ptr, y.stride_b, y.stride_h, y.stride_n}, nrows);
   return cudaGetLastError();
 }
-// the 64-wide problem and arguments of a narrow forward call, over buffers at `base` (nullptr: only for the predicates)
+// the 64-wide problem and arguments of a narrow forward call, over buffers at `base` (nullptr: only for the predicates);
+// a state-only call (no output) has no q: the keys stand in, as they do for the caller
 static void padded_forward(const fastmax_problem* pb, const fastmax_forward_args* a, char* base, fastmax_problem& pp,
                            fastmax_forward_args& in, size_t& used) {
   pp = *pb;
   pp.d = 64;
-  char* p = base ? base : (char*)256;   // never dereferenced when base is null
+  char* const p0 = base ? base : (char*)256;   // never dereferenced when base is null
+  char* p = p0;
+  const bool want_o = a->o.ptr != nullptr;
   in = fastmax_forward_args{};
-  in.q = padded_view(p, pb, pb->nq); p += padded_bytes(pb, pb->nq);
   in.k = padded_view(p, pb, pb->nk); p += padded_bytes(pb, pb->nk);
   in.v = padded_view(p, pb, pb->nk); p += padded_bytes(pb, pb->nk);
-  in.o = padded_view(p, pb, pb->nq); p += padded_bytes(pb, pb->nq);
-  in.g = a->g;
-  used = (size_t)(p - (base ? base : (char*)256));
+  if (want_o) {
+    in.q = padded_view(p, pb, pb->nq); p += padded_bytes(pb, pb->nq);
+    in.o = padded_view(p, pb, pb->nq); p += padded_bytes(pb, pb->nq);
+    in.g = a->g;
+  } else {
+    in.q = in.k;
+  }
+  if (a->state_in) { in.state_in = (const float*)p; p += wide_state_bytes(pb); }
+  if (a->state_out) { in.state_out = (float*)p; p += wide_state_bytes(pb); }
+  used = (size_t)(p - p0);
 }
 static void padded_backward(const fastmax_problem* pb, const fastmax_backward_args* a, char* base, fastmax_problem& pp,
                             fastmax_backward_args& in, size_t& used) {
   pp = *pb;
   pp.d = 64;
-  char* p = base ? base : (char*)256;
+  char* const p0 = base ? base : (char*)256;
+  char* p = p0;
   in = fastmax_backward_args{};
   in.q = padded_view(p, pb, pb->nq); p += padded_bytes(pb, pb->nq);
   in.k = padded_view(p, pb, pb->nk); p += padded_bytes(pb, pb->nk);
   in.v = padded_view(p, pb, pb->nk); p += padded_bytes(pb, pb->nk);
   in.o = padded_view(p, pb, pb->nq); p += padded_bytes(pb, pb->nq);
   in.d_out = padded_view(p, pb, pb->nq); p += padded_bytes(pb, pb->nq);
-  in.dq = padded_view(p, pb, pb->nq); p += padded_bytes(pb, pb->nq);
-  in.dk = padded_view(p, pb, pb->nk); p += padded_bytes(pb, pb->nk);
-  in.dv = padded_view(p, pb, pb->nk); p += padded_bytes(pb, pb->nk);
+  if (a->dq.ptr) {
+    in.dq = padded_view(p, pb, pb->nq); p += padded_bytes(pb, pb->nq);
+    in.dk = padded_view(p, pb, pb->nk); p += padded_bytes(pb, pb->nk);
+    in.dv = padded_view(p, pb, pb->nk); p += padded_bytes(pb, pb->nk);
+  }
   in.g = a->g;
-  used = (size_t)(p - (base ? base : (char*)256));
+  if (a->state_in) { in.state_in = (const float*)p; p += wide_state_bytes(pb); }
+  if (a->dstate_in) { in.dstate_in = (const float*)p; p += wide_state_bytes(pb); }
+  if (a->dstate_out) { in.dstate_out = (float*)p; p += wide_state_bytes(pb); }
+  used = (size_t)(p - p0);
 }
 static bool tc_forward_paddable(const fastmax_problem* pb, const fastmax_forward_args* a);
 static bool tc_backward_paddable(const fastmax_problem* pb, const fastmax_backward_args* a);
@@ -762,8 +822,10 @@ bool tc_takes_forward(const fastmax_problem* pb, const fastmax_forward_args* a) 
   return tc_p1_supported(pb, a) || tc_forward_segmentable(pb, a) || tc_forward_supported(pb, a) || tc_forward_paddable(pb, a);
 }
 static bool tc_forward_paddable(const fastmax_problem* pb, const fastmax_forward_args* a) {
-  if (!tc_narrow_head(pb) || a->state_in || a->state_out || pb->nq <= 0 || pb->nk <= 0) return false;
-  if (!pad_view_ok(a->q) || !pad_view_ok(a->k) || !pad_view_ok(a->v) || !pad_view_ok(a->o) || !a->g.ptr) return false;
+  if (!tc_narrow_head(pb) || pb->nk <= 0) return false;
+  const bool want_o = a->o.ptr != nullptr;
+  if (want_o ? (pb->nq <= 0 || !pad_view_ok(a->q) || !pad_view_ok(a->o) || !a->g.ptr) : !a->state_out) return false;
+  if (!pad_view_ok(a->k) || !pad_view_ok(a->v)) return false;
   fastmax_problem pp;
   fastmax_forward_args in;
   size_t used;
@@ -777,13 +839,16 @@ static int tc_forward_padded(const fastmax_problem* pb, const fastmax_forward_ar
   fastmax_forward_args in;
   size_t used;
   padded_forward(pb, a, (char*)ws, pp, in, used);
-  cudaError_t e = launch_pad(a->q, pb, pb->nq, in.q.ptr, st);
-  if (e == cudaSuccess) e = launch_pad(a->k, pb, pb->nk, in.k.ptr, st);
+  const bool want_o = a->o.ptr != nullptr;
+  cudaError_t e = launch_pad(a->k, pb, pb->nk, in.k.ptr, st);
   if (e == cudaSuccess) e = launch_pad(a->v, pb, pb->nk, in.v.ptr, st);
+  if (e == cudaSuccess && want_o) e = launch_pad(a->q, pb, pb->nq, in.q.ptr, st);
+  if (e == cudaSuccess && a->state_in) e = launch_state_width(a->state_in, const_cast<float*>(in.state_in), pb, true, st);
   if (e != cudaSuccess) return report_cuda_error(e);
   const int rc = tc_forward(&pp, &in, (char*)ws + used, ws_bytes - used, st);
   if (rc != FASTMAX_OK) return rc == FASTMAX_TC_NOT_HANDLED ? (int)FASTMAX_ERR_UNSUPPORTED : rc;
-  e = launch_unpad(in.o.ptr, pb, pb->nq, a->o, st);
+  if (want_o) e = launch_unpad(in.o.ptr, pb, pb->nq, a->o, st);
+  if (e == cudaSuccess && a->state_out) e = launch_state_width(in.state_out, a->state_out, pb, false, st);
   return e == cudaSuccess ? FASTMAX_OK : report_cuda_error(e);
 }
 
@@ -994,9 +1059,11 @@ bool tc_takes_backward(const fastmax_problem* pb, const fastmax_backward_args* a
   return tc_backward_segmentable(pb, a) || tc_backward_supported(pb, a) || tc_backward_paddable(pb, a);
 }
 static bool tc_backward_paddable(const fastmax_problem* pb, const fastmax_backward_args* a) {
-  if (!tc_narrow_head(pb) || a->state_in || a->dstate_in || a->dstate_out || pb->nq <= 0 || pb->nk <= 0) return false;
-  for (const fastmax_tensor* t : {&a->q, &a->k, &a->v, &a->o, &a->d_out, &a->dq, &a->dk, &a->dv})
+  if (!tc_narrow_head(pb) || pb->nq <= 0 || pb->nk <= 0) return false;
+  for (const fastmax_tensor* t : {&a->q, &a->k, &a->v, &a->o, &a->d_out})
     if (!pad_view_ok(*t)) return false;
+  const bool want_grads = a->dq.ptr != nullptr;
+  if (want_grads ? (!pad_view_ok(a->dq) || !pad_view_ok(a->dk) || !pad_view_ok(a->dv)) : !a->dstate_out) return false;
   if (!a->g.ptr) return false;
   fastmax_problem pp;
   fastmax_backward_args in;
@@ -1015,12 +1082,17 @@ static int tc_backward_padded(const fastmax_problem* pb, const fastmax_backward_
   if (e == cudaSuccess) e = launch_pad(a->v, pb, pb->nk, in.v.ptr, st);
   if (e == cudaSuccess) e = launch_pad(a->o, pb, pb->nq, in.o.ptr, st);
   if (e == cudaSuccess) e = launch_pad(a->d_out, pb, pb->nq, in.d_out.ptr, st);
+  if (e == cudaSuccess && a->state_in) e = launch_state_width(a->state_in, const_cast<float*>(in.state_in), pb, true, st);
+  if (e == cudaSuccess && a->dstate_in) e = launch_state_width(a->dstate_in, const_cast<float*>(in.dstate_in), pb, true, st);
   if (e != cudaSuccess) return report_cuda_error(e);
   const int rc = tc_backward(&pp, &in, (char*)ws + used, ws_bytes - used, st);
   if (rc != FASTMAX_OK) return rc == FASTMAX_TC_NOT_HANDLED ? (int)FASTMAX_ERR_UNSUPPORTED : rc;
-  e = launch_unpad(in.dq.ptr, pb, pb->nq, a->dq, st);
-  if (e == cudaSuccess) e = launch_unpad(in.dk.ptr, pb, pb->nk, a->dk, st);
-  if (e == cudaSuccess) e = launch_unpad(in.dv.ptr, pb, pb->nk, a->dv, st);
+  if (a->dq.ptr) {
+    e = launch_unpad(in.dq.ptr, pb, pb->nq, a->dq, st);
+    if (e == cudaSuccess) e = launch_unpad(in.dk.ptr, pb, pb->nk, a->dk, st);
+    if (e == cudaSuccess) e = launch_unpad(in.dv.ptr, pb, pb->nk, a->dv, st);
+  }
+  if (e == cudaSuccess && a->dstate_out) e = launch_state_width(in.dstate_out, a->dstate_out, pb, false, st);
   return e == cudaSuccess ? FASTMAX_OK : report_cuda_error(e);
 }
 

@@ -74,8 +74,19 @@ class CudaEngine:
         self.ext = load_extension()
         self.cfg = (float(inv_temp), float(a0), float(a1), float(a2), int(p))
 
+    def _compute_dtype(self, k, v):
+        """float32 pieces after torch.set_float32_matmul_precision("medium") (PyTorch's permission to compute float32
+        matmuls in bfloat16) run on bfloat16 copies when that puts them on the tensor-memory kernels; the states that
+        travel between the ranks, the outputs and the gradients stay float32."""
+        if k.dtype != torch.float32 or torch.get_float32_matmul_precision() != "medium":
+            return None
+        kb, vb = k.bfloat16(), v.bfloat16()
+        return torch.bfloat16 if self.ext.forward_engine(kb, kb, vb, True, self.cfg[4]) == 1 else None
+
     def key_state(self, k, v, moments=None):
         it, a0, a1, a2, p = self.cfg
+        if self._compute_dtype(k, v) is not None:
+            k, v = k.bfloat16(), v.bfloat16()
         if moments is None:
             return self.ext.forward(k, k, v, True, it, a0, a1, a2, p, None, True, False, 0)[2]
         res = self.ext.forward(k, k, v, True, it, a0, a1, a2, p, None, True, False, 0, None, moments.buf, True)
@@ -84,15 +95,20 @@ class CudaEngine:
 
     def forward(self, q, k, v, state_in, moments=None):
         it, a0, a1, a2, p = self.cfg
+        cast = self._compute_dtype(k, v) is not None
+        if cast:
+            q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
         if moments is None:
             o, g, _ = self.ext.forward(q, k, v, True, it, a0, a1, a2, p, state_in, False, True, 0)
-            return o, g
+            return (o.float() if cast else o), g
         res = self.ext.forward(q, k, v, True, it, a0, a1, a2, p, state_in, False, True, 0, None, moments.buf, True)
         moments.buf = res[3]
-        return res[0], res[1]
+        return (res[0].float() if cast else res[0]), res[1]
 
     def grad_state(self, q, k, v, o, g, do, state_in, moments=None):
         it, a0, a1, a2, p = self.cfg
+        if self._compute_dtype(k, v) is not None:
+            q, k, v, o, do = q.bfloat16(), k.bfloat16(), v.bfloat16(), o.bfloat16(), do.bfloat16()
         if moments is None:
             return self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, None, True, False, 0)[3]
         res = self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, None, True, False, 0, None, None,
@@ -102,9 +118,13 @@ class CudaEngine:
 
     def backward(self, q, k, v, o, g, do, state_in, dstate_in, moments=None):
         it, a0, a1, a2, p = self.cfg
+        cast = self._compute_dtype(k, v) is not None
+        if cast:
+            q, k, v, o, do = q.bfloat16(), k.bfloat16(), v.bfloat16(), o.bfloat16(), do.bfloat16()
         km, gm = (None, None) if moments is None else (moments.buf, moments.grad_buf)
-        return tuple(self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, dstate_in, False, True, 0,
-                                       None, km, gm, False)[:3])
+        grads = self.ext.backward(q, k, v, o, g, do, True, it, a0, a1, a2, p, state_in, dstate_in, False, True, 0,
+                                  None, km, gm, False)[:3]
+        return tuple(t.float() for t in grads) if cast else tuple(grads)
 
 
 def _moments_kw(engine, carry=None):

@@ -270,6 +270,40 @@ def test_narrow_bf16_heads_run_zero_padded_on_the_tensor_memory_kernels(d, causa
         assert orc.max_norm_err(host(a), host(b)) < 2e-2, name
 
 
+@pytest.mark.parametrize("order", [1, 2])
+def test_narrow_bf16_heads_carry_states_through_the_padded_kernels(order):
+    """Carried moment states of 32-wide heads are converted to the 64-wide layout on the way in and back on the way out:
+    state-only call, continuation from a state, backward with state_in / dstate_in / dstate_out, all against the
+    CUDA-core engine on the narrow tensors."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    d, B, H, n = 32, 2, (40 if order == 1 else 16), 384
+    g = torch.Generator(device="cuda").manual_seed(5 + order)
+    q, k, v, do, k0, v0, q1, do1 = ((torch.randn(B, H, n, d, device="cuda", generator=g) * 0.8).bfloat16() for _ in range(8))
+    it = 1.0 / (2.0 * math.sqrt(d))
+
+    def run(flags):
+        L.profile_collect()
+        L.profile(True)
+        _, _, s0 = L.forward(k0, k0, v0, True, it, order=order, want_state=True, want_output=False, flags=flags)   # earlier keys
+        o, gg, s1 = L.forward(q, k, v, True, it, order=order, state_in=s0, want_state=True, flags=flags)
+        ds1 = L.backward(q1, k, v, o, gg, do1, True, it, order=order, state_in=s0, want_dstate=True, want_grads=False,
+                         flags=flags)[3]                                                                          # "later queries"
+        dq, dk, dv, ds = L.backward(q, k, v, o, gg, do, True, it, order=order, state_in=s0, dstate_in=ds1, want_dstate=True,
+                                    flags=flags)
+        L.check_status()
+        L.profile(False)
+        return (s0, o, gg, s1, ds1, dq, dk, dv, ds), set(L.profile_collect())
+
+    got, kinds = run(0)
+    ref, kinds_ref = run(L.FLAG_NO_TENSOR_CORES)
+    assert "tc_pad" in kinds and not (FFMA & kinds), kinds
+    assert "tc_pad" not in kinds_ref
+    for a, b, name in zip(got, ref, ("s0", "o", "g", "s1", "ds1", "dq", "dk", "dv", "ds")):
+        assert a.shape == b.shape
+        assert orc.max_norm_err(host(a), host(b)) < 2e-2, name
+
+
 def test_random_call_shapes_agree_with_the_cuda_core_engine():
     """Seeded random shapes (order, mask, nq, nk, heads, carried states, state outputs) through the tensor-memory
     kernels and through the CUDA-core engine (FASTMAX_FLAG_NO_TENSOR_CORES): every output within the bf16 tolerance,

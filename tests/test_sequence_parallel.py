@@ -100,7 +100,8 @@ def test_gloo_ranks_reproduce_the_unsplit_sequence(tmp_path, cuts):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("D,dtype,pieces", [(32, torch.float32, 4), (64, torch.float32, 2), (64, torch.bfloat16, 2)])
+@pytest.mark.parametrize("D,dtype,pieces", [(32, torch.float32, 4), (64, torch.float32, 2), (64, torch.bfloat16, 2),
+                                            (32, torch.bfloat16, 2)])
 def test_cuda_engine_pieces_match_whole_sequence(D, dtype, pieces):
     """The schedule of sequence_parallel.forward/backward with the CUDA engine; the exchange between ranks is
     done by hand (sum of the other pieces' states) because all pieces live on one device here."""
