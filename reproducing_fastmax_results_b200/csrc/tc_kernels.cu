@@ -681,6 +681,8 @@ static void padded_forward(const fastmax_problem* pb, const fastmax_forward_args
   }
   if (a->state_in) { in.state_in = (const float*)p; p += wide_state_bytes(pb); }
   if (a->state_out) { in.state_out = (float*)p; p += wide_state_bytes(pb); }
+  in.key_moments_in = a->key_moments_in;     // per-segment moments of the padded problem: opaque to the caller
+  in.key_moments_out = a->key_moments_out;
   used = (size_t)(p - p0);
 }
 static void padded_backward(const fastmax_problem* pb, const fastmax_backward_args* a, char* base, fastmax_problem& pp,
@@ -704,6 +706,9 @@ static void padded_backward(const fastmax_problem* pb, const fastmax_backward_ar
   if (a->state_in) { in.state_in = (const float*)p; p += wide_state_bytes(pb); }
   if (a->dstate_in) { in.dstate_in = (const float*)p; p += wide_state_bytes(pb); }
   if (a->dstate_out) { in.dstate_out = (float*)p; p += wide_state_bytes(pb); }
+  in.key_moments_in = a->key_moments_in;
+  in.grad_moments_in = a->grad_moments_in;
+  in.grad_moments_out = a->grad_moments_out;
   used = (size_t)(p - p0);
 }
 static bool tc_forward_paddable(const fastmax_problem* pb, const fastmax_forward_args* a);
@@ -719,7 +724,9 @@ static bool tc_forward_supported(const fastmax_problem* pb, const fastmax_forwar
 }
 
 static bool tc_forward_segmentable(const fastmax_problem* pb, const fastmax_forward_args* a) {
-  return tc_segments(pb) > 0 && a->o.ptr && a->q.ptr && a->k.ptr && a->v.ptr && a->g.ptr;
+  if (tc_segments(pb) <= 0 || !a->k.ptr || !a->v.ptr) return false;
+  if (a->o.ptr) return a->q.ptr && a->g.ptr;
+  return a->state_out != nullptr;   // a state-only call: the segment moments and their sum
 }
 
 size_t tc_forward_workspace(const fastmax_problem* pb, const fastmax_forward_args* a) {
@@ -731,12 +738,22 @@ size_t tc_forward_workspace(const fastmax_problem* pb, const fastmax_forward_arg
     return used + tc_forward_workspace(&pp, &in) + 256;
   }
   if (tc_forward_segmentable(pb, a)) {
-    // segment states + the workspace of the larger of the two inner calls (the full call: it also has the output)
+    // segment states + the workspace of the larger of the two inner calls
     const int nseg = tc_segments(pb);
     const fastmax_problem vp = seg_problem(pb, nseg);
-    fastmax_forward_args in = *a;
-    in.state_in = nullptr; in.state_out = nullptr;
-    return seg_state_bytes(pb, nseg) + tc_forward_workspace(&vp, &in);
+    fastmax_forward_args mom{};   // the state-only call over the segments
+    mom.q = a->k; mom.k = a->k; mom.v = a->v;
+    float dummy = 0.f;
+    mom.state_out = &dummy;
+    size_t inner = tc_forward_workspace(&vp, &mom);
+    if (a->o.ptr) {               // the full call on the segment view
+      fastmax_forward_args in = *a;
+      in.state_in = &dummy; in.state_out = nullptr;
+      in.key_moments_in = nullptr; in.key_moments_out = nullptr;
+      const size_t full = tc_forward_workspace(&vp, &in);
+      if (full > inner) inner = full;
+    }
+    return seg_state_bytes(pb, nseg) + inner;
   }
   if (!tc_forward_supported(pb, a)) return 0;
   const bool want_o = a->o.ptr && pb->nq > 0;
@@ -810,6 +827,7 @@ static int tc_forward_segmented(const fastmax_problem* pb, const fastmax_forward
   }
   rc = launch_seg_scan(seg, nseg, pb, a->state_in, a->state_out, false, st);   // (2) exclusive prefix, total = state_out
   if (rc != FASTMAX_OK) return rc;
+  if (!a->o.ptr) return FASTMAX_OK;   // a state-only call ends here
   fastmax_forward_args m{};   // (3) every segment from its prefix
   m.q = seg_view(a->q, vp.nq); m.k = seg_view(a->k, vp.nk); m.v = seg_view(a->v, vp.nk);
   m.o = seg_view(a->o, vp.nq); m.g = seg_view(a->g, vp.nq);
@@ -853,6 +871,13 @@ static int tc_forward_padded(const fastmax_problem* pb, const fastmax_forward_ar
 }
 
 size_t tc_key_moments_bytes(const fastmax_problem* pb, const fastmax_forward_args* a) {
+  if (tc_forward_paddable(pb, a)) {
+    fastmax_problem pp;
+    fastmax_forward_args in;
+    size_t used;
+    padded_forward(pb, a, nullptr, pp, in, used);
+    return tc_key_moments_bytes(&pp, &in);
+  }
   return tc_forward_segmentable(pb, a) ? seg_state_bytes(pb, tc_segments(pb)) : 0;
 }
 
@@ -973,7 +998,8 @@ static void tc_bwd_layout(const fastmax_problem* pb, bool want_grads, TcBwdLayou
 }
 
 static bool tc_backward_segmentable(const fastmax_problem* pb, const fastmax_backward_args* a) {
-  if (tc_segments(pb) <= 0 || !(a->dq.ptr && a->dk.ptr && a->dv.ptr)) return false;
+  if (tc_segments(pb) <= 0) return false;
+  if (!(a->dq.ptr && a->dk.ptr && a->dv.ptr) && !(a->dstate_out && !a->dq.ptr)) return false;   // gradients, or a state-only call
   for (const fastmax_tensor* t : {&a->o, &a->d_out})
     if (((uintptr_t)t->ptr & 3) || (t->stride_b & 1) || (t->stride_h & 1) || (t->stride_n & 1)) return false;
   return true;
@@ -990,11 +1016,13 @@ size_t tc_backward_workspace(const fastmax_problem* pb, const fastmax_backward_a
   if (tc_backward_segmentable(pb, a)) {
     const int nseg = tc_segments(pb);
     const fastmax_problem vp = seg_problem(pb, nseg);
+    float dummy = 0.f;
     fastmax_backward_args in = *a;
-    in.state_in = nullptr; in.dstate_in = nullptr; in.dstate_out = nullptr;
+    in.state_in = nullptr; in.dstate_in = nullptr;
+    in.dstate_out = a->dq.ptr ? nullptr : &dummy;   // a state-only call: the gradient-moment call over the segments is the inner call
+    in.key_moments_in = nullptr; in.grad_moments_in = nullptr; in.grad_moments_out = nullptr;
     fastmax_forward_args f{};
     f.q = a->k; f.k = a->k; f.v = a->v;
-    float dummy = 0.f;
     f.state_out = &dummy;   // sizes the state-only inner call
     const size_t inner_f = tc_forward_workspace(&vp, &f), inner_b = tc_backward_workspace(&vp, &in);
     return 2 * seg_state_bytes(pb, nseg) + (inner_f > inner_b ? inner_f : inner_b);
@@ -1049,6 +1077,7 @@ static int tc_backward_segmented(const fastmax_problem* pb, const fastmax_backwa
     if (e != cudaSuccess) return report_cuda_error(e);
   }
   rc = launch_seg_scan(segD, nseg, pb, a->dstate_in, a->dstate_out, true, st);
+  if (rc == FASTMAX_OK && !want_grads) return FASTMAX_OK;   // a state-only call ends here
   if (rc != FASTMAX_OK) return rc;
   m.dq = seg_view(a->dq, vp.nq); m.dk = seg_view(a->dk, vp.nk); m.dv = seg_view(a->dv, vp.nk);
   m.state_in = segS; m.dstate_in = segD;
@@ -1097,6 +1126,13 @@ static int tc_backward_padded(const fastmax_problem* pb, const fastmax_backward_
 }
 
 size_t tc_grad_moments_bytes(const fastmax_problem* pb, const fastmax_backward_args* a) {
+  if (tc_backward_paddable(pb, a)) {
+    fastmax_problem pp;
+    fastmax_backward_args in;
+    size_t used;
+    padded_backward(pb, a, nullptr, pp, in, used);
+    return tc_grad_moments_bytes(&pp, &in);
+  }
   return tc_backward_segmentable(pb, a) ? seg_state_bytes(pb, tc_segments(pb)) : 0;
 }
 

@@ -210,6 +210,42 @@ def test_long_sequence_with_few_heads_is_cut_into_segments(shape):
         assert np.abs(host(dv[0, h])[r] - dv_ref).max() < 2e-2 * scale(dv)
 
 
+@pytest.mark.parametrize("d", [64, 32])
+def test_state_only_calls_of_a_long_sequence_with_few_heads_stay_on_tensor_memory(d):
+    """What a sequence-parallel rank with few heads asks for: the moments of its keys, its piece from a carried state, the
+    gradient moments of its queries, its gradients from a carried state and gradient state.  All four are cut into
+    segments for the tensor-memory kernels (32-wide heads zero-padded on top), none falls back to the CUDA cores."""
+    from reproducing_fastmax_results_b200 import _lib as L
+
+    H, N = 4, 4096
+    g = torch.Generator(device="cuda").manual_seed(31 + d)
+    q, k, v, do, k0, v0 = ((torch.randn(1, H, N, d, device="cuda", generator=g) * 0.7).bfloat16() for _ in range(6))
+    it = 1.0 / (2.0 * math.sqrt(d))
+
+    def run(flags):
+        L.profile_collect()
+        L.profile(True)
+        km = L.KeyMoments()
+        _, _, s0 = L.forward(k0, k0, v0, True, it, order=2, want_state=True, want_output=False, flags=flags)
+        _, _, total = L.forward(k, k, v, True, it, order=2, want_state=True, want_output=False, flags=flags, key_moments=km)
+        o, gg, _ = L.forward(q, k, v, True, it, order=2, state_in=s0, flags=flags, key_moments=km)
+        ds = L.backward(q, k, v, o, gg, do, True, it, order=2, state_in=s0, want_dstate=True, want_grads=False, flags=flags,
+                        key_moments=km)[3]
+        dq, dk, dv, _ = L.backward(q, k, v, o, gg, do, True, it, order=2, state_in=s0, dstate_in=ds * 0.5, flags=flags,
+                                   key_moments=km)
+        L.check_status()
+        L.profile(False)
+        return (s0, total, o, gg, ds, dq, dk, dv), L.profile_collect()
+
+    got, prof = run(0)
+    ref, _ = run(L.FLAG_NO_TENSOR_CORES)
+    assert not (FFMA & set(prof)) and TC_SCANS <= set(prof), prof
+    # key moments: summed by the first state-only call of k, v and handed on (one pass for s0, one for k, v)
+    assert prof["tc_scan_fwd"][1] == 3, prof
+    for a, b, name in zip(got, ref, ("s0", "total", "o", "g", "ds", "dq", "dk", "dv")):
+        assert orc.max_norm_err(host(a), host(b)) < 2e-2, name
+
+
 def test_segmented_call_hands_its_key_moments_to_the_backward():
     """The segmented form sums the key moments of every segment first; with a KeyMoments holder the backward takes the
     forward's sums instead of running that pass again: one update-only scan less, same gradients."""
