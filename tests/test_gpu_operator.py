@@ -316,3 +316,40 @@ def test_float32_callers_reach_the_tensor_memory_kernels_under_medium_matmul_pre
         assert "scan_fwd" in set(_lib.profile_collect())
     finally:
         torch.set_float32_matmul_precision(before)
+
+
+def test_medium_matmul_precision_with_every_option_of_the_operator_switched_on():
+    """Normalisation, RPE add and noise dropout around the bfloat16 attention of a float32 caller under the "medium"
+    float32 matmul precision: outputs and all three gradients agree with the exact float32 run to the bfloat16 tolerance."""
+    import reproducing_fastmax_results_b200 as pkg
+    from reproducing_fastmax_results_b200 import _lib
+
+    B, H, N, D, rate = 2, 16, 256, 32, 0.1   # 32-wide heads: zero-padded on top
+    g = torch.Generator(device="cuda").manual_seed(8)
+    q0, k0, v0, do, noise = (torch.randn(B, H, N, D, device="cuda", generator=g) * 0.7 for _ in range(5))
+    rpe = 0.05 * torch.randn(2 * N - 1, D, device="cuda", generator=g)
+    op = pkg.FASTMultiHeadAttention(apply_rpe=True, noise_dropout=True)
+
+    def run():
+        q, k, v = (t.clone().requires_grad_(True) for t in (q0, k0, v0))
+        _lib.profile_collect()
+        _lib.profile(True)
+        out = op(q, k, v, noise, rpe, True, rate, True, 1.0, 1.0, 1.0, 0.5, 1.0, 2)
+        out.backward(do)
+        torch.cuda.synchronize()
+        _lib.profile(False)
+        assert out.dtype == torch.float32
+        return (out.detach(), q.grad, k.grad, v.grad), set(_lib.profile_collect())
+
+    before = torch.get_float32_matmul_precision()
+    try:
+        torch.set_float32_matmul_precision("highest")
+        exact, kinds_exact = run()
+        torch.set_float32_matmul_precision("medium")
+        fast, kinds_fast = run()
+    finally:
+        torch.set_float32_matmul_precision(before)
+    assert "scan_fwd" in kinds_exact and "tc_scan_fwd" not in kinds_exact
+    assert {"tc_pad", "tc_scan_fwd", "tc_scan_bwd_q"} <= kinds_fast and "scan_fwd" not in kinds_fast, kinds_fast
+    for a, b, name in zip(fast, exact, ("out", "dq", "dk", "dv")):
+        assert orc.max_norm_err(host(a), host(b)) < 2e-2, name
