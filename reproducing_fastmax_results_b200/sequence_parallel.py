@@ -27,17 +27,24 @@ def _world(group=None):
     return dist.get_world_size(group), dist.get_rank(group)
 
 
+def _gather_all(local: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """(world, *local.shape): every rank's `local`, one collective into one buffer."""
+    local = local.contiguous()
+    buf = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+    try:
+        dist.all_gather_into_tensor(buf, local, group=group)
+    except (RuntimeError, NotImplementedError):   # a backend without the single-buffer form
+        dist.all_gather(list(buf.unbind(0)), local, group=group)
+    return buf
+
+
 def exclusive_prefix(local: torch.Tensor, group=None) -> torch.Tensor:
     """Sum of `local` over the ranks BEFORE this one (zeros on rank 0)."""
     world, rank = _world(group)
     if world == 1:
         return torch.zeros_like(local)
-    parts = [torch.empty_like(local) for _ in range(world)]
-    dist.all_gather(parts, local.contiguous(), group=group)
-    out = torch.zeros_like(local)
-    for r in range(rank):
-        out += parts[r]
-    return out
+    buf = _gather_all(local, world, group)
+    return buf[:rank].sum(0) if rank > 0 else torch.zeros_like(local)
 
 
 def exclusive_suffix(local: torch.Tensor, group=None) -> torch.Tensor:
@@ -45,12 +52,8 @@ def exclusive_suffix(local: torch.Tensor, group=None) -> torch.Tensor:
     world, rank = _world(group)
     if world == 1:
         return torch.zeros_like(local)
-    parts = [torch.empty_like(local) for _ in range(world)]
-    dist.all_gather(parts, local.contiguous(), group=group)
-    out = torch.zeros_like(local)
-    for r in range(rank + 1, world):
-        out += parts[r]
-    return out
+    buf = _gather_all(local, world, group)
+    return buf[rank + 1:].sum(0) if rank + 1 < world else torch.zeros_like(local)
 
 
 class KeyMoments:
