@@ -469,7 +469,7 @@ struct ScanGeom {
   int nslices, tps, tile_first, state_rows;
 };
 static int device_sms();
-static ScanGeom scan_geom(const fastmax_problem* pb) {
+static ScanGeom scan_geom(const fastmax_problem* pb, bool backward = false) {
   ScanGeom g{};
   g.k0 = pb->causal ? pb->nk - pb->nq : (pb->nk + tc::CH - 1) / tc::CH * tc::CH;
   const int npos = pb->causal ? pb->nk : g.k0 + pb->nq;
@@ -478,11 +478,20 @@ static ScanGeom scan_geom(const fastmax_problem* pb) {
   g.qc1 = pb->nq > 0 ? (g.k0 + pb->nq - 1) / tc::CH : g.qc0 - 1;
   g.kc0 = 0;
   g.kc1 = (pb->nk - 1) / tc::CH;
-  // Order 2: 19 feature tiles per head, four per thread block (5 slices).  When even that leaves SMs without a block
-  // (fewer than 30 heads on 148 SMs) three per block (7 slices: more, shorter blocks).  Measured on B8..B1 x H16 x
-  // N4096: 4 tiles win from 32 heads up (0.82 vs 0.84 ms, 1.44 vs 1.51 ms), 3 tiles by 2 % at 16 heads.
+  // Order 2: 19 feature tiles per head, four per thread block (5 slices) or three (7 slices: more, shorter blocks; a
+  // block of three tiles takes 0.79 of the time of one of four, so four are 5 % more efficient per tile).  What decides
+  // is how many whole rounds of blocks the 148 SMs run: one scan kernel at a time in the forward call, the three scans
+  // of the backward call side by side.  Three tiles are taken where they save a round.  Measured on B x H16 x N4096,
+  // forward alone / whole step: 16 heads 0.110 vs 0.127 ms with three tiles in the forward call and 0.446 vs 0.459 ms
+  // with four in the backward call; 32 heads 0.200 vs 0.225 and 0.785 vs 0.835; 48 heads and from 96 up four tiles in
+  // both (128 heads: 0.52 vs 0.54 ms forward scan).
   g.tps = 4;
-  if (pb->order == 2 && (long long)pb->batch * pb->heads * 5 < (long long)device_sms()) g.tps = 3;
+  if (pb->order == 2) {
+    const long long bh = (long long)pb->batch * pb->heads, sms = device_sms(), kernels = backward ? 3 : 1;
+    const long long rounds4 = (kernels * 5 * bh + sms - 1) / sms, rounds3 = (kernels * 7 * bh + sms - 1) / sms;
+    // the backward's three scans differ in length, so its rounds are only roughly whole: a wider margin there
+    if ((double)rounds3 * 0.786 < (backward ? 0.90 : 0.97) * (double)rounds4) g.tps = 3;
+  }
   g.nslices = pb->order == 2 ? (tc::NTILES + g.tps - 1) / g.tps : 1;
   g.tile_first = pb->order == 2 ? 0 : tc::NTILES - 1;
   g.state_rows = pb->order == 2 ? 64 * 36 + 65 : 65;
@@ -985,7 +994,7 @@ struct TcBwdLayout {
 };
 static void tc_bwd_layout(const fastmax_problem* pb, bool want_grads, TcBwdLayout& L) {
   const size_t bh = (size_t)pb->batch * pb->heads;
-  const ScanGeom G = scan_geom(pb);
+  const ScanGeom G = scan_geom(pb, true);
   auto up = [](size_t x) { return (x + 255) / 256 * 256; };
   size_t off = 0;
   L.dop = off; off += up(bh * pb->nq * 80 * sizeof(__nv_bfloat16));
@@ -1145,7 +1154,7 @@ int tc_backward(const fastmax_problem* pb, const fastmax_backward_args* a, void*
   tc_bwd_layout(pb, want_grads, L);
   if (ws_bytes < L.total) return FASTMAX_ERR_WORKSPACE;
   const int bh = pb->batch * pb->heads;
-  const ScanGeom G = scan_geom(pb);
+  const ScanGeom G = scan_geom(pb, true);
   char* base = (char*)ws;
   __nv_bfloat16* dop = (__nv_bfloat16*)(base + L.dop);
   float* dqa = (float*)(base + L.dq);
